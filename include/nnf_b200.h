@@ -1,0 +1,179 @@
+/*
+ * nnf_b200 -- C ABI of the hand-written sm_100a kernels for NNFusion's
+ * dequantize-fused low-bit linear path.
+ *
+ * The library is what the generated `cuda_codegen` runtime links instead of
+ * (a) the element-wise Convert / Subtract / Multiply kernels that materialise
+ * dequantised weights and (b) the cuBLAS call behind `Dot`.  All entry points
+ * are stream-ordered, take plain device pointers, and never allocate device
+ * memory: like every kernel of the generated runtime they receive tensors that
+ * live in the runtime's own memory pool.
+ *
+ * Each declaration names the reference interface it stands in for (paths are
+ * relative to the reference project root).
+ */
+#ifndef NNF_B200_H_
+#define NNF_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NNF_B200_VERSION 1
+
+#if defined(__GNUC__)
+#define NNF_B200_API __attribute__((visibility("default")))
+#else
+#define NNF_B200_API
+#endif
+
+/* Status codes.  The generated code wraps calls in a macro that throws
+ * std::runtime_error on non-zero, shaped like CUDA_SAFE_CALL / CUBLAS_SAFE_CALL
+ * (src/nnfusion/core/kernels/cuda_gpu/cuda_langunit.cpp:47-62,115-129). */
+enum
+{
+    NNF_B200_OK = 0,
+    NNF_B200_EINVAL = 1,     /* malformed descriptor or null pointer            */
+    NNF_B200_ENOTSUP = 2,    /* shape / type combination not implemented         */
+    NNF_B200_ECUDA = 3,      /* a CUDA runtime or driver call failed             */
+    NNF_B200_EWORKSPACE = 4, /* workspace too small or missing                   */
+    NNF_B200_ETIMEDOUT = 5,  /* a bounded device-side wait gave up               */
+    NNF_B200_EALIGN = 6      /* a pointer or leading dimension is misaligned     */
+};
+
+/* Element types of activations, scales and outputs (the reference's
+ * element::f32 / element::f16, src/nnfusion/common/type/element_type.hpp:41-55). */
+enum
+{
+    NNF_B200_F32 = 0,
+    NNF_B200_F16 = 1
+};
+
+enum
+{
+    NNF_B200_PROLOGUE_NONE = 0,
+    /* x <- x * rsqrt(mean(x^2) + eps) * gain, row-wise, before the contraction.
+     * Replaces the Multiply -> Sum -> Divide -> Add -> Rsqrt -> Multiply chain
+     * (reduce: src/nnfusion/core/kernels/cuda_gpu/kernels/reduce.hpp:18-600). */
+    NNF_B200_PROLOGUE_RMSNORM = 1
+};
+
+enum
+{
+    NNF_B200_EPILOGUE_NONE = 0,
+    /* y += bias[n].  Replaces cuda::MatMulAdd's separate add kernel
+     * (src/nnfusion/core/kernels/cuda_gpu/kernels/matmuladd.cpp:43-71,145-217). */
+    NNF_B200_EPILOGUE_BIAS = 1,
+    /* y = SiLU(x.W^T) * (x.W2^T) with a second weight set; replaces the fused
+     * Sigmoid -> Multiply -> Multiply element-wise kernel
+     * (src/nnfusion/core/kernels/cuda_gpu/kernels/elementwise_fused.cpp:42-189). */
+    NNF_B200_EPILOGUE_SILU_MUL = 2
+};
+
+enum
+{
+    NNF_B200_KERNEL_AUTO = 0,
+    NNF_B200_KERNEL_GEMV = 1, /* small-M, HBM-bound: M <= 16                         */
+    NNF_B200_KERNEL_GEMM = 2  /* large-M, tensor-bound: TMA + tcgen05 + TMEM          */
+};
+
+/* One quantised weight matrix W[N, K] as the kernels read it.
+ *   bits 8: wq is uint8 [N, K]; zp is uint8 [N, K/group].
+ *   bits 4: wq is [N, K/2] bytes, element k in bits 0-3 of byte k/2 for even k
+ *           and in bits 4-7 for odd k; zp is packed the same way along the
+ *           group axis, [N, ceil(K/group / 2)] bytes.
+ *   scale is fp32 or fp16 [N, K/group] (descriptor field scale_dtype).
+ * dequant(W)[n,k] = (float(q[n,k]) - float(zp[n,k/group])) * scale[n,k/group],
+ * i.e. the Cast -> Sub -> Mul chain of the imported graph
+ * (src/nnfusion/core/kernels/cuda_gpu/kernels/elementwise.hpp:33-157, op table
+ * src/nnfusion/core/kernels/cuda_gpu/cuda_common_ops.hpp:28-97). */
+typedef struct
+{
+    const void* wq;
+    const void* scale;
+    const void* zp;
+} nnf_b200_qweight;
+
+/* Descriptor of y[M,N] = epilogue(prologue(x)[M,K] . dequant(W)[N,K]^T), the
+ * fused replacement of op::Dot with transpose_B
+ * (src/nnfusion/core/operators/op_define/dot.cpp:43-135) fed by the dequant chain.
+ * x and y are dense row-major (leading dimensions K and N). */
+typedef struct
+{
+    int32_t M, N, K;
+    int32_t w_bits;      /* 8 or 4                                                  */
+    int32_t group_size;  /* K elements sharing one (scale, zp); 0 = per row (= K)   */
+    int32_t x_dtype;     /* NNF_B200_F32 / NNF_B200_F16                             */
+    int32_t y_dtype;
+    int32_t scale_dtype;
+    int32_t prologue;
+    int32_t epilogue;
+    float rms_eps;
+    int32_t kernel;      /* NNF_B200_KERNEL_*                                       */
+    int32_t split_k;     /* 0 = chosen by the library                               */
+    int32_t reserved[3]; /* must be zero                                            */
+} nnf_b200_linear_desc;
+
+typedef struct nnf_b200_ctx nnf_b200_ctx;
+
+/* Per-device set-up, called from the generated runtime's cuda_init() next to
+ * cublasCreate (src/nnfusion/engine/pass/codegen/cuda_codegen_pass.cpp:117-168);
+ * reads device properties and raises the kernels' shared-memory limits. */
+NNF_B200_API int nnf_b200_init(int device, nnf_b200_ctx** ctx);
+
+/* Called from cuda_free() (same file, :194-211). */
+NNF_B200_API int nnf_b200_free(nnf_b200_ctx* ctx);
+
+NNF_B200_API const char* nnf_b200_strerror(int status);
+
+/* Text of the last failure on this context ("" if none). */
+NNF_B200_API const char* nnf_b200_last_error(const nnf_b200_ctx* ctx);
+
+/* Number of SMs the context's device reports. */
+NNF_B200_API int nnf_b200_sm_count(const nnf_b200_ctx* ctx);
+
+/* Bytes of scratch the described call needs (0 if none).  The emitter requests
+ * it with KernelEmitter::allocate_tensor so that it is planned into the static
+ * pool (src/nnfusion/core/kernels/kernel_emitter.cpp:282-319).  The scratch must
+ * be zero-filled once before its first use (nnf_b200_workspace_reset); every
+ * call leaves it zeroed again.  Calls that share one scratch buffer must not
+ * overlap on the device. */
+NNF_B200_API size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc);
+
+/* Stream-ordered zero fill of a workspace (cudaMemsetAsync). */
+NNF_B200_API int nnf_b200_workspace_reset(nnf_b200_ctx* ctx, void* stream, void* workspace, size_t bytes);
+
+/* The fused linear.  Stands in for the kernel sequence
+ *   Convert_* -> FusedKernel_*Subtract*Multiply* -> Dot_*_cuda_lib (cuBLAS)
+ * that the reference emits into kernel_entry (cuda::Dot:
+ * src/nnfusion/core/kernels/cuda_gpu/kernels/dot.cpp:27-372; cuda::ElementWiseFused:
+ * .../elementwise_fused.cpp:42-189).
+ *   stream     cudaStream_t the emitted call site passes
+ *              (src/nnfusion/core/kernels/kernel_emitter.cpp:160-181)
+ *   x          [M,K] activations, x_dtype
+ *   w          weight set; w2 second set for NNF_B200_EPILOGUE_SILU_MUL, else NULL
+ *   gain       [K] fp32 RMSNorm gain, or NULL without that prologue
+ *   bias       [N] fp32 bias, or NULL without that epilogue
+ *   y          [M,N] output, y_dtype
+ * Accumulation is fp32.  Returns a status code; failures are also kept as text
+ * for nnf_b200_last_error. */
+NNF_B200_API int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc* desc, const void* x,
+                    const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
+                    const void* bias, void* y, void* workspace, size_t workspace_bytes);
+
+/* Number of kernels the library has launched on this context since init
+ * (a counter for benchmarks; reset by passing reset != 0). */
+NNF_B200_API uint64_t nnf_b200_launch_count(nnf_b200_ctx* ctx, int reset);
+
+/* Host helper: pack `rows` x `cols` uint4 values (one per byte) two per byte,
+ * low nibble first, into rows x ceil(cols/2) bytes.  Used when constants are
+ * written at compile time (src/nnfusion/core/kernels/cuda_gpu/kernels/constant.cpp:34-61). */
+NNF_B200_API int nnf_b200_pack_u4(const uint8_t* vals, size_t rows, size_t cols, uint8_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNF_B200_H_ */

@@ -1,0 +1,238 @@
+// C ABI of the library (declarations and reference citations: include/nnf_b200.h).
+#include <cuda_runtime.h>
+#include <cstring>
+#include <new>
+
+#include "nnf_internal.h"
+
+namespace nnf
+{
+int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg)
+{
+    if (ctx)
+        ctx->last_error = msg;
+    return status;
+}
+} // namespace nnf
+
+namespace
+{
+bool aligned16(const void* p)
+{
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+int validate(nnf_b200_ctx* ctx, const nnf_b200_linear_desc* d)
+{
+    if (!ctx)
+        return NNF_B200_EINVAL;
+    if (!d)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "null descriptor");
+    if (d->M < 1 || d->N < 1 || d->K < 1)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "M, N and K must be positive");
+    if (d->w_bits != 4 && d->w_bits != 8)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "w_bits must be 4 or 8");
+    if (d->group_size < 0)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "group_size must be >= 0");
+    for (int v : {d->x_dtype, d->y_dtype, d->scale_dtype})
+        if (v != NNF_B200_F32 && v != NNF_B200_F16)
+            return nnf::set_error(ctx, NNF_B200_EINVAL, "dtype fields must be NNF_B200_F32 or NNF_B200_F16");
+    if (d->prologue != NNF_B200_PROLOGUE_NONE && d->prologue != NNF_B200_PROLOGUE_RMSNORM)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown prologue");
+    if (d->epilogue < NNF_B200_EPILOGUE_NONE || d->epilogue > NNF_B200_EPILOGUE_SILU_MUL)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown epilogue");
+    if (d->kernel < NNF_B200_KERNEL_AUTO || d->kernel > NNF_B200_KERNEL_GEMM)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown kernel selector");
+    if (d->reserved[0] || d->reserved[1] || d->reserved[2] || d->split_k < 0)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "reserved fields must be zero and split_k >= 0");
+    return NNF_B200_OK;
+}
+
+// Which kernel serves a descriptor: the HBM-bound small-M kernel up to 16 rows, the tensor-core kernel above.
+int pick_kernel(const nnf_b200_linear_desc& d)
+{
+    if (d.kernel != NNF_B200_KERNEL_AUTO)
+        return d.kernel;
+    return d.M <= 16 ? NNF_B200_KERNEL_GEMV : NNF_B200_KERNEL_GEMM;
+}
+} // namespace
+
+extern "C" {
+
+int nnf_b200_init(int device, nnf_b200_ctx** out)
+{
+    if (!out)
+        return NNF_B200_EINVAL;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)
+        return NNF_B200_ECUDA;
+    if (cudaSetDevice(device) != cudaSuccess)
+        return NNF_B200_ECUDA;
+    nnf_b200_ctx* ctx = new (std::nothrow) nnf_b200_ctx();
+    if (!ctx)
+        return NNF_B200_ECUDA;
+    ctx->device = device;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess)
+    {
+        delete ctx;
+        return NNF_B200_ECUDA;
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    ctx->cc_major = prop.major;
+    ctx->cc_minor = prop.minor;
+    if (prop.major != 10)
+    {
+        // Built for sm_100a only: there is no fallback path.
+        delete ctx;
+        return NNF_B200_ENOTSUP;
+    }
+    int rc = nnf::gemv_configure(ctx);
+    if (rc == NNF_B200_OK)
+        rc = nnf::gemm_configure(ctx);
+    if (rc != NNF_B200_OK)
+    {
+        delete ctx;
+        return rc;
+    }
+    *out = ctx;
+    return NNF_B200_OK;
+}
+
+int nnf_b200_free(nnf_b200_ctx* ctx)
+{
+    delete ctx;
+    return NNF_B200_OK;
+}
+
+const char* nnf_b200_strerror(int status)
+{
+    switch (status)
+    {
+    case NNF_B200_OK: return "ok";
+    case NNF_B200_EINVAL: return "invalid argument";
+    case NNF_B200_ENOTSUP: return "not supported";
+    case NNF_B200_ECUDA: return "CUDA call failed";
+    case NNF_B200_EWORKSPACE: return "workspace missing or too small";
+    case NNF_B200_ETIMEDOUT: return "device-side wait timed out";
+    case NNF_B200_EALIGN: return "misaligned pointer";
+    default: return "unknown status";
+    }
+}
+
+const char* nnf_b200_last_error(const nnf_b200_ctx* ctx)
+{
+    return ctx ? ctx->last_error.c_str() : "";
+}
+
+int nnf_b200_sm_count(const nnf_b200_ctx* ctx)
+{
+    return ctx ? ctx->sm_count : 0;
+}
+
+size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc)
+{
+    if (!ctx || !desc)
+        return 0;
+    if (pick_kernel(*desc) == NNF_B200_KERNEL_GEMV)
+    {
+        nnf::GemvPlan plan;
+        std::string why;
+        if (nnf::gemv_plan(ctx, *desc, &plan, &why) != NNF_B200_OK)
+            return 0;
+        return plan.workspace_bytes;
+    }
+    return nnf::gemm_workspace_bytes(ctx, *desc);
+}
+
+int nnf_b200_workspace_reset(nnf_b200_ctx* ctx, void* stream, void* workspace, size_t bytes)
+{
+    if (!ctx)
+        return NNF_B200_EINVAL;
+    if (bytes == 0)
+        return NNF_B200_OK;
+    if (!workspace)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "null workspace");
+    cudaError_t e = cudaMemsetAsync(workspace, 0, bytes, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess)
+        return nnf::set_error(ctx, NNF_B200_ECUDA, std::string("cudaMemsetAsync: ") + cudaGetErrorString(e));
+    return NNF_B200_OK;
+}
+
+int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc* desc, const void* x,
+                    const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias,
+                    void* y, void* workspace, size_t workspace_bytes)
+{
+    int rc = validate(ctx, desc);
+    if (rc != NNF_B200_OK)
+        return rc;
+    const nnf_b200_linear_desc& d = *desc;
+    if (!x || !y || !w || !w->wq || !w->scale || !w->zp)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "x, y and the weight set must be non-null");
+    const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
+    if (dual && (!w2 || !w2->wq || !w2->scale || !w2->zp))
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "SiLU*mul epilogue needs the second weight set");
+    if (!dual && w2)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "second weight set given without the SiLU*mul epilogue");
+    if (d.prologue == NNF_B200_PROLOGUE_RMSNORM && !gain)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "RMSNorm prologue needs gain");
+    if (d.prologue != NNF_B200_PROLOGUE_RMSNORM && gain)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "gain given without the RMSNorm prologue");
+    if (d.epilogue == NNF_B200_EPILOGUE_BIAS && !bias)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "bias epilogue needs bias");
+    if (d.epilogue != NNF_B200_EPILOGUE_BIAS && bias)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "bias given without the bias epilogue");
+    if (!aligned16(x) || !aligned16(w->wq) || (dual && !aligned16(w2->wq)) || (gain && !aligned16(gain)))
+        return nnf::set_error(ctx, NNF_B200_EALIGN, "x, wq and gain must be 16-byte aligned");
+    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return nnf::set_error(ctx, NNF_B200_EALIGN, "workspace must be 256-byte aligned");
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (pick_kernel(d) == NNF_B200_KERNEL_GEMV)
+    {
+        nnf::GemvPlan plan;
+        std::string why;
+        rc = nnf::gemv_plan(ctx, d, &plan, &why);
+        if (rc != NNF_B200_OK)
+            return nnf::set_error(ctx, rc, why);
+        if (plan.workspace_bytes > 0 && (!workspace || workspace_bytes < plan.workspace_bytes))
+            return nnf::set_error(ctx, NNF_B200_EWORKSPACE,
+                                  "workspace of " + std::to_string(plan.workspace_bytes) + " bytes required");
+        return nnf::gemv_launch(ctx, s, d, plan, x, w, w2, gain, bias, y, workspace);
+    }
+    std::string why;
+    rc = nnf::gemm_supported(ctx, d, &why);
+    if (rc != NNF_B200_OK)
+        return nnf::set_error(ctx, rc, why);
+    return nnf::gemm_launch(ctx, s, d, x, w, w2, gain, bias, y, workspace, workspace_bytes);
+}
+
+uint64_t nnf_b200_launch_count(nnf_b200_ctx* ctx, int reset)
+{
+    if (!ctx)
+        return 0;
+    uint64_t v = ctx->launches;
+    if (reset)
+        ctx->launches = 0;
+    return v;
+}
+
+int nnf_b200_pack_u4(const uint8_t* vals, size_t rows, size_t cols, uint8_t* out)
+{
+    if (!vals || !out)
+        return NNF_B200_EINVAL;
+    const size_t ob = (cols + 1) / 2;
+    for (size_t r = 0; r < rows; r++)
+        for (size_t b = 0; b < ob; b++)
+        {
+            const uint8_t lo = vals[r * cols + 2 * b];
+            const uint8_t hi = (2 * b + 1 < cols) ? vals[r * cols + 2 * b + 1] : 0;
+            if (lo > 15 || hi > 15)
+                return NNF_B200_EINVAL;
+            out[r * ob + b] = (uint8_t)(lo | (hi << 4));
+        }
+    return NNF_B200_OK;
+}
+}

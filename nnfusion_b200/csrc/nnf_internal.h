@@ -1,0 +1,53 @@
+// Internal declarations shared by the C-ABI translation unit and the kernel launchers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+
+#include "nnf_b200.h"
+
+struct nnf_b200_ctx
+{
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;          // max dynamic shared memory per block (opt-in)
+    int cc_major = 0, cc_minor = 0;
+    uint64_t launches = 0;
+    std::string last_error;
+    void* encode_tiled = nullptr; // cuTensorMapEncodeTiled entry point (driver)
+};
+
+namespace nnf
+{
+// Launch plan of the small-M kernel, shared by workspace sizing and launch.
+struct GemvPlan
+{
+    int mb = 1;          // 8-row batches of x (1: M <= 8, 2: M <= 16)
+    int warps = 8;       // warps per CTA = K slices per split
+    int splits = 1;      // split-K factor
+    int depth = 4;       // tiles in the shared-memory load ring
+    int ctas_per_split = 1;
+    int row_tiles = 0;   // ceil(N / 16)
+    int slices = 0;      // 128-byte weight-row slices along K
+    bool dual = false;
+    bool xsplit = false; // activations carried as fp16 hi + lo
+    size_t slot_floats = 0;     // floats per (split, row tile) partial slot
+    size_t workspace_bytes = 0; // 0 when splits == 1
+};
+
+int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
+
+int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan, std::string* why);
+int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan,
+                const void* x, const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
+                const void* bias, void* y, void* workspace);
+int gemv_configure(nnf_b200_ctx* ctx);
+
+size_t gemm_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d);
+int gemm_supported(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, std::string* why);
+int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const void* x,
+                const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias,
+                void* y, void* workspace, size_t workspace_bytes);
+int gemm_configure(nnf_b200_ctx* ctx);
+} // namespace nnf
