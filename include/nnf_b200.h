@@ -80,6 +80,16 @@ enum
     NNF_B200_KERNEL_GEMM = 2  /* large-M, tensor-bound: TMA + tcgen05 + TMEM          */
 };
 
+/* Descriptor flags. */
+enum
+{
+    /* Small-M kernel: subtract the zero-point from the fp16 integers before the
+     * tensor-core multiply (bit-exact integer operands) instead of taking
+     * sum((offset + zp) * x) out of the fp32 accumulator afterwards.  Slower;
+     * the default differs from it by fp32 rounding only. */
+    NNF_B200_FLAG_EXACT_ZP = 1
+};
+
 /* One quantised weight matrix W[N, K] as the kernels read it.
  *   bits 8: wq is uint8 [N, K]; zp is uint8 [N, K/group].
  *   bits 4: wq is [N, K/2] bytes, element k in bits 0-3 of byte k/2 for even k
@@ -114,7 +124,8 @@ typedef struct
     float rms_eps;
     int32_t kernel;      /* NNF_B200_KERNEL_*                                       */
     int32_t split_k;     /* 0 = chosen by the library                               */
-    int32_t reserved[3]; /* must be zero                                            */
+    int32_t flags;       /* NNF_B200_FLAG_*                                         */
+    int32_t reserved[2]; /* must be zero                                            */
 } nnf_b200_linear_desc;
 
 typedef struct nnf_b200_ctx nnf_b200_ctx;
@@ -143,6 +154,13 @@ NNF_B200_API int nnf_b200_sm_count(const nnf_b200_ctx* ctx);
  * overlap on the device. */
 NNF_B200_API size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc);
 
+/* Launch shape the library would use for a descriptor, for tuning and reporting:
+ * out[0] kernel (NNF_B200_KERNEL_*), out[1] warps per CTA, out[2] split-K factor,
+ * out[3] load-ring depth, out[4] CTAs, out[5] dynamic shared memory in bytes,
+ * out[6..7] zero.  ctx may be NULL (a 148-SM device is assumed).  No reference
+ * counterpart: the reference leaves such choices to cuBLAS. */
+NNF_B200_API int nnf_b200_linear_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc, int32_t out[8]);
+
 /* Stream-ordered zero fill of a workspace (cudaMemsetAsync). */
 NNF_B200_API int nnf_b200_workspace_reset(nnf_b200_ctx* ctx, void* stream, void* workspace, size_t bytes);
 
@@ -163,6 +181,11 @@ NNF_B200_API int nnf_b200_workspace_reset(nnf_b200_ctx* ctx, void* stream, void*
 NNF_B200_API int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc* desc, const void* x,
                     const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
                     const void* bias, void* y, void* workspace, size_t workspace_bytes);
+
+/* Reads (and clears) the device-side status word: 0, or NNF_B200_ETIMEDOUT when a
+ * bounded wait inside a kernel gave up since the last query.  Synchronises the
+ * stream; meant for tests and debugging, not for the hot path. */
+NNF_B200_API int nnf_b200_device_status(nnf_b200_ctx* ctx, void* stream);
 
 /* Number of kernels the library has launched on this context since init
  * (a counter for benchmarks; reset by passing reset != 0). */

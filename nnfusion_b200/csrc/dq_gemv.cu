@@ -5,42 +5,43 @@
 // followed by the cuBLAS Dot (src/nnfusion/core/kernels/cuda_gpu/kernels/dot.cpp:27-372): the
 // weights are read once, at their packed size, and never materialised in fp32.
 //
-// The kernel is HBM-bound.  Work decomposition:
-//   * a weight row is cut into 128-byte "slices" (256 uint4 / 128 uint8 elements); warp w of a CTA owns
-//     slice (split * warps + w) for the whole launch, so the activations it needs are loaded once and
-//     live in registers as mma B-fragments;
-//   * a CTA walks over 16-row tiles of W (persistent, round-robin); per tile every lane issues four
-//     128-bit loads (rows g and g+8, two 64-byte halves of the slice), so each row is touched in
-//     128 contiguous bytes per warp and 128*warps contiguous bytes per CTA.  The loads are cp.async copies
-//     into a shared-memory ring several tiles deep; every thread later reads back exactly the 16-byte
-//     chunks it copied itself, so the ring needs no barrier and holds the bytes in flight that an
-//     HBM-bound kernel needs without spending registers on them;
-//   * nibbles/bytes are turned into exact fp16 integers with one LOP3/PRMT each (the 0x6400 / 0x5400
-//     exponent trick), the zero-point is removed exactly in fp16, and the products are accumulated in
-//     fp32 by mma.sync.m16n8k16 with W as the 16-row operand and up to 8 batch rows as the 8-column
-//     operand (the contraction index is permuted identically on both sides, so no data shuffling is
-//     needed).  The group scale multiplies the fp32 partial sum once per 64-byte half, which keeps the
-//     arithmetic equal to (q - zp) * scale accumulated in fp32;
-//   * the partial sums of the CTA's warps are added in shared memory; with split-K each split stores
-//     its tile sums into its own workspace slot and the split that arrives last (a counter per tile)
-//     adds the slots in a fixed order, so results do not depend on timing.  No thread ever waits on
-//     another CTA.
+// The kernel is HBM-bound and, next to that, bound by instruction issue; its shape follows from both:
+//   * a weight row is cut into 128-byte "slices" (256 uint4 / 128 uint8 elements).  Warp w of a CTA owns slice
+//     (first slice of the CTA's K range + w) for the whole launch, so the activations it needs are loaded and
+//     converted once and live in registers as mma B fragments;
+//   * CTAs are persistent: CTA c of a K split walks over the 16-row tiles c, c + P, c + 2P ...  The weight tiles
+//     arrive by TMA (one thread issues a 16-row x 128-byte box per warp and tile, 128-byte swizzle, completion
+//     counted on an mbarrier per ring slot) into a shared-memory ring several tiles deep, which holds the bytes in
+//     flight that an HBM-bound kernel needs without spending registers or load instructions on them; scales and
+//     zero-points are prefetched two tiles ahead in registers;
+//   * nibbles/bytes become exact fp16 integers with one LOP3/PRMT per pair (the 0x6400 / 0x5400 exponent trick)
+//     and feed mma.sync.m16n8k16 with W as the 16-row operand and up to 8 batch rows as the 8-column operand (the
+//     contraction index is permuted identically on both sides, so nothing is shuffled); accumulation is fp32 and
+//     the group scale multiplies the fp32 sum of each 64-byte unit, i.e. sum((q - zp) * x) * scale;
+//   * the partial sums of the CTA's warps are added in shared memory in a fixed order, once per two tiles; with
+//     split-K each split stores its tile sums into its own workspace slot and the split that arrives last (a
+//     counter per tile) adds the slots in a fixed order, so results are bitwise repeatable.  Nothing ever waits on
+//     another CTA, and every mbarrier wait is bounded.
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <cstdio>
 
 #include "nnf_internal.h"
+#include "sm100_ptx.cuh"
 
 namespace
 {
-constexpr int kMaxWarps = 8;
-constexpr int kBatch = 8;    // row tiles whose results are kept in shared memory between flushes
-constexpr int kMaxDepth = 8; // deepest load ring
+using namespace nnf::ptx;
+
+constexpr int kMaxWarps = 16;
+constexpr int kBatch = 8;            // row tiles whose results are kept in shared memory between flushes
+constexpr int kMaxDepth = 8;         // deepest load ring
+constexpr int kTileBytes = 16 * 128; // one warp's weight tile: 16 rows x 128 bytes
 
 struct GemvParams
 {
-    const uint8_t* wq[2];
     const void* scale[2];
     const uint8_t* zp[2];
     const void* x;
@@ -49,54 +50,26 @@ struct GemvParams
     void* y;
     float* ws_slots;
     unsigned* ws_count;
+    int* status; // device status word: set to 1 when a bounded wait gave up
     int M, N, K;
-    int group, G, zp_row_bytes, row_bytes;
+    int group, G, zp_row_bytes;
     int units;  // 64-byte units per weight row
     int slices; // ceil(units / 2)
     int row_tiles, splits, ctas_per_split;
-    int slices_base, slices_rem; // split s owns slices_base + (s < slices_rem) consecutive slices
     int x_f32, y_f32, scale_f32, rmsnorm, has_bias;
     int fast_params; // scale / zero-point tensors may be read as aligned 32-bit words
-    int depth;       // ring depth (tiles in flight + 1)
+    int depth;       // ring depth in row tiles
     float eps;
     int slot_floats;
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t smem, const void* g)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(g) : "memory");
-}
-__device__ __forceinline__ void cp_async4(uint32_t smem, const void* g)
-{
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem), "l"(g) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit()
-{
-    asm volatile("cp.async.commit_group;" ::: "memory");
-}
-// Wait until at most `pending` of this thread's committed groups are still in flight.
-__device__ __forceinline__ void cp_async_wait(int pending)
-{
-    switch (pending)
-    {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
-    }
-}
-
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1)
 {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-                 "{%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 template <uint32_t MASK, uint32_t ORV>
@@ -123,8 +96,8 @@ template <int WBITS>
 struct Fmt
 {
     static constexpr int UE = (WBITS == 4) ? 128 : 64; // elements per 64-byte unit
-    static constexpr int LE = UE / 4;                  // elements per lane per 16-byte load
-    static constexpr int NF = LE / 2;                  // half2 fragments per load
+    static constexpr int LE = UE / 4;                  // elements per lane per 16-byte chunk
+    static constexpr int NF = LE / 2;                  // half2 fragments per chunk
 };
 
 // Shared-memory footprint, shared by host and device.
@@ -134,22 +107,27 @@ struct Smem
     static constexpr int SETS = DUAL ? 2 : 1;
     static constexpr int TILE_F = SETS * MB * 128; // floats of one tile result: [set][mb][lane][4]
     static constexpr int MPAD = 8 * MB;
-    // per thread and ring slot: SETS * 4 weight chunks of 16 bytes + SETS * 2 (scale word, zp word) pairs
-    static constexpr int SLOT_BYTES_PER_THREAD = SETS * (4 * 16 + 2 * 8);
-    __host__ __device__ static size_t ring_bytes(int threads, int depth)
+    __host__ __device__ static size_t ring_bytes(int warps, int depth)
     {
-        return (size_t)depth * threads * SLOT_BYTES_PER_THREAD;
+        return (size_t)depth * SETS * warps * kTileBytes;
     }
     __host__ __device__ static size_t total_bytes(int warps, int depth)
     {
-        return ring_bytes(warps * 32, depth) +
+        return 1024 /* alignment slack */ + ring_bytes(warps, depth) + 8 * kMaxDepth +
                sizeof(float) * ((size_t)2 * warps * 2 * TILE_F + kBatch * TILE_F + warps * MPAD + MPAD) +
                sizeof(int) * kBatch;
     }
 };
 
-template <int WBITS, int MB, bool XSPLIT, bool DUAL>
-__global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_kernel(const GemvParams p)
+// EXACT = true : zero-points are removed from the fp16 integers before the multiply (bit-exact integers into the
+//                tensor core).
+// EXACT = false: the tensor core multiplies x by (offset + q) and the offset and zero-point are taken out of the
+//                fp32 sum afterwards, acc - (C1 + zp * C2), with C1 = sum(offset_k * x_k), C2 = sum(x_k) over the
+//                64-byte unit.  Same fp32 accumulation, about 40 % fewer unpack instructions.
+template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1)
+    dq_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap0,
+                   const __grid_constant__ CUtensorMap tmap1)
 {
     using F = Fmt<WBITS>;
     using S = Smem<MB, DUAL>;
@@ -159,29 +137,65 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
     constexpr int TILE_F = S::TILE_F;
     constexpr int MPAD = S::MPAD;
 
-    extern __shared__ uint4 smem_u4[];
+    extern __shared__ uint8_t smem_raw[];
     const int nthreads = blockDim.x;
     const int nwarps = nthreads >> 5;
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
 
-    // ring: [depth][SETS*4][nthreads] uint4 weights, then [depth][SETS*2][nthreads] uint2 {scale word, zp word}
-    uint4* wring = smem_u4;
-    uint2* pring = reinterpret_cast<uint2*>(wring + (size_t)p.depth * SETS * 4 * nthreads);
-    float* red = reinterpret_cast<float*>(pring + (size_t)p.depth * SETS * 2 * nthreads); // [2][nwarps][2*TILE_F]
-    float* res = red + 2 * nwarps * 2 * TILE_F;                                           // [kBatch][TILE_F]
-    float* ss_w = res + kBatch * TILE_F;                                                  // [nwarps][MPAD]
-    float* ss_cta = ss_w + nwarps * MPAD;                                                 // [MPAD]
-    int* last_flag = reinterpret_cast<int*>(ss_cta + MPAD);                               // [kBatch]
-    const uint32_t wring_s = (uint32_t)__cvta_generic_to_shared(wring);
-    const uint32_t pring_s = (uint32_t)__cvta_generic_to_shared(pring);
+    // ring (1024-byte aligned: the TMA 128-byte swizzle is a function of the shared-memory address):
+    //   [depth][SETS][nwarps] tiles of 16 rows x 128 bytes
+    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + S::ring_bytes(nwarps, p.depth)); // [kMaxDepth]
+    float* red = reinterpret_cast<float*>(full_bar + kMaxDepth);                             // [2][nwarps][2*TILE_F]
+    float* res = red + 2 * nwarps * 2 * TILE_F;                                              // [kBatch][TILE_F]
+    float* ss_w = res + kBatch * TILE_F;                                                     // [nwarps][MPAD]
+    float* ss_cta = ss_w + nwarps * MPAD;                                                    // [MPAD]
+    int* last_flag = reinterpret_cast<int*>(ss_cta + MPAD);                                  // [kBatch]
+    const uint32_t ring_s = smem_u32(ring);
+    const uint32_t bar_s = smem_u32(full_bar);
 
     const int split = blockIdx.x / p.ctas_per_split;
     const int cta_in_split = blockIdx.x - split * p.ctas_per_split;
-    const int my_slices = p.slices_base + (split < p.slices_rem ? 1 : 0);
-    const int slice = split * p.slices_base + min(split, p.slices_rem) + warp;
+    const int sb = p.slices / p.splits, sr = p.slices % p.splits; // K ranges differ by at most one slice
+    const int my_slices = sb + (split < sr ? 1 : 0);
+    const int slice0 = split * sb + min(split, sr);
+    const int slice = slice0 + warp;
     const bool has_slice = warp < my_slices;
+    const int nsteps = (cta_in_split < p.row_tiles)
+                           ? (p.row_tiles - cta_in_split + p.ctas_per_split - 1) / p.ctas_per_split
+                           : 0;
+
+    // ---------------------------------------------------------------- TMA producer (thread 0)
+    // One 16-row x 128-byte box per (weight set, slice) and row tile, all counted on the slot's barrier.
+    auto produce = [&](int step) {
+        if (step < nsteps)
+        {
+            const int slot = step % p.depth;
+            const uint32_t bar = bar_s + 8 * slot;
+            const int row0 = (cta_in_split + step * p.ctas_per_split) * 16;
+            mbar_arrive_expect_tx(bar, (uint32_t)(SETS * my_slices * kTileBytes));
+            for (int w = 0; w < my_slices; w++)
+            {
+                tma_load_2d(ring_s + (uint32_t)(((slot * SETS + 0) * nwarps + w) * kTileBytes), &tmap0, bar,
+                            (slice0 + w) * 128, row0);
+                if (DUAL)
+                    tma_load_2d(ring_s + (uint32_t)(((slot * SETS + 1) * nwarps + w) * kTileBytes), &tmap1, bar,
+                                (slice0 + w) * 128, row0);
+            }
+        }
+    };
+    if (tid == 0)
+    {
+        for (int i = 0; i < p.depth; i++)
+            mbar_init(bar_s + 8 * i, 1);
+        fence_barrier_init();
+        // Weights do not depend on the activations: start streaming before anybody touches x.  (The arrive on
+        // the barrier waits for this thread's earlier loads, so nothing is loaded ahead of it.)
+        for (int i = 0; i < p.depth; i++)
+            produce(i);
+    }
 
     int unit_of[2], grp_of[2];
     bool unit_ok[2];
@@ -205,49 +219,40 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
         fast = fast && sc_ok && zp_ok;
     }
 
-    const int nsteps = (cta_in_split < p.row_tiles)
-                           ? (p.row_tiles - cta_in_split + p.ctas_per_split - 1) / p.ctas_per_split
-                           : 0;
-
-    // ---------------------------------------------------------------- asynchronous loads of one row tile
-    auto issue = [&](int step) {
-        if (has_slice && step < nsteps)
-        {
-            const int slot = step % p.depth;
-            const int rt = cta_in_split + step * p.ctas_per_split;
-            int row[2];
-            row[0] = min(rt * 16 + g, p.N - 1);
-            row[1] = min(rt * 16 + g + 8, p.N - 1);
-#pragma unroll
-            for (int s = 0; s < SETS; s++)
-#pragma unroll
-                for (int h = 0; h < 2; h++)
-                {
-                    const uint8_t* wrow = p.wq[s] + (size_t)row[h] * p.row_bytes + t * 16;
-#pragma unroll
-                    for (int l = 0; l < 2; l++)
-                        cp_async16(wring_s + (uint32_t)(((slot * SETS + s) * 4 + h * 2 + l) * nthreads + tid) * 16u,
-                                   wrow + unit_of[l] * 64);
-                    if (fast)
-                    {
-                        const uint32_t dst = pring_s + (uint32_t)(((slot * SETS + s) * 2 + h) * nthreads + tid) * 8u;
-                        const size_t sidx = (size_t)row[h] * p.G + grp_of[0];
-                        const char* sp = static_cast<const char*>(p.scale[s]);
-                        cp_async4(dst, p.scale_f32 ? sp + sidx * 4 : sp + ((sidx * 2) & ~(size_t)3));
-                        const size_t zoff = (WBITS == 4) ? (size_t)row[h] * p.zp_row_bytes + (grp_of[0] >> 1) : sidx;
-                        cp_async4(dst + 4, p.zp[s] + (zoff & ~(size_t)3));
-                    }
-                }
-        }
-        cp_async_commit();
+    // ---------------------------------------------------------------- quantisation parameters of one row tile
+    struct PReg
+    {
+        uint32_t sw[SETS][2]; // word holding the scale(s) of row g / g+8
+        uint32_t zw[SETS][2]; // word holding the zero-point(s)
     };
+    auto row_of = [&](int step, int h) { return min((cta_in_split + step * p.ctas_per_split) * 16 + g + 8 * h, p.N - 1); };
+    auto load_params = [&](PReg& r, int step) {
+        if (fast && has_slice && step < nsteps)
+        {
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+            {
+                const int row = row_of(step, h);
+                const size_t sidx = (size_t)row * p.G + grp_of[0];
+                const size_t zoff = (WBITS == 4) ? (size_t)row * p.zp_row_bytes + (grp_of[0] >> 1) : sidx;
+#pragma unroll
+                for (int s = 0; s < SETS; s++)
+                {
+                    const char* sp = static_cast<const char*>(p.scale[s]);
+                    r.sw[s][h] = __ldg(reinterpret_cast<const uint32_t*>(
+                        p.scale_f32 ? sp + sidx * 4 : sp + ((sidx * 2) & ~(size_t)3)));
+                    r.zw[s][h] = __ldg(reinterpret_cast<const uint32_t*>(p.zp[s] + (zoff & ~(size_t)3)));
+                }
+            }
+        }
+    };
+    PReg pr[3]; // tiles step, step + 1, step + 2
+    load_params(pr[0], 0);
+    load_params(pr[1], 1);
 
-    // Weights do not depend on the activations: start streaming before touching x.
-    for (int j = 0; j < p.depth - 1; j++)
-        issue(j);
-
-    // ---------------------------------------------------------------- activations -> B fragments
+    // ---------------------------------------------------------------- activations -> B fragments in registers
     uint32_t xf[2][MB][XS][NF];
+    float c1[2][MB][2], c2[2][MB][2]; // offset / zero-point corrections for accumulator columns 2t, 2t+1
     float ss_local[MB];
 #pragma unroll
     for (int mb = 0; mb < MB; mb++)
@@ -311,31 +316,48 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
                     xv[j] = 0.f;
             }
             __half hi[F::LE], lo[F::LE];
+            float se = 0.f, so = 0.f; // sums of what the tensor core will see, even / odd element positions
 #pragma unroll
             for (int j = 0; j < F::LE; j++)
             {
                 hi[j] = __float2half_rn(xv[j]);
-                lo[j] = XSPLIT ? __float2half_rn(xv[j] - __half2float(hi[j])) : __half();
+                float seen = __half2float(hi[j]);
+                if (XSPLIT)
+                {
+                    lo[j] = __float2half_rn(xv[j] - seen);
+                    seen += __half2float(lo[j]);
+                }
+                if (j & 1)
+                    so += seen;
+                else
+                    se += seen;
             }
 #pragma unroll
             for (int f = 0; f < NF; f++)
             {
                 // Element order inside a fragment mirrors the order the weight unpacking produces:
                 // uint4 word i yields pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7); uint8 word i yields (b0,b1) (b2,b3).
-                int e0, e1;
-                if (WBITS == 4)
-                {
-                    e0 = 8 * (f >> 2) + (f & 3);
-                    e1 = e0 + 4;
-                }
-                else
-                {
-                    e0 = 2 * f;
-                    e1 = e0 + 1;
-                }
+                const int e0 = (WBITS == 4) ? 8 * (f >> 2) + (f & 3) : 2 * f;
+                const int e1 = (WBITS == 4) ? e0 + 4 : e0 + 1;
                 xf[l][mb][0][f] = pack_h2(hi[e0], hi[e1]);
                 if (XSPLIT)
                     xf[l][mb][XS - 1][f] = pack_h2(lo[e0], lo[e1]);
+            }
+            if (!EXACT)
+            {
+                // uint4: even positions carry offset 1024 (bits 0-3 of a half), odd positions 64 (bits 4-7);
+                // uint8: every position carries 1024.
+                float a1 = (WBITS == 4) ? 1024.f * se + 64.f * so : 1024.f * (se + so);
+                float a2 = se + so;
+                a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+                a2 += __shfl_xor_sync(0xffffffffu, a2, 1);
+                a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+                a2 += __shfl_xor_sync(0xffffffffu, a2, 2);
+                // every lane of quad g now holds the unit sums of batch row g; fetch those of rows 2t, 2t+1
+                c1[l][mb][0] = __shfl_sync(0xffffffffu, a1, (2 * t) * 4);
+                c1[l][mb][1] = __shfl_sync(0xffffffffu, a1, (2 * t + 1) * 4);
+                c2[l][mb][0] = __shfl_sync(0xffffffffu, a2, (2 * t) * 4);
+                c2[l][mb][1] = __shfl_sync(0xffffffffu, a2, (2 * t + 1) * 4);
             }
         }
     }
@@ -353,7 +375,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
             if (t == 0)
                 ss_w[warp * MPAD + g + 8 * mb] = v;
         }
-        __syncthreads();
+    }
+    __syncthreads(); // barrier initialisation and ss_w visible to everybody
+    if (p.rmsnorm)
+    {
         if (tid < MPAD)
         {
             float v = 0.f;
@@ -366,15 +391,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
 
     // ---------------------------------------------------------------- arithmetic on one landed row tile
     float tot[SETS][MB][4];
-    auto compute = [&](int step) {
-        const int slot = step % p.depth;
-#pragma unroll
-        for (int s = 0; s < SETS; s++)
-#pragma unroll
-            for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-                for (int c = 0; c < 4; c++)
-                    tot[s][mb][c] = 0.f;
+    auto compute = [&](int step, int slot, const PReg& prm) {
 #pragma unroll
         for (int s = 0; s < SETS; s++)
         {
@@ -386,23 +403,23 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
 #pragma unroll
                 for (int h = 0; h < 2; h++)
                 {
-                    const uint2 pw = pring[((slot * SETS + s) * 2 + h) * nthreads + tid];
-                    const int row = min((cta_in_split + step * p.ctas_per_split) * 16 + g + 8 * h, p.N - 1);
-                    const size_t sidx = (size_t)row * p.G + grp_of[0];
-                    const size_t zoff = (WBITS == 4) ? (size_t)row * p.zp_row_bytes + (grp_of[0] >> 1) : sidx;
+                    const int row = row_of(step, h);
+                    const uint32_t sidx_lo = (uint32_t)row * (uint32_t)p.G + (uint32_t)grp_of[0];
+                    const uint32_t zoff_lo =
+                        (WBITS == 4) ? (uint32_t)row * (uint32_t)p.zp_row_bytes + (uint32_t)(grp_of[0] >> 1) : sidx_lo;
 #pragma unroll
                     for (int l = 0; l < 2; l++)
                     {
                         const int dg = grp_of[l] - grp_of[0];
                         if (p.scale_f32)
-                            sc[l][h] = __uint_as_float(pw.x);
+                            sc[l][h] = __uint_as_float(prm.sw[s][h]);
                         else
                             sc[l][h] = __half2float(
-                                __ushort_as_half((unsigned short)(pw.x >> (16 * (int)((sidx + dg) & 1)))));
+                                __ushort_as_half((unsigned short)(prm.sw[s][h] >> (16 * ((sidx_lo + dg) & 1)))));
                         if (WBITS == 4)
-                            zq[l][h] = (pw.y >> (8 * (int)(zoff & 3) + 4 * (grp_of[l] & 1))) & 0xF;
+                            zq[l][h] = (prm.zw[s][h] >> (8 * (zoff_lo & 3) + 4 * (grp_of[l] & 1))) & 0xF;
                         else
-                            zq[l][h] = (pw.y >> (8 * (int)((zoff + dg) & 3))) & 0xFF;
+                            zq[l][h] = (prm.zw[s][h] >> (8 * ((zoff_lo + dg) & 3))) & 0xFF;
                     }
                 }
             }
@@ -411,7 +428,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
 #pragma unroll
                 for (int h = 0; h < 2; h++)
                 {
-                    const int row = min((cta_in_split + step * p.ctas_per_split) * 16 + g + 8 * h, p.N - 1);
+                    const int row = row_of(step, h);
 #pragma unroll
                     for (int l = 0; l < 2; l++)
                     {
@@ -427,70 +444,105 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
                     }
                 }
             }
+            // this warp's tile: row r at r*128, 16-byte chunk c stored at chunk (c ^ (r & 7))
+            const uint8_t* wt = ring + (size_t)((slot * SETS + s) * nwarps + warp) * kTileBytes;
+            uint32_t wq[2][2][4]; // [unit][row half][word]
 #pragma unroll
             for (int l = 0; l < 2; l++)
-            {
-                float acc[MB][4];
-#pragma unroll
-                for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-                        acc[mb][c] = 0.f;
-                uint32_t zA[2], zB[2]; // fp16x2 constants holding (offset + zero-point)
 #pragma unroll
                 for (int h = 0; h < 2; h++)
                 {
-                    zA[h] = (0x6400u | zq[l][h]) * 0x00010001u; // 1024 + zp
-                    zB[h] = (WBITS == 4) ? (0x5400u | (zq[l][h] << 4)) * 0x00010001u : zA[h]; // 64 + zp
+                    const uint4 v = *reinterpret_cast<const uint4*>(wt + (g + 8 * h) * 128 + ((4 * l + t) ^ g) * 16);
+                    wq[l][h][0] = v.x, wq[l][h][1] = v.y, wq[l][h][2] = v.z, wq[l][h][3] = v.w;
                 }
-                const uint4 w_lo = wring[((slot * SETS + s) * 4 + 0 * 2 + l) * nthreads + tid];
-                const uint4 w_hi = wring[((slot * SETS + s) * 4 + 1 * 2 + l) * nthreads + tid];
-                const uint32_t wl[4] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w};
-                const uint32_t wh[4] = {w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+            uint32_t zA[2][2], zB[2][2]; // fp16x2 constants holding (offset + zero-point)
+            if (EXACT)
+            {
 #pragma unroll
-                for (int i = 0; i < 4; i++)
+                for (int l = 0; l < 2; l++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+                    {
+                        zA[l][h] = (0x6400u | zq[l][h]) * 0x00010001u;                                  // 1024 + zp
+                        zB[l][h] = (WBITS == 4) ? (0x5400u | (zq[l][h] << 4)) * 0x00010001u : zA[l][h]; // 64 + zp
+                    }
+            }
+            // four independent accumulation chains: (unit, word parity)
+            float acc[2][2][MB][4];
+#pragma unroll
+            for (int l = 0; l < 2; l++)
+#pragma unroll
+                for (int e = 0; e < 2; e++)
+#pragma unroll
+                    for (int mb = 0; mb < MB; mb++)
+#pragma unroll
+                        for (int c = 0; c < 4; c++)
+                            acc[l][e][mb][c] = 0.f;
+#pragma unroll
+            for (int w4 = 0; w4 < 4; w4++)
+#pragma unroll
+                for (int l = 0; l < 2; l++)
                 {
                     uint32_t a[2][4]; // [row half][pair]
 #pragma unroll
                     for (int h = 0; h < 2; h++)
                     {
-                        const uint32_t w = h ? wh[i] : wl[i];
+                        const uint32_t w = wq[l][h][w4];
                         if (WBITS == 4)
                         {
                             const uint32_t w8 = w >> 8;
-                            a[h][0] = hsub2_u32(and_or<0x000F000Fu, 0x64006400u>(w), zA[h]);  // n0, n4
-                            a[h][1] = hsub2_u32(and_or<0x00F000F0u, 0x54005400u>(w), zB[h]);  // n1, n5
-                            a[h][2] = hsub2_u32(and_or<0x000F000Fu, 0x64006400u>(w8), zA[h]); // n2, n6
-                            a[h][3] = hsub2_u32(and_or<0x00F000F0u, 0x54005400u>(w8), zB[h]); // n3, n7
+                            a[h][0] = and_or<0x000F000Fu, 0x64006400u>(w);  // 1024 + (n0, n4)
+                            a[h][1] = and_or<0x00F000F0u, 0x54005400u>(w);  //   64 + (n1, n5)
+                            a[h][2] = and_or<0x000F000Fu, 0x64006400u>(w8); // 1024 + (n2, n6)
+                            a[h][3] = and_or<0x00F000F0u, 0x54005400u>(w8); //   64 + (n3, n7)
+                            if (EXACT)
+                            {
+                                a[h][0] = hsub2_u32(a[h][0], zA[l][h]);
+                                a[h][1] = hsub2_u32(a[h][1], zB[l][h]);
+                                a[h][2] = hsub2_u32(a[h][2], zA[l][h]);
+                                a[h][3] = hsub2_u32(a[h][3], zB[l][h]);
+                            }
                         }
                         else
                         {
-                            a[h][0] = hsub2_u32(__byte_perm(w, 0x64646464u, 0x4140), zA[h]); // b0, b1
-                            a[h][1] = hsub2_u32(__byte_perm(w, 0x64646464u, 0x4342), zA[h]); // b2, b3
+                            a[h][0] = __byte_perm(w, 0x64646464u, 0x4140); // 1024 + (b0, b1)
+                            a[h][1] = __byte_perm(w, 0x64646464u, 0x4342); // 1024 + (b2, b3)
+                            if (EXACT)
+                            {
+                                a[h][0] = hsub2_u32(a[h][0], zA[l][h]);
+                                a[h][1] = hsub2_u32(a[h][1], zA[l][h]);
+                            }
                         }
                     }
                     constexpr int PAIRS = (WBITS == 4) ? 4 : 2; // half2 pairs per word
 #pragma unroll
                     for (int q = 0; q < PAIRS; q += 2)
                     {
-                        const int f = i * PAIRS + q;
+                        const int f = w4 * PAIRS + q;
 #pragma unroll
                         for (int mb = 0; mb < MB; mb++)
 #pragma unroll
-                            for (int xs = 0; xs < XS; xs++)
-                                mma16816(acc[mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1], xf[l][mb][xs][f],
-                                         xf[l][mb][xs][f + 1]);
+                            for (int xsn = 0; xsn < XS; xsn++)
+                                mma16816(acc[l][w4 & 1][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
+                                         xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
                     }
                 }
 #pragma unroll
-                for (int mb = 0; mb < MB; mb++)
+            for (int mb = 0; mb < MB; mb++)
+#pragma unroll
+                for (int c = 0; c < 4; c++)
                 {
-                    tot[s][mb][0] = fmaf(sc[l][0], acc[mb][0], tot[s][mb][0]);
-                    tot[s][mb][1] = fmaf(sc[l][0], acc[mb][1], tot[s][mb][1]);
-                    tot[s][mb][2] = fmaf(sc[l][1], acc[mb][2], tot[s][mb][2]);
-                    tot[s][mb][3] = fmaf(sc[l][1], acc[mb][3], tot[s][mb][3]);
+                    float v = 0.f;
+#pragma unroll
+                    for (int l = 0; l < 2; l++)
+                    {
+                        float u = acc[l][0][mb][c] + acc[l][1][mb][c];
+                        if (!EXACT)
+                            u -= fmaf((float)zq[l][c >> 1], c2[l][mb][c & 1], c1[l][mb][c & 1]);
+                        v = fmaf(sc[l][c >> 1], u, v);
+                    }
+                    tot[s][mb][c] = v;
                 }
-            }
         }
     };
 
@@ -594,89 +646,105 @@ __global__ void __launch_bounds__(kMaxWarps * 32, (MB == 1) ? 2 : 1) dq_gemv_ker
     };
 
     // ---------------------------------------------------------------- main loop: two row tiles per barrier
-    for (int step = 0; step < nsteps; step += 2)
+    int slot = 0;
+    uint32_t parity = 0;
+    bool timed_out = false;
+    for (int step = 0; step < nsteps; step += 6)
     {
-        const int pair_n = min(2, nsteps - step);
-        float* my = red + (((step >> 1) & 1) * nwarps + warp) * 2 * TILE_F;
-        for (int j = 0; j < pair_n; j++)
+        // unrolled by 6 = lcm(2 tiles per barrier, 3 parameter registers) so that every register index is static
+#pragma unroll
+        for (int pair = 0; pair < 3; pair++)
         {
-            issue(step + j + p.depth - 1);
-            cp_async_wait(p.depth - 1);
-            if (has_slice)
+            const int st = step + 2 * pair;
+            if (st < nsteps)
             {
-                compute(step + j);
+                const int pair_n = min(2, nsteps - st);
+                float* my = red + (((st >> 1) & 1) * nwarps + warp) * 2 * TILE_F;
 #pragma unroll
-                for (int s = 0; s < SETS; s++)
+                for (int j = 0; j < 2; j++)
+                {
+                    if (j < pair_n)
+                    {
+                        constexpr int kRegs = 3;
+                        const int ri = (2 * pair + j) % kRegs;
+                        load_params(pr[(ri + 2) % kRegs], st + j + 2); // two tiles ahead, in registers
+                        if (has_slice)
+                        {
+                            if (!mbar_wait(bar_s + 8 * slot, parity))
+                                timed_out = true;
+                            compute(st + j, slot, pr[ri]);
 #pragma unroll
-                    for (int mb = 0; mb < MB; mb++)
-                        reinterpret_cast<float4*>(my + j * TILE_F)[(s * MB + mb) * 32 + lane] =
-                            make_float4(tot[s][mb][0], tot[s][mb][1], tot[s][mb][2], tot[s][mb][3]);
-            }
-            else
-            {
+                            for (int s = 0; s < SETS; s++)
 #pragma unroll
-                for (int q = 0; q < SETS * MB; q++)
-                    reinterpret_cast<float4*>(my + j * TILE_F)[q * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                for (int mb = 0; mb < MB; mb++)
+                                    reinterpret_cast<float4*>(my + j * TILE_F)[(s * MB + mb) * 32 + lane] =
+                                        make_float4(tot[s][mb][0], tot[s][mb][1], tot[s][mb][2], tot[s][mb][3]);
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int q = 0; q < SETS * MB; q++)
+                                reinterpret_cast<float4*>(my + j * TILE_F)[q * 32 + lane] =
+                                    make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                        if (++slot == p.depth)
+                            slot = 0, parity ^= 1;
+                    }
+                }
+                __syncthreads(); // every warp has read its tiles of this pair: the slots may be refilled
+                if (tid == 0)
+                    for (int j = 0; j < pair_n; j++)
+                        produce(st + j + p.depth); // lands in the slot of tile st + j
+                const float* rb = red + ((st >> 1) & 1) * nwarps * 2 * TILE_F;
+                for (int o = tid; o < pair_n * TILE_F; o += nthreads)
+                {
+                    const int j = o / TILE_F, oo = o - j * TILE_F;
+                    float v = 0.f;
+                    for (int w = 0; w < nwarps; w++)
+                        v += rb[w * 2 * TILE_F + j * TILE_F + oo];
+                    res[((st + j) % kBatch) * TILE_F + oo] = v;
+                }
+                const int last = st + pair_n - 1;
+                if ((last % kBatch) == kBatch - 1 || last == nsteps - 1)
+                    flush(last - (last % kBatch), (last % kBatch) + 1);
             }
         }
-        __syncthreads();
-        const float* rb = red + ((step >> 1) & 1) * nwarps * 2 * TILE_F;
-        for (int o = tid; o < pair_n * TILE_F; o += nthreads)
-        {
-            const int j = o / TILE_F, oo = o - j * TILE_F;
-            float v = 0.f;
-            for (int w = 0; w < nwarps; w++)
-                v += rb[w * 2 * TILE_F + j * TILE_F + oo];
-            res[((step + j) % kBatch) * TILE_F + oo] = v;
-        }
-        const int last = step + pair_n - 1;
-        if ((last % kBatch) == kBatch - 1 || last == nsteps - 1)
-            flush(last - (last % kBatch), (last % kBatch) + 1);
     }
-    cp_async_wait(0);
+    if (timed_out)
+        atomicExch(p.status, 1);
 }
 
 // Raise the kernel's dynamic shared-memory limit (monotonically: the attribute is a plain setter).
-template <int WBITS, int MB, bool XSPLIT, bool DUAL>
+template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT>
 cudaError_t ensure_smem(size_t smem)
 {
     static size_t configured = 48 * 1024;
     if (smem <= configured)
         return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL>,
+    cudaError_t e = cudaFuncSetAttribute(dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
         configured = smem;
     return e;
 }
 
-template <int WBITS, int MB, bool XSPLIT, bool DUAL>
-cudaError_t launch(const GemvParams& p, int warps, int grid, cudaStream_t stream)
+template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT>
+cudaError_t launch(const GemvParams& p, const CUtensorMap& t0, const CUtensorMap& t1, int warps, int grid,
+                   size_t smem, cudaStream_t stream)
 {
-    const size_t smem = Smem<MB, DUAL>::total_bytes(warps, p.depth);
-    cudaError_t e = ensure_smem<WBITS, MB, XSPLIT, DUAL>(smem);
+    cudaError_t e = ensure_smem<WBITS, MB, XSPLIT, DUAL, EXACT>(smem);
     if (e != cudaSuccess)
         return e;
     (void)cudaGetLastError(); // do not inherit a stale error left behind by an unrelated earlier call
-    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL><<<grid, warps * 32, smem, stream>>>(p);
+    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT><<<grid, warps * 32, smem, stream>>>(p, t0, t1);
     return cudaGetLastError();
 }
 
-template <int WBITS, int MB, bool XSPLIT, bool DUAL>
-int occupancy(int warps, int depth)
+size_t smem_for(int mb, bool dual, int warps, int depth)
 {
-    static int cache[kMaxWarps + 1][kMaxDepth + 1]; // 0 = not queried yet
-    if (cache[warps][depth] > 0)
-        return cache[warps][depth];
-    const size_t smem = Smem<MB, DUAL>::total_bytes(warps, depth);
-    if (ensure_smem<WBITS, MB, XSPLIT, DUAL>(smem) != cudaSuccess)
-        return 0;
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL>, warps * 32,
-                                                      smem) != cudaSuccess)
-        return 0;
-    cache[warps][depth] = n;
-    return n;
+    if (mb == 1)
+        return dual ? Smem<1, true>::total_bytes(warps, depth) : Smem<1, false>::total_bytes(warps, depth);
+    return dual ? Smem<2, true>::total_bytes(warps, depth) : Smem<2, false>::total_bytes(warps, depth);
 }
 
 #define NNF_GEMV_FOR_EACH_VARIANT(X)                                                                              \
@@ -695,34 +763,17 @@ int occupancy(int warps, int depth)
     X(8, 2, true, false)                                                                                          \
     X(8, 2, true, true)
 
-cudaError_t dispatch(int wbits, const nnf::GemvPlan& plan, const GemvParams& p, int grid, cudaStream_t stream)
+cudaError_t dispatch(int wbits, const nnf::GemvPlan& plan, const GemvParams& p, const CUtensorMap& t0,
+                     const CUtensorMap& t1, int grid, cudaStream_t stream)
 {
 #define NNF_X(WB, MBV, XSP, DU)                                                                                   \
     if (wbits == WB && plan.mb == MBV && plan.xsplit == XSP && plan.dual == DU)                                   \
-        return launch<WB, MBV, XSP, DU>(p, plan.warps, grid, stream);
+        return plan.exact                                                                                         \
+                   ? launch<WB, MBV, XSP, DU, true>(p, t0, t1, plan.warps, grid, plan.smem_bytes, stream)         \
+                   : launch<WB, MBV, XSP, DU, false>(p, t0, t1, plan.warps, grid, plan.smem_bytes, stream);
     NNF_GEMV_FOR_EACH_VARIANT(NNF_X)
 #undef NNF_X
     return cudaErrorInvalidValue;
-}
-
-// Resident CTAs per SM of the variant a plan selects (0 when it cannot be queried, e.g. without a device).
-int query_occupancy(int wbits, const nnf::GemvPlan& plan)
-{
-#define NNF_X(WB, MBV, XSP, DU)                                                                                   \
-    if (wbits == WB && plan.mb == MBV && plan.xsplit == XSP && plan.dual == DU)                                   \
-        return occupancy<WB, MBV, XSP, DU>(plan.warps, plan.depth);
-    NNF_GEMV_FOR_EACH_VARIANT(NNF_X)
-#undef NNF_X
-    return 0;
-}
-
-size_t smem_for(const nnf::GemvPlan& plan)
-{
-    if (plan.mb == 1)
-        return plan.dual ? Smem<1, true>::total_bytes(plan.warps, plan.depth)
-                         : Smem<1, false>::total_bytes(plan.warps, plan.depth);
-    return plan.dual ? Smem<2, true>::total_bytes(plan.warps, plan.depth)
-                     : Smem<2, false>::total_bytes(plan.warps, plan.depth);
 }
 } // namespace
 
@@ -750,41 +801,58 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
     GemvPlan pl;
     pl.mb = d.M > 8 ? 2 : 1;
     pl.dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
+    pl.exact = (d.flags & NNF_B200_FLAG_EXACT_ZP) != 0;
     // fp32 activations are carried as fp16 hi + lo where the register budget allows it
     pl.xsplit = d.x_dtype == NNF_B200_F32 && !(d.w_bits == 4 && pl.mb == 2);
     pl.row_tiles = (d.N + 15) / 16;
     const int units = d.K / ue;
     pl.slices = (units + 1) / 2;
-    // Split K so that every CTA has at most kMaxWarps slices, spread evenly (sizes differ by at most one).
-    pl.splits = (pl.slices + kMaxWarps - 1) / kMaxWarps;
-    if (d.split_k > 0)
-    {
-        if ((pl.slices + d.split_k - 1) / d.split_k > kMaxWarps)
-        {
-            *why = "split_k too small: more than " + std::to_string(kMaxWarps) + " slices of 128 bytes per split";
-            return NNF_B200_EINVAL;
-        }
-        pl.splits = std::min(d.split_k, pl.slices);
-    }
-    pl.warps = (pl.slices + pl.splits - 1) / pl.splits;
-    // Ring depth: as deep as lets two CTAs share an SM's shared memory (one for the 16-row-batch variants).
+    const int sms = ctx ? ctx->sm_count : 148;
     const int smem_cap = ctx ? ctx->smem_optin : 227 * 1024;
-    const int want_ctas = pl.mb == 1 ? 2 : 1;
-    pl.depth = 2;
-    for (int depth = kMaxDepth; depth >= 2; depth--)
+    const int sets = pl.dual ? 2 : 1;
+    // Warps per CTA: one per slice of the CTA's K range; split K when a row has more slices than that.  The
+    // widest CTA whose reduction buffers and a ring of at least two tiles fit in shared memory is taken.
+    int resident = 1;
+    bool fits = false;
+    for (int max_warps : {16, 12, 8, 6, 4, 2, 1})
     {
-        pl.depth = depth;
-        if ((int)smem_for(pl) + 1024 <= smem_cap / want_ctas)
+        pl.splits = (pl.slices + max_warps - 1) / max_warps;
+        if (d.split_k > 0)
+        {
+            if ((pl.slices + d.split_k - 1) / d.split_k > kMaxWarps)
+            {
+                *why = "split_k too small: more than " + std::to_string(kMaxWarps) + " slices of 128 bytes per split";
+                return NNF_B200_EINVAL;
+            }
+            pl.splits = std::min(d.split_k, pl.slices);
+        }
+        pl.warps = (pl.slices + pl.splits - 1) / pl.splits;
+        // CTAs per SM by registers (the kernel is compiled for at most 128 per thread: 512 threads per SM), then
+        // the deepest ring that lets that many CTAs share the SM's shared memory.
+        resident = std::max(1, 512 / (pl.warps * 32));
+        for (int depth = kMaxDepth; depth >= 2 && !fits; depth--)
+        {
+            pl.depth = depth;
+            fits = (int)smem_for(pl.mb, pl.dual, pl.warps, depth) + 1024 <= smem_cap / resident;
+        }
+        if (!fits && resident > 1)
+        {
+            resident = 1;
+            pl.depth = 2;
+            fits = (int)smem_for(pl.mb, pl.dual, pl.warps, 2) + 1024 <= smem_cap;
+        }
+        if (fits || d.split_k > 0)
             break;
     }
-    const int sms = ctx ? ctx->sm_count : 148;
-    int resident = ctx ? query_occupancy(d.w_bits, pl) : 0;
-    if (resident <= 0)
-        resident = 1;
+    pl.smem_bytes = smem_for(pl.mb, pl.dual, pl.warps, pl.depth);
+    if (!fits || (int)pl.smem_bytes > smem_cap)
+    {
+        *why = "shared memory: the launch shape does not fit";
+        return NNF_B200_ENOTSUP;
+    }
     int per_split = std::max(1, (sms * resident) / pl.splits);
     per_split = std::min(per_split, pl.row_tiles);
     pl.ctas_per_split = per_split;
-    const int sets = pl.dual ? 2 : 1;
     pl.slot_floats = (size_t)sets * pl.mb * 128 + 8 * pl.mb;
     pl.workspace_bytes = 0;
     if (pl.splits > 1)
@@ -802,31 +870,33 @@ int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
 {
     GemvParams p{};
     const int ue = (d.w_bits == 4) ? 128 : 64;
-    p.wq[0] = static_cast<const uint8_t*>(w->wq);
+    const int row_bytes = (d.w_bits == 4) ? d.K / 2 : d.K;
     p.scale[0] = w->scale;
     p.zp[0] = static_cast<const uint8_t*>(w->zp);
     if (plan.dual)
     {
-        p.wq[1] = static_cast<const uint8_t*>(w2->wq);
         p.scale[1] = w2->scale;
         p.zp[1] = static_cast<const uint8_t*>(w2->zp);
     }
+    // Weight tensor maps: bytes [N][row_bytes], boxes of 16 rows x 128 bytes, 128-byte swizzle.
+    const CUtensorMap* t0 = weight_tensor_map(ctx, w->wq, d.N, row_bytes, 128, 16);
+    const CUtensorMap* t1 = plan.dual ? weight_tensor_map(ctx, w2->wq, d.N, row_bytes, 128, 16) : t0;
+    if (!t0 || !t1)
+        return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
     p.x = x;
     p.gain = static_cast<const float*>(gain);
     p.bias = static_cast<const float*>(bias);
     p.y = y;
+    p.status = ctx->dev_status;
     p.M = d.M, p.N = d.N, p.K = d.K;
     p.group = d.group_size > 0 ? d.group_size : d.K;
     p.G = d.K / p.group;
     p.zp_row_bytes = (d.w_bits == 4) ? (p.G + 1) / 2 : p.G;
-    p.row_bytes = (d.w_bits == 4) ? d.K / 2 : d.K;
     p.units = d.K / ue;
     p.slices = plan.slices;
     p.row_tiles = plan.row_tiles;
     p.splits = plan.splits;
     p.ctas_per_split = plan.ctas_per_split;
-    p.slices_base = plan.slices / plan.splits;
-    p.slices_rem = plan.slices % plan.splits;
     p.x_f32 = d.x_dtype == NNF_B200_F32;
     p.y_f32 = d.y_dtype == NNF_B200_F32;
     p.scale_f32 = d.scale_dtype == NNF_B200_F32;
@@ -850,12 +920,11 @@ int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
         p.ws_slots = reinterpret_cast<float*>(static_cast<char*>(workspace) + cnt);
     }
     const int grid = plan.splits * plan.ctas_per_split;
-    cudaError_t e = dispatch(d.w_bits, plan, p, grid, stream);
+    cudaError_t e = dispatch(d.w_bits, plan, p, *t0, *t1, grid, stream);
     if (e != cudaSuccess)
         return set_error(ctx, NNF_B200_ECUDA,
                          std::string("dq_gemv launch: ") + cudaGetErrorString(e) + " (grid " + std::to_string(grid) +
-                             ", warps " + std::to_string(plan.warps) + ", depth " + std::to_string(plan.depth) +
-                             ", smem " + std::to_string(smem_for(plan)) + ")");
+                             ", warps " + std::to_string(plan.warps) + ", smem " + std::to_string(plan.smem_bytes) + ")");
     ctx->launches++;
     return NNF_B200_OK;
 }

@@ -4,6 +4,7 @@
 #include <new>
 
 #include "nnf_internal.h"
+#include "sm100_ptx.cuh"
 
 namespace nnf
 {
@@ -12,6 +13,55 @@ int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg)
     if (ctx)
         ctx->last_error = msg;
     return status;
+}
+
+void* load_encode_tiled()
+{
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    return fn;
+}
+
+bool encode_tensor_map_2d(void* encode_fn, CUtensorMap* map, CUtensorMapDataType dtype, size_t elem_bytes,
+                          const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                          uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle)
+{
+    using Fn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                            const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                            CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    if (!encode_fn)
+        return false;
+    (void)elem_bytes;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = reinterpret_cast<Fn>(encode_fn)(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                                 CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+const CUtensorMap* weight_tensor_map(nnf_b200_ctx* ctx, const void* base, int rows, int row_bytes, int box_bytes,
+                                     int box_rows)
+{
+    const int swz = box_bytes == 128 ? 1 : 0;
+    auto key = std::make_tuple(base, rows, row_bytes, box_bytes, box_rows, swz);
+    auto it = ctx->tensor_maps.find(key);
+    if (it != ctx->tensor_maps.end())
+        return &it->second;
+    alignas(64) CUtensorMap map;
+    if (!encode_tensor_map_2d(ctx->encode_tiled, &map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, (uint64_t)row_bytes,
+                              (uint64_t)rows, (uint64_t)row_bytes, (uint32_t)box_bytes, (uint32_t)box_rows,
+                              swz ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE))
+        return nullptr;
+    if (ctx->tensor_maps.size() > 4096) // callers that churn through weight buffers: start over
+        ctx->tensor_maps.clear();
+    return &(ctx->tensor_maps[key] = map);
 }
 } // namespace nnf
 
@@ -43,8 +93,8 @@ int validate(nnf_b200_ctx* ctx, const nnf_b200_linear_desc* d)
         return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown epilogue");
     if (d->kernel < NNF_B200_KERNEL_AUTO || d->kernel > NNF_B200_KERNEL_GEMM)
         return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown kernel selector");
-    if (d->reserved[0] || d->reserved[1] || d->reserved[2] || d->split_k < 0)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "reserved fields must be zero and split_k >= 0");
+    if (d->reserved[0] || d->reserved[1] || d->split_k < 0 || (d->flags & ~NNF_B200_FLAG_EXACT_ZP))
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "reserved fields must be zero, split_k >= 0, flags known");
     return NNF_B200_OK;
 }
 
@@ -89,6 +139,13 @@ int nnf_b200_init(int device, nnf_b200_ctx** out)
         delete ctx;
         return NNF_B200_ENOTSUP;
     }
+    ctx->encode_tiled = nnf::load_encode_tiled();
+    if (!ctx->encode_tiled || cudaMalloc(&ctx->dev_status, 256) != cudaSuccess ||
+        cudaMemset(ctx->dev_status, 0, 256) != cudaSuccess)
+    {
+        delete ctx;
+        return NNF_B200_ECUDA;
+    }
     int rc = nnf::gemv_configure(ctx);
     if (rc == NNF_B200_OK)
         rc = nnf::gemm_configure(ctx);
@@ -103,6 +160,8 @@ int nnf_b200_init(int device, nnf_b200_ctx** out)
 
 int nnf_b200_free(nnf_b200_ctx* ctx)
 {
+    if (ctx && ctx->dev_status)
+        cudaFree(ctx->dev_status);
     delete ctx;
     return NNF_B200_OK;
 }
@@ -145,6 +204,26 @@ size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_l
         return plan.workspace_bytes;
     }
     return nnf::gemm_workspace_bytes(ctx, *desc);
+}
+
+int nnf_b200_linear_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc, int32_t out[8])
+{
+    if (!desc || !out)
+        return NNF_B200_EINVAL;
+    for (int i = 0; i < 8; i++)
+        out[i] = 0;
+    out[0] = pick_kernel(*desc);
+    if (out[0] == NNF_B200_KERNEL_GEMV)
+    {
+        nnf::GemvPlan plan;
+        std::string why;
+        int rc = nnf::gemv_plan(ctx, *desc, &plan, &why);
+        if (rc != NNF_B200_OK)
+            return rc;
+        out[1] = plan.warps, out[2] = plan.splits, out[3] = plan.depth, out[4] = plan.splits * plan.ctas_per_split;
+        out[5] = (int32_t)plan.smem_bytes;
+    }
+    return NNF_B200_OK;
 }
 
 int nnf_b200_workspace_reset(nnf_b200_ctx* ctx, void* stream, void* workspace, size_t bytes)
@@ -207,6 +286,20 @@ int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc*
     if (rc != NNF_B200_OK)
         return nnf::set_error(ctx, rc, why);
     return nnf::gemm_launch(ctx, s, d, x, w, w2, gain, bias, y, workspace, workspace_bytes);
+}
+
+int nnf_b200_device_status(nnf_b200_ctx* ctx, void* stream)
+{
+    if (!ctx)
+        return NNF_B200_EINVAL;
+    int host = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&host, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess)
+        return nnf::set_error(ctx, NNF_B200_ECUDA, "reading the device status word failed");
+    if (host != 0)
+        return nnf::set_error(ctx, NNF_B200_ETIMEDOUT, "a bounded device-side wait gave up");
+    return NNF_B200_OK;
 }
 
 uint64_t nnf_b200_launch_count(nnf_b200_ctx* ctx, int reset)

@@ -1,9 +1,12 @@
 // Internal declarations shared by the C-ABI translation unit and the kernel launchers.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <map>
 #include <string>
+#include <tuple>
 
 #include "nnf_b200.h"
 
@@ -16,6 +19,9 @@ struct nnf_b200_ctx
     uint64_t launches = 0;
     std::string last_error;
     void* encode_tiled = nullptr; // cuTensorMapEncodeTiled entry point (driver)
+    int* dev_status = nullptr;    // device word set to non-zero when a bounded device-side wait gave up
+    // Tensor maps of weight tensors, keyed by (address, rows, row bytes, box bytes, box rows, swizzle).
+    std::map<std::tuple<const void*, int, int, int, int, int>, CUtensorMap> tensor_maps;
 };
 
 namespace nnf
@@ -32,11 +38,20 @@ struct GemvPlan
     int slices = 0;      // 128-byte weight-row slices along K
     bool dual = false;
     bool xsplit = false; // activations carried as fp16 hi + lo
+    bool exact = false;  // remove zero-points before the multiply instead of correcting the fp32 sum
     size_t slot_floats = 0;     // floats per (split, row tile) partial slot
     size_t workspace_bytes = 0; // 0 when splits == 1
+    size_t smem_bytes = 0;      // dynamic shared memory of the launch
+    int units_cap = 0;          // 64-byte units per split (upper bound): sizes the staged activations
+    int ng_cap = 0;             // quantisation groups per warp (upper bound)
 };
 
 int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
+
+// Cached 2-D byte tensor map [rows][row_bytes] with a box of box_rows x box_bytes (128-byte swizzle when
+// box_bytes == 128, none otherwise); nullptr if the driver refuses it.
+const CUtensorMap* weight_tensor_map(nnf_b200_ctx* ctx, const void* base, int rows, int row_bytes, int box_bytes,
+                                     int box_rows);
 
 int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan, std::string* why);
 int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan,

@@ -46,6 +46,11 @@ class Context:
     def sm_count(self) -> int:
         return int(self.lib.nnf_b200_sm_count(self.handle))
 
+    def device_status(self) -> None:
+        """Raise if a bounded device-side wait gave up since the last query (synchronises)."""
+        import torch
+        self.check(self.lib.nnf_b200_device_status(self.handle, torch.cuda.current_stream().cuda_stream))
+
     def launch_count(self, reset: bool = False) -> int:
         return int(self.lib.nnf_b200_launch_count(self.handle, int(reset)))
 
@@ -111,9 +116,9 @@ class DequantDot:
     def __init__(self, weight: DeviceWeight, weight2: Optional[DeviceWeight] = None,
                  gain: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
                  eps: float = 1e-6, y_dtype: Optional[torch.dtype] = None, kernel: int = L.KERNEL_AUTO,
-                 split_k: int = 0, ctx: Optional[Context] = None):
+                 split_k: int = 0, flags: int = 0, ctx: Optional[Context] = None):
         self.w, self.w2, self.gain, self.bias = weight, weight2, gain, bias
-        self.eps, self.y_dtype, self.kernel, self.split_k = eps, y_dtype, kernel, split_k
+        self.eps, self.y_dtype, self.kernel, self.split_k, self.flags = eps, y_dtype, kernel, split_k, flags
         self.ctx = ctx or default_context(weight.wq.device.index or 0)
         if weight2 is not None and (weight2.N, weight2.K, weight2.bits, weight2.group) != \
                 (weight.N, weight.K, weight.bits, weight.group):
@@ -140,6 +145,7 @@ class DequantDot:
         d.rms_eps = self.eps
         d.kernel = self.kernel
         d.split_k = self.split_k
+        d.flags = self.flags
         return d
 
     def workspace(self, d: L.LinearDesc) -> Optional[torch.Tensor]:

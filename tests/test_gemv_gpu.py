@@ -26,6 +26,20 @@ def test_u4_g128_fp16_small(M, N, K):
     _check(gpu_linear(x, w), oracle_linear(x, w), TOL_F16, tight=1.5e-3)
 
 
+@pytest.mark.parametrize("exact", [0, 1])
+@pytest.mark.parametrize("M,N,K,bits", [(1, 64, 1024, 4), (7, 96, 2304, 4), (16, 48, 512, 4), (3, 80, 640, 8), (16, 32, 1024, 8)])
+def test_exact_zero_point_flag(exact, M, N, K, bits):
+    """Both zero-point treatments (removed before the multiply / taken out of the fp32 sum) meet the tolerance,
+    and agree with each other to fp32 rounding."""
+    from nnfusion_b200 import _lib as L
+    rng = np.random.Generator(np.random.PCG64(77))
+    x = synth.make_x(rng, M, K, np.float16)
+    w = synth.make_weights(rng, N, K, bits, 128)
+    r = oracle_linear(x, w, out_dtype=np.float32)
+    y = gpu_linear(x, w, out_dtype=np.float32, flags=L.FLAG_EXACT_ZP if exact else 0)
+    _check(y, r, TOL_F16, tight=3e-5 if exact else 1e-4)
+
+
 @pytest.mark.parametrize("N,K", [(11008, 4096), (4096, 11008)])
 def test_config2_decode_gemv_full_size(N, K):
     x, w = synth.u4g128(0, 1, N, K)
@@ -70,7 +84,7 @@ def test_u4_fp32_activations_fp32_scale(M):
     rng = np.random.Generator(np.random.PCG64(9))
     x = synth.make_x(rng, M, 768, np.float32)
     w = synth.make_weights(rng, 64, 768, 4, 128, np.float32, (0.002, 0.02))
-    _check(gpu_linear(x, w), oracle_linear(x, w), TOL_F32, tight=None if M > 8 else 2e-5)
+    _check(gpu_linear(x, w), oracle_linear(x, w), TOL_F32, tight=None if M > 8 else 1e-4)
 
 
 @pytest.mark.parametrize("M", [1, 8, 13])
@@ -101,19 +115,24 @@ def test_bias_epilogue(M):
     _check(gpu_linear(x, w, bias=bias), oracle_linear(x, w, bias=bias), TOL_F16, tight=1.5e-3)
 
 
-@pytest.mark.parametrize("split_k", [5, 6, 7, 11, 43])
+@pytest.mark.parametrize("split_k", [3, 4, 7, 43])
 def test_split_k_agrees_and_workspace_is_reusable(split_k):
     x, w = synth.u4g128(13, 2, 200, 11008)
     r = oracle_linear(x, w)
-    if split_k == 5:   # 43 slices over 5 splits would need 9 warps per CTA; the kernel has 8
-        with pytest.raises(RuntimeError, match="split_k too small"):
-            gpu_linear(x, w, split_k=split_k)
-        return
     ys = gpu_linear(x, w, split_k=split_k, repeat=3)   # same workspace, three calls in a row
     for y in ys:
         _check(y, r, TOL_F16, tight=1.5e-3)
     np.testing.assert_array_equal(ys[0], ys[1])         # fixed summation order: bitwise repeatable
     np.testing.assert_array_equal(ys[0], ys[2])
+
+
+def test_split_k_too_small_is_rejected():
+    """One CTA has at most 16 warps, one per 128-byte slice of a row: K = 8192 (32 slices) needs two splits."""
+    x, w = synth.u4g128(13, 1, 16, 8192)
+    with pytest.raises(RuntimeError, match="split_k too small"):
+        gpu_linear(x, w, split_k=1)
+    assert len(gpu_linear(x, w, split_k=2, repeat=2)) == 2
+    _check(gpu_linear(x, w), oracle_linear(x, w), TOL_F16, tight=1.5e-3)
 
 
 def test_empty_and_invalid_arguments():
@@ -145,7 +164,7 @@ def test_empty_and_invalid_arguments():
     assert e.value.status == L.EALIGN
     # split-K without a workspace
     xb, wb = synth.u4g128(15, 1, 32, 11008)
-    opb = DequantDot(DeviceWeight.from_host(wb))
+    opb = DequantDot(DeviceWeight.from_host(wb), split_k=4)
     txb = torch.from_numpy(xb).cuda()
     d = opb.desc(1, txb.dtype)
     y = torch.empty((1, 32), dtype=torch.float16, device="cuda")

@@ -17,7 +17,7 @@ def oracle_linear(x, w, w2=None, gain=None, bias=None, eps=1e-6, out_dtype=None)
 
 
 def gpu_linear(x, w, w2=None, gain=None, bias=None, eps=1e-6, out_dtype=None, kernel=0, split_k=0,
-               repeat=1, return_op=False):
+               repeat=1, return_op=False, flags=0):
     import torch
     from nnfusion_b200.linear import DequantDot, DeviceWeight
 
@@ -29,13 +29,14 @@ def gpu_linear(x, w, w2=None, gain=None, bias=None, eps=1e-6, out_dtype=None, ke
     ydt = None
     if out_dtype is not None:
         ydt = torch.float16 if np.dtype(out_dtype) == np.float16 else torch.float32
-    op = DequantDot(dw, dw2, gain=tg, bias=tb, eps=eps, y_dtype=ydt, kernel=kernel, split_k=split_k)
+    op = DequantDot(dw, dw2, gain=tg, bias=tb, eps=eps, y_dtype=ydt, kernel=kernel, split_k=split_k, flags=flags)
     tx = torch.from_numpy(np.ascontiguousarray(x)).to(dev)
     outs = []
     for _ in range(repeat):
         y = op(tx)
         torch.cuda.synchronize()
         outs.append(y.cpu().numpy())
+    op.ctx.device_status()   # no bounded wait inside the kernels may have given up
     if return_op:
         return outs, op
     return outs[0] if repeat == 1 else outs
