@@ -1,17 +1,501 @@
-// placeholder until the tcgen05 kernel lands
+// Large-M (prefill) dequantize-fused linear for sm_100a on the 5th-generation tensor cores.
+//
+//   y[M,N] = epi( x[M,K] . dequant(W)[N,K]^T )        x fp16, W uint4 / uint8 with group scales and zero-points
+//
+// Fused replacement of the reference's Convert -> Subtract -> Multiply element-wise kernels that materialise the
+// dequantised weights (src/nnfusion/core/kernels/cuda_gpu/kernels/elementwise.hpp:33-157,
+// elementwise_fused.cpp:42-189) followed by cublasHgemm / cublasSgemm behind cuda::Dot
+// (src/nnfusion/core/kernels/cuda_gpu/kernels/dot.cpp:103-125,264-363).
+//
+// The CTA computes a transposed output tile  D[128 weight rows, BX batch rows] = Wdq[128, K] . X[BX, K]^T  so
+// that the dequantised weights are the MMA's A operand and can be handed to the tensor core through TENSOR MEMORY
+// instead of shared memory:
+//   * warp "TMA"  : one thread streams x tiles (BX rows x 64 fp16, 128-byte swizzle, the MMA's B operand) and raw
+//                   packed-weight chunks (128 rows x 128 bytes, 128-byte swizzle) into shared-memory rings;
+//   * warps "DQ"  : thread r owns weight row r of the tile = TMEM lane r.  Per 64-element k-block it reads its 32
+//                   (uint4) or 64 (uint8) bytes from the raw ring, turns them into fp16 (q - zp) * scale with the
+//                   exponent trick (PRMT + LOP3 + HSUB2 + HMUL2 per pair, exact integer before the scale), and
+//                   writes the 32 packed registers into the A stage in TMEM with tcgen05.st.  Two groups of four
+//                   warps alternate k-blocks so that the conversion keeps ahead of the tensor core;
+//   * warp "MMA"  : one thread issues tcgen05.mma.kind::f16 (A from TMEM, B from the shared-memory descriptor,
+//                   fp32 accumulator D in TMEM, 128 x BX x 16 per instruction) and releases stages with
+//                   tcgen05.commit;
+//   * epilogue    : the DQ warps read D with tcgen05.ld, apply bias or SiLU(gate) * up, convert and store y.
+// With the SiLU * mul epilogue the CTA carries two weight sets (gate, up), two accumulators of 128 columns each
+// and BX = 128.  Every mbarrier wait is bounded; on a time-out the CTA raises a status flag, skips its remaining
+// work, and still frees its tensor memory.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
 #include "nnf_internal.h"
+#include "sm100_ptx.cuh"
+
+namespace
+{
+using namespace nnf::ptx;
+
+template <int WBITS, bool DUAL>
+struct Cfg
+{
+    static constexpr int SETS = DUAL ? 2 : 1;
+    static constexpr int BN = 128;              // weight rows per CTA  (UMMA M, TMEM lanes)
+    static constexpr int BX = DUAL ? 128 : 256; // batch rows per CTA   (UMMA N, accumulator columns per set)
+    static constexpr int BK = 64;               // k-block: one 128-byte swizzle row of fp16
+    static constexpr int XSTAGES = DUAL ? 6 : 4;
+    static constexpr int WSTAGES = 3;
+    static constexpr int ASTAGES = 4;
+    static constexpr int KB_PER_CHUNK = (WBITS == 4) ? 4 : 2; // k-blocks per 128-byte raw chunk
+    static constexpr int RAW_BYTES = (WBITS == 4) ? 32 : 64;  // raw bytes per row and k-block
+    static constexpr int DQ_GROUPS = 2;                       // groups of 4 warps alternating k-blocks
+    static constexpr int DQ_WARPS = 4 * DQ_GROUPS * SETS;
+    static constexpr int THREADS = (DQ_WARPS + 2) * 32;
+    static constexpr int X_STAGE_BYTES = BX * 128;
+    static constexpr int W_STAGE_BYTES = BN * 128;
+    static constexpr int A_COL0 = SETS * BX;     // first TMEM column of the A stages
+    static constexpr int A_STAGE_COLS = BK / 2;  // 64 fp16 per lane = 32 columns
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int NUM_BARRIERS = 2 * XSTAGES + 2 * SETS * WSTAGES + 2 * SETS * ASTAGES + 1;
+    static constexpr size_t SMEM_BYTES =
+        1024 + (size_t)XSTAGES * X_STAGE_BYTES + (size_t)SETS * WSTAGES * W_STAGE_BYTES + NUM_BARRIERS * 8 + 64;
+    static_assert(A_COL0 + SETS * ASTAGES * A_STAGE_COLS <= TMEM_COLS, "tensor memory budget");
+    static_assert(KB_PER_CHUNK % DQ_GROUPS == 0, "every group must touch every raw chunk");
+};
+
+struct GemmParams
+{
+    const void* scale[2];
+    const uint8_t* zp[2];
+    const float* bias;
+    void* y;
+    int* status;
+    int M, N, K;
+    int group, G, zp_row_bytes;
+    int y_f32, scale_f32, has_bias;
+    int m_tiles;
+};
+
+constexpr uint32_t kGemmSpin = 1u << 22;
+
+// Bounded wait that also gives up as soon as another role of the CTA has raised the abort flag.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    for (uint32_t i = 0; i < kGemmSpin; i++)
+    {
+        if (mbar_try_wait(bar, parity))
+            return true;
+        if ((i & 255u) == 255u && *abort_flag)
+            return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// UMMA shared-memory descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr)
+{
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
+}
+
+template <int WBITS, bool DUAL>
+__global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
+    dq_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x,
+                   const __grid_constant__ CUtensorMap tmap_w0, const __grid_constant__ CUtensorMap tmap_w1)
+{
+    using C = Cfg<WBITS, DUAL>;
+    constexpr int SETS = C::SETS;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* xs = base;                                             // [XSTAGES][BX][128 B]
+    uint8_t* wsm = xs + (size_t)C::XSTAGES * C::X_STAGE_BYTES;      // [SETS][WSTAGES][128][128 B]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(wsm + (size_t)SETS * C::WSTAGES * C::W_STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARRIERS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint32_t bar0 = smem_u32(bars);
+    auto full_x = [&](int s) { return bar0 + 8u * s; };
+    auto empty_x = [&](int s) { return bar0 + 8u * (C::XSTAGES + s); };
+    auto full_w = [&](int set, int s) { return bar0 + 8u * (2 * C::XSTAGES + set * C::WSTAGES + s); };
+    auto empty_w = [&](int set, int s) { return bar0 + 8u * (2 * C::XSTAGES + SETS * C::WSTAGES + set * C::WSTAGES + s); };
+    auto full_a = [&](int set, int s) { return bar0 + 8u * (2 * C::XSTAGES + 2 * SETS * C::WSTAGES + set * C::ASTAGES + s); };
+    auto empty_a = [&](int set, int s) {
+        return bar0 + 8u * (2 * C::XSTAGES + 2 * SETS * C::WSTAGES + SETS * C::ASTAGES + set * C::ASTAGES + s);
+    };
+    const uint32_t acc_full = bar0 + 8u * (C::NUM_BARRIERS - 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m_tile = blockIdx.x % p.m_tiles, n_tile = blockIdx.x / p.m_tiles;
+    const int m0 = m_tile * C::BX, n0 = n_tile * C::BN;
+    const int KB = p.K / C::BK;
+    constexpr int TMA_WARP = C::DQ_WARPS, MMA_WARP = C::DQ_WARPS + 1;
+
+    // ---------------------------------------------------------------- set-up
+    if (tid == 0)
+    {
+        for (int s = 0; s < C::XSTAGES; s++)
+        {
+            mbar_init(full_x(s), 1);
+            mbar_init(empty_x(s), 1);
+        }
+        for (int set = 0; set < SETS; set++)
+        {
+            for (int s = 0; s < C::WSTAGES; s++)
+            {
+                mbar_init(full_w(set, s), 1);
+                mbar_init(empty_w(set, s), 4 * C::DQ_GROUPS * 32);
+            }
+            for (int s = 0; s < C::ASTAGES; s++)
+            {
+                mbar_init(full_a(set, s), 128);
+                mbar_init(empty_a(set, s), 1);
+            }
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == MMA_WARP)
+    {
+        tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS); // whole warp; the address lands in shared memory
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == TMA_WARP)
+    {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0)
+        {
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; kb++)
+            {
+                if (kb % C::KB_PER_CHUNK == 0)
+                {
+                    const int chunk = kb / C::KB_PER_CHUNK, s = chunk % C::WSTAGES;
+                    const uint32_t ph = (uint32_t)(chunk / C::WSTAGES) & 1u;
+                    for (int set = 0; set < SETS && ok; set++)
+                    {
+                        ok = wait_or_abort(empty_w(set, s), ph ^ 1u, abort_flag);
+                        if (!ok)
+                            break;
+                        mbar_arrive_expect_tx(full_w(set, s), C::W_STAGE_BYTES);
+                        tma_load_2d(smem_u32(wsm + (size_t)(set * C::WSTAGES + s) * C::W_STAGE_BYTES),
+                                    set == 0 ? &tmap_w0 : &tmap_w1, full_w(set, s), chunk * 128, n0);
+                    }
+                }
+                if (!ok)
+                    break;
+                const int s = kb % C::XSTAGES;
+                const uint32_t ph = (uint32_t)(kb / C::XSTAGES) & 1u;
+                ok = wait_or_abort(empty_x(s), ph ^ 1u, abort_flag);
+                if (!ok)
+                    break;
+                mbar_arrive_expect_tx(full_x(s), C::X_STAGE_BYTES);
+                tma_load_2d(smem_u32(xs + (size_t)s * C::X_STAGE_BYTES), &tmap_x, full_x(s), kb * C::BK, m0);
+            }
+        }
+    }
+    else if (warp == MMA_WARP)
+    {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0)
+        {
+            // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = BX, M = 128
+            constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(C::BX >> 3) << 17) | ((uint32_t)(C::BN >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; kb++)
+            {
+                const int sx = kb % C::XSTAGES, sa = kb % C::ASTAGES;
+                ok = wait_or_abort(full_x(sx), (uint32_t)(kb / C::XSTAGES) & 1u, abort_flag);
+                for (int set = 0; set < SETS && ok; set++)
+                    ok = wait_or_abort(full_a(set, sa), (uint32_t)(kb / C::ASTAGES) & 1u, abort_flag);
+                if (!ok)
+                    break;
+                tcgen05_fence_after();
+                const uint32_t xaddr = smem_u32(xs + (size_t)sx * C::X_STAGE_BYTES);
+#pragma unroll
+                for (int set = 0; set < SETS; set++)
+                {
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(set * C::BX);
+                    const uint32_t a_tmem = tmem_base + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS);
+#pragma unroll
+                    for (int kk = 0; kk < C::BK / 16; kk++)
+                        tcgen05_mma_ts(d_tmem, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
+                                       (kb | kk) != 0 ? 1u : 0u);
+                }
+                tcgen05_commit(empty_x(sx)); // arrives when the MMAs above have consumed the stage
+#pragma unroll
+                for (int set = 0; set < SETS; set++)
+                    tcgen05_commit(empty_a(set, sa));
+            }
+            tcgen05_commit(acc_full);
+        }
+    }
+    else
+    {
+        // ------------------------------------------------------------ dequantise into tensor memory
+        const int set = DUAL ? warp / (4 * C::DQ_GROUPS) : 0;
+        const int grp = (warp >> 2) % C::DQ_GROUPS;
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;           // row of the tile = TMEM lane
+        const int n = min(n0 + r, p.N - 1);          // rows past N read the last row's parameters, never stored
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const int kb_per_group = p.group / C::BK;
+        bool ok = true;
+
+        auto load_scale = [&](int gidx) -> float {
+            const size_t i = (size_t)n * p.G + gidx;
+            return p.scale_f32 ? __ldg(static_cast<const float*>(p.scale[set]) + i)
+                               : __half2float(__ldg(static_cast<const __half*>(p.scale[set]) + i));
+        };
+        auto load_zp = [&](int gidx) -> uint32_t {
+            if (WBITS == 4)
+                return (__ldg(p.zp[set] + (size_t)n * p.zp_row_bytes + (gidx >> 1)) >> (4 * (gidx & 1))) & 0xF;
+            return __ldg(p.zp[set] + (size_t)n * p.G + gidx);
+        };
+        int cur_g = -1;
+        float sc = 0.f;
+        uint32_t zq = 0;
+
+        for (int kb = grp; kb < KB && ok; kb += C::DQ_GROUPS)
+        {
+            const int chunk = kb / C::KB_PER_CHUNK, j = kb % C::KB_PER_CHUNK, sw = chunk % C::WSTAGES;
+            const int gidx = kb / kb_per_group;
+            if (gidx != cur_g)
+            {
+                cur_g = gidx;
+                sc = load_scale(gidx);
+                zq = load_zp(gidx);
+            }
+            if (j < C::DQ_GROUPS) // first k-block of this chunk for this thread
+                ok = wait_or_abort(full_w(set, sw), (uint32_t)(chunk / C::WSTAGES) & 1u, abort_flag);
+            if (!ok)
+                break;
+            // this row's raw bytes: 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
+            const uint8_t* row = wsm + (size_t)(set * C::WSTAGES + sw) * C::W_STAGE_BYTES + r * 128;
+            constexpr int NV = C::RAW_BYTES / 16;
+            uint4 raw[NV];
+#pragma unroll
+            for (int v = 0; v < NV; v++)
+                raw[v] = *reinterpret_cast<const uint4*>(row + (((j * NV + v) ^ (r & 7)) * 16));
+            if (j + C::DQ_GROUPS >= C::KB_PER_CHUNK || kb + C::DQ_GROUPS >= KB)
+                mbar_arrive(empty_w(set, sw)); // last read of this chunk by this thread
+
+            const __half2 s2 = __float2half2_rn(sc);
+            uint32_t a[32]; // 64 fp16 in k order: register i holds k = 2i (low half) and 2i + 1 (high half)
+            if (WBITS == 4)
+            {
+                const uint32_t zc = (0x6400u | zq) | ((0x5400u | (zq << 4)) << 16); // (1024 + zp, 64 + zp)
+#pragma unroll
+                for (int v = 0; v < NV; v++)
+                {
+                    const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
+#pragma unroll
+                    for (int wi = 0; wi < 4; wi++)
+#pragma unroll
+                        for (int b = 0; b < 4; b++)
+                        {
+                            // byte b of the word holds elements 2b (bits 0-3) and 2b+1 (bits 4-7)
+                            uint32_t t = __byte_perm(w4[wi], 0u, 0x1111u * b);
+                            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(t), "n"(0x00F0000Fu), "n"(0x54006400u));
+                            __half2 h = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<const __half2*>(&zc));
+                            h = __hmul2(h, s2);
+                            a[(v * 4 + wi) * 4 + b] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                }
+            }
+            else
+            {
+                const uint32_t zc = (0x6400u | zq) * 0x00010001u; // 1024 + zp in both halves
+#pragma unroll
+                for (int v = 0; v < NV; v++)
+                {
+                    const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
+#pragma unroll
+                    for (int wi = 0; wi < 4; wi++)
+#pragma unroll
+                        for (int b = 0; b < 2; b++)
+                        {
+                            uint32_t t = __byte_perm(w4[wi], 0x64646464u, b ? 0x4342 : 0x4140); // 1024 + (b0, b1)
+                            __half2 h = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<const __half2*>(&zc));
+                            h = __hmul2(h, s2);
+                            a[(v * 4 + wi) * 2 + b] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                }
+            }
+            const int sa = kb % C::ASTAGES;
+            ok = wait_or_abort(empty_a(set, sa), ((uint32_t)(kb / C::ASTAGES) & 1u) ^ 1u, abort_flag);
+            if (!ok)
+                break;
+            tcgen05_fence_after();
+            tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS), a);
+            tcgen05_wait_st();
+            tcgen05_fence_before();
+            mbar_arrive(full_a(set, sa));
+        }
+
+        // ------------------------------------------------------------ epilogue
+        if (ok)
+            ok = wait_or_abort(acc_full, 0u, abort_flag);
+        if (ok)
+        {
+            tcgen05_fence_after();
+            // column blocks of 32 batch rows, dealt over the warps that share this TMEM lane quarter
+            constexpr int PEERS = C::DQ_WARPS / 4;   // warps per quarter
+            const int peer = warp >> 2;              // 0 .. PEERS-1
+            const int nrow = n0 + r;
+            const float bias = (p.has_bias && nrow < p.N) ? __ldg(p.bias + nrow) : 0.f;
+            for (int cb = peer; cb < C::BX / 32; cb += PEERS)
+            {
+                uint32_t d0[32], d1[32];
+                tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(cb * 32), d0);
+                if (DUAL)
+                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::BX + cb * 32), d1);
+                tcgen05_wait_ld();
+#pragma unroll
+                for (int jx = 0; jx < 32; jx++)
+                {
+                    const int m = m0 + cb * 32 + jx;
+                    float v = __uint_as_float(d0[jx]);
+                    if (DUAL)
+                    {
+                        const float u = __uint_as_float(d1[jx]);
+                        v = v * (1.0f / (1.0f + expf(-v))) * u;
+                    }
+                    v += bias;
+                    if (m < p.M && nrow < p.N)
+                    {
+                        if (p.y_f32)
+                            static_cast<float*>(p.y)[(size_t)m * p.N + nrow] = v;
+                        else
+                            static_cast<__half*>(p.y)[(size_t)m * p.N + nrow] = __float2half_rn(v);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- tear-down
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP)
+    {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+    if (tid == 0 && *abort_flag)
+        atomicExch(p.status, 1);
+}
+
+template <int WBITS, bool DUAL>
+cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap& tw0, const CUtensorMap& tw1,
+                   int grid, cudaStream_t stream)
+{
+    using C = Cfg<WBITS, DUAL>;
+    static bool configured = false;
+    if (!configured)
+    {
+        cudaError_t e = cudaFuncSetAttribute(dq_gemm_kernel<WBITS, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)C::SMEM_BYTES);
+        if (e != cudaSuccess)
+            return e;
+        configured = true;
+    }
+    (void)cudaGetLastError();
+    dq_gemm_kernel<WBITS, DUAL><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, tx, tw0, tw1);
+    return cudaGetLastError();
+}
+} // namespace
+
 namespace nnf
 {
-size_t gemm_workspace_bytes(const nnf_b200_ctx*, const nnf_b200_linear_desc&) { return 0; }
-int gemm_supported(const nnf_b200_ctx*, const nnf_b200_linear_desc&, std::string* why)
+int gemm_configure(nnf_b200_ctx*)
 {
-    *why = "large-M kernel not built";
-    return NNF_B200_ENOTSUP;
+    return NNF_B200_OK;
 }
-int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t, const nnf_b200_linear_desc&, const void*, const nnf_b200_qweight*,
-                const nnf_b200_qweight*, const void*, const void*, void*, void*, size_t)
+
+size_t gemm_workspace_bytes(const nnf_b200_ctx*, const nnf_b200_linear_desc&)
 {
-    return set_error(ctx, NNF_B200_ENOTSUP, "large-M kernel not built");
+    return 0;
 }
-int gemm_configure(nnf_b200_ctx*) { return NNF_B200_OK; }
+
+int gemm_supported(const nnf_b200_ctx*, const nnf_b200_linear_desc& d, std::string* why)
+{
+    const int group = d.group_size > 0 ? d.group_size : d.K;
+    if (d.x_dtype != NNF_B200_F16)
+    {
+        *why = "tensor-core kernel takes fp16 activations";
+        return NNF_B200_ENOTSUP;
+    }
+    if (d.prologue != NNF_B200_PROLOGUE_NONE)
+    {
+        *why = "tensor-core kernel has no RMSNorm prologue";
+        return NNF_B200_ENOTSUP;
+    }
+    if (d.K % 64 != 0 || group % 64 != 0 || d.K % group != 0)
+    {
+        *why = "K and group_size must be multiples of 64 and K a multiple of group_size";
+        return NNF_B200_ENOTSUP;
+    }
+    if ((d.w_bits == 4 ? d.K / 2 : d.K) % 16 != 0)
+    {
+        *why = "weight rows must be a multiple of 16 bytes";
+        return NNF_B200_ENOTSUP;
+    }
+    return NNF_B200_OK;
+}
+
+int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const void* x,
+                const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void*, const void* bias, void* y, void*,
+                size_t)
+{
+    const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
+    const int bx = dual ? 128 : 256;
+    const int row_bytes = d.w_bits == 4 ? d.K / 2 : d.K;
+    GemmParams p{};
+    p.scale[0] = w->scale;
+    p.zp[0] = static_cast<const uint8_t*>(w->zp);
+    if (dual)
+    {
+        p.scale[1] = w2->scale;
+        p.zp[1] = static_cast<const uint8_t*>(w2->zp);
+    }
+    p.bias = static_cast<const float*>(bias);
+    p.y = y;
+    p.status = ctx->dev_status;
+    p.M = d.M, p.N = d.N, p.K = d.K;
+    p.group = d.group_size > 0 ? d.group_size : d.K;
+    p.G = d.K / p.group;
+    p.zp_row_bytes = d.w_bits == 4 ? (p.G + 1) / 2 : p.G;
+    p.y_f32 = d.y_dtype == NNF_B200_F32;
+    p.scale_f32 = d.scale_dtype == NNF_B200_F32;
+    p.has_bias = bias != nullptr;
+    p.m_tiles = (d.M + bx - 1) / bx;
+    const int n_tiles = (d.N + 127) / 128;
+
+    // x: fp16 [M][K], boxes of BX rows x 64 elements (the tensor map is not cached: x moves between calls)
+    alignas(64) CUtensorMap tx;
+    if (!encode_tensor_map_2d(ctx->encode_tiled, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)d.K,
+                              (uint64_t)d.M, (uint64_t)d.K * 2, 64, (uint32_t)bx, CU_TENSOR_MAP_SWIZZLE_128B))
+        return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the activations");
+    const CUtensorMap* tw0 = weight_tensor_map(ctx, w->wq, d.N, row_bytes, 128, 128);
+    const CUtensorMap* tw1 = dual ? weight_tensor_map(ctx, w2->wq, d.N, row_bytes, 128, 128) : tw0;
+    if (!tw0 || !tw1)
+        return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
+
+    const int grid = p.m_tiles * n_tiles;
+    cudaError_t e;
+    if (d.w_bits == 4)
+        e = dual ? launch<4, true>(p, tx, *tw0, *tw1, grid, stream) : launch<4, false>(p, tx, *tw0, *tw1, grid, stream);
+    else
+        e = dual ? launch<8, true>(p, tx, *tw0, *tw1, grid, stream) : launch<8, false>(p, tx, *tw0, *tw1, grid, stream);
+    if (e != cudaSuccess)
+        return set_error(ctx, NNF_B200_ECUDA, std::string("dq_gemm launch: ") + cudaGetErrorString(e));
+    ctx->launches++;
+    return NNF_B200_OK;
+}
 } // namespace nnf
