@@ -10,8 +10,8 @@
 // The CTA computes a transposed output tile  D[128 weight rows, BX batch rows] = Wdq[128, K] . X[BX, K]^T  so
 // that the dequantised weights are the MMA's A operand and can be handed to the tensor core through TENSOR MEMORY
 // instead of shared memory:
-//   * warp "TMA"  : one thread streams x tiles (BX rows x 64 fp16, 128-byte swizzle, the MMA's B operand) and raw
-//                   packed-weight chunks (128 rows x 128 bytes, 128-byte swizzle) into shared-memory rings;
+//   * warps "TMA" : one thread streams x tiles (BX rows x 64 fp16, 128-byte swizzle, the MMA's B operand), another
+//                   raw packed-weight chunks (128 rows x 128 bytes, 128-byte swizzle), into shared-memory rings;
 //   * warps "DQ"  : thread r owns weight row r of the tile = TMEM lane r.  Per 64-element k-block it reads its 32
 //                   (uint4) or 64 (uint8) bytes from the raw ring, turns them into fp16 (q - zp) * scale with the
 //                   exponent trick (PRMT + LOP3 + HSUB2 + HMUL2 per pair, exact integer before the scale), and
@@ -42,14 +42,14 @@ struct Cfg
     static constexpr int BN = 128;              // weight rows per CTA  (UMMA M, TMEM lanes)
     static constexpr int BX = DUAL ? 128 : 256; // batch rows per CTA   (UMMA N, accumulator columns per set)
     static constexpr int BK = 64;               // k-block: one 128-byte swizzle row of fp16
-    static constexpr int XSTAGES = DUAL ? 6 : 4;
+    static constexpr int XSTAGES = DUAL ? 6 : 5;
     static constexpr int WSTAGES = 3;
-    static constexpr int ASTAGES = 4;
+    static constexpr int ASTAGES = DUAL ? 4 : 8;
     static constexpr int KB_PER_CHUNK = (WBITS == 4) ? 4 : 2; // k-blocks per 128-byte raw chunk
     static constexpr int RAW_BYTES = (WBITS == 4) ? 32 : 64;  // raw bytes per row and k-block
     static constexpr int DQ_GROUPS = 2;                       // groups of 4 warps alternating k-blocks
     static constexpr int DQ_WARPS = 4 * DQ_GROUPS * SETS;
-    static constexpr int THREADS = (DQ_WARPS + 2) * 32;
+    static constexpr int THREADS = (DQ_WARPS + 3) * 32;
     static constexpr int X_STAGE_BYTES = BX * 128;
     static constexpr int W_STAGE_BYTES = BN * 128;
     static constexpr int A_COL0 = SETS * BX;     // first TMEM column of the A stages
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     const int m_tile = blockIdx.x % p.m_tiles, n_tile = blockIdx.x / p.m_tiles;
     const int m0 = m_tile * C::BX, n0 = n_tile * C::BN;
     const int KB = p.K / C::BK;
-    constexpr int TMA_WARP = C::DQ_WARPS, MMA_WARP = C::DQ_WARPS + 1;
+    constexpr int TMA_WARP = C::DQ_WARPS, MMA_WARP = C::DQ_WARPS + 1, TMAW_WARP = C::DQ_WARPS + 2;
 
     // ---------------------------------------------------------------- set-up
     if (tid == 0)
@@ -167,28 +167,12 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
 
     if (warp == TMA_WARP)
     {
-        // ------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------ TMA producer: activation tiles
         if (lane == 0)
         {
             bool ok = true;
             for (int kb = 0; kb < KB && ok; kb++)
             {
-                if (kb % C::KB_PER_CHUNK == 0)
-                {
-                    const int chunk = kb / C::KB_PER_CHUNK, s = chunk % C::WSTAGES;
-                    const uint32_t ph = (uint32_t)(chunk / C::WSTAGES) & 1u;
-                    for (int set = 0; set < SETS && ok; set++)
-                    {
-                        ok = wait_or_abort(empty_w(set, s), ph ^ 1u, abort_flag);
-                        if (!ok)
-                            break;
-                        mbar_arrive_expect_tx(full_w(set, s), C::W_STAGE_BYTES);
-                        tma_load_2d(smem_u32(wsm + (size_t)(set * C::WSTAGES + s) * C::W_STAGE_BYTES),
-                                    set == 0 ? &tmap_w0 : &tmap_w1, full_w(set, s), chunk * 128, n0);
-                    }
-                }
-                if (!ok)
-                    break;
                 const int s = kb % C::XSTAGES;
                 const uint32_t ph = (uint32_t)(kb / C::XSTAGES) & 1u;
                 ok = wait_or_abort(empty_x(s), ph ^ 1u, abort_flag);
@@ -196,6 +180,31 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                     break;
                 mbar_arrive_expect_tx(full_x(s), C::X_STAGE_BYTES);
                 tma_load_2d(smem_u32(xs + (size_t)s * C::X_STAGE_BYTES), &tmap_x, full_x(s), kb * C::BK, m0);
+            }
+        }
+    }
+    else if (warp == TMAW_WARP)
+    {
+        // ------------------------------------------------------------ TMA producer: raw weight chunks
+        // A loop of its own: the chunks run as far ahead as their ring allows (WSTAGES * KB_PER_CHUNK k-blocks),
+        // so that their load latency and the conversion stay off the tensor core's critical path.
+        if (lane == 0)
+        {
+            bool ok = true;
+            const int chunks = (KB + C::KB_PER_CHUNK - 1) / C::KB_PER_CHUNK;
+            for (int chunk = 0; chunk < chunks && ok; chunk++)
+            {
+                const int s = chunk % C::WSTAGES;
+                const uint32_t ph = (uint32_t)(chunk / C::WSTAGES) & 1u;
+                for (int set = 0; set < SETS && ok; set++)
+                {
+                    ok = wait_or_abort(empty_w(set, s), ph ^ 1u, abort_flag);
+                    if (!ok)
+                        break;
+                    mbar_arrive_expect_tx(full_w(set, s), C::W_STAGE_BYTES);
+                    tma_load_2d(smem_u32(wsm + (size_t)(set * C::WSTAGES + s) * C::W_STAGE_BYTES),
+                                set == 0 ? &tmap_w0 : &tmap_w1, full_w(set, s), chunk * 128, n0);
+                }
             }
         }
     }
@@ -257,24 +266,32 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 return (__ldg(p.zp[set] + (size_t)n * p.zp_row_bytes + (gidx >> 1)) >> (4 * (gidx & 1))) & 0xF;
             return __ldg(p.zp[set] + (size_t)n * p.G + gidx);
         };
-        int cur_g = -1;
-        float sc = 0.f;
-        uint32_t zq = 0;
-
-        for (int kb = grp; kb < KB && ok; kb += C::DQ_GROUPS)
+        // (scale, zero-point) of the k-block in hand and, prefetched one iteration ahead, of the next one: the
+        // loads complete while the current k-block is converted.
+        float sc = 0.f, sc_next = 0.f;
+        uint32_t zq = 0, zq_next = 0;
+        if (grp < KB)
         {
+            sc_next = load_scale(grp / kb_per_group);
+            zq_next = load_zp(grp / kb_per_group);
+        }
+
+        // Raw bytes of k-block kb -> 64 fp16 (q - zp) * scale in k order: register i holds k = 2i (low half) and
+        // k = 2i + 1 (high half).  Returns false if the wait for the raw chunk was aborted.
+        auto convert = [&](int kb, uint32_t (&a)[32]) -> bool {
             const int chunk = kb / C::KB_PER_CHUNK, j = kb % C::KB_PER_CHUNK, sw = chunk % C::WSTAGES;
-            const int gidx = kb / kb_per_group;
-            if (gidx != cur_g)
+            sc = sc_next, zq = zq_next;
             {
-                cur_g = gidx;
-                sc = load_scale(gidx);
-                zq = load_zp(gidx);
+                const int kb_n = kb + C::DQ_GROUPS;
+                if (kb_n < KB && kb_n / kb_per_group != kb / kb_per_group)
+                {
+                    sc_next = load_scale(kb_n / kb_per_group);
+                    zq_next = load_zp(kb_n / kb_per_group);
+                }
             }
             if (j < C::DQ_GROUPS) // first k-block of this chunk for this thread
-                ok = wait_or_abort(full_w(set, sw), (uint32_t)(chunk / C::WSTAGES) & 1u, abort_flag);
-            if (!ok)
-                break;
+                if (!wait_or_abort(full_w(set, sw), (uint32_t)(chunk / C::WSTAGES) & 1u, abort_flag))
+                    return false;
             // this row's raw bytes: 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
             const uint8_t* row = wsm + (size_t)(set * C::WSTAGES + sw) * C::W_STAGE_BYTES + r * 128;
             constexpr int NV = C::RAW_BYTES / 16;
@@ -286,7 +303,6 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 mbar_arrive(empty_w(set, sw)); // last read of this chunk by this thread
 
             const __half2 s2 = __float2half2_rn(sc);
-            uint32_t a[32]; // 64 fp16 in k order: register i holds k = 2i (low half) and 2i + 1 (high half)
             if (WBITS == 4)
             {
                 const uint32_t zc = (0x6400u | zq) | ((0x5400u | (zq << 4)) << 16); // (1024 + zp, 64 + zp)
@@ -327,15 +343,43 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                         }
                 }
             }
+            return true;
+        };
+        // Hand the converted k-block to the tensor core: wait for the A stage, store to tensor memory.
+        auto stage = [&](int kb, const uint32_t (&a)[32]) -> bool {
             const int sa = kb % C::ASTAGES;
-            ok = wait_or_abort(empty_a(set, sa), ((uint32_t)(kb / C::ASTAGES) & 1u) ^ 1u, abort_flag);
-            if (!ok)
-                break;
+            if (!wait_or_abort(empty_a(set, sa), ((uint32_t)(kb / C::ASTAGES) & 1u) ^ 1u, abort_flag))
+                return false;
             tcgen05_fence_after();
             tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS), a);
+            return true;
+        };
+        auto publish = [&](int kb) {
             tcgen05_wait_st();
             tcgen05_fence_before();
-            mbar_arrive(full_a(set, sa));
+            mbar_arrive(full_a(set, kb % C::ASTAGES));
+        };
+        // Two register buffers: while the tensor-memory store of one k-block drains, the next one is converted.
+        uint32_t a0[32], a1[32];
+        int kb = grp;
+        if (kb < KB)
+            ok = convert(kb, a0);
+        while (ok && kb < KB)
+        {
+            const int kb1 = kb + C::DQ_GROUPS, kb2 = kb1 + C::DQ_GROUPS;
+            if (!(ok = stage(kb, a0)))
+                break;
+            if (kb1 < KB && !(ok = convert(kb1, a1)))
+                break;
+            publish(kb);
+            if (kb1 >= KB)
+                break;
+            if (!(ok = stage(kb1, a1)))
+                break;
+            if (kb2 < KB && !(ok = convert(kb2, a0)))
+                break;
+            publish(kb1);
+            kb = kb2;
         }
 
         // ------------------------------------------------------------ epilogue
