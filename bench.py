@@ -1,0 +1,509 @@
+#!/usr/bin/env python
+"""Benchmark of the dequantize-fused low-bit linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  Workloads (``--workload``; ``auto`` picks by ``--gpus``):
+
+  decode_gemv     (1 GPU, default)  uint4 group-128 decode GEMV: X fp16 [1,4096], W [11008,4096]; a step is one call of
+                  the fused linear on the next of 12 weight copies (282 MB in rotation, larger than L2), so every step
+                  reads its weights from HBM.  value = algorithmic bytes / time in GB/s.
+  mlp70b_decode   (N GPUs, default for N > 1)  LLaMA-70B-shaped SwiGLU MLP at M = 1, uint4 group-128: gate/up split
+                  by column, down by row, one NCCL all-reduce of the fp16 [1,8192] output; a step is the whole MLP
+                  (366 MB of weights, larger than L2).  value = algorithmic bytes of the whole job / time, GB/s.
+  prefill_gemm    (1 GPU)  uint4 group-128 GEMM, X fp16 [4096,4096], W [11008,4096]; value in TFLOP/s.
+
+``--impl reference`` times the reference's own CPU path for the same workload (vendored MLAS SGEMM behind the
+Convert / Subtract / Multiply kernels its CPU code generation emits, all host threads) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+L2_BYTES = 126e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one dq_gemv_kernel launch on the decode_gemv workload
+# (ncu capture summarised in profiles/dq_gemv_decode_11008x4096.md).
+NCU_TRAFFIC_DECODE_GEMV = 23_493_888
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                r = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                    "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                if r.returncode == 0 and r.stdout.strip():
+                    self.rows.append([c.strip() for c in r.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=10)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = [float(r[0]) for r in self.rows if r[0].replace(".", "").isdigit()]
+        reasons = []
+        for name, col in (("hw_slowdown", 3), ("hw_thermal_slowdown", 4), ("sw_thermal_slowdown", 5), ("sw_power_cap", 6)):
+            if any(r[col] == "Active" for r in self.rows if len(r) > col):
+                reasons.append(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(self.rows[0][1]),
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def rand_device_weight(torch, N, K, bits=4, group=128, scale_dtype=None, device="cuda"):
+    """Random quantised weights generated on the device (content does not matter for timing)."""
+    from nnfusion_b200.linear import DeviceWeight
+    scale_dtype = scale_dtype or torch.float16
+    G = K // group
+    wq = torch.randint(0, 256, (N, K // 2 if bits == 4 else K), dtype=torch.uint8, device=device)
+    sc = (torch.rand((N, G), device=device) * 0.018 + 0.002).to(scale_dtype)
+    zp = torch.randint(0, 256, (N, (G + 1) // 2 if bits == 4 else G), dtype=torch.uint8, device=device)
+    return DeviceWeight(N, K, bits, group, wq, sc, zp)
+
+
+def linear_bytes(M, N, K, bits=4, group=128, act_bytes=2, scale_bytes=2):
+    """Algorithmic bytes of one linear: packed weights + scales + zero-points + x + y, each once."""
+    G = K // group
+    return N * K * bits // 8 + N * G * scale_bytes + N * ((G + 1) // 2 if bits == 4 else G) + M * K * act_bytes + M * N * act_bytes
+
+
+def timed_graph_steps(torch, step_fns, steps, warmup, dist=None):
+    """Runs `steps` steps (step i calls step_fns[i % len]) replayed from CUDA graphs, timed with CUDA events on the
+    launching stream between barrier + synchronize on both sides.  Returns milliseconds (max over ranks)."""
+    n = len(step_fns)
+    stream = torch.cuda.Stream()
+    chunk = min(steps, max(n, (1200 // n) * n))
+    graphs = {}
+
+    def graph_of(count):
+        if count not in graphs:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(count):
+                    step_fns[i % n]()
+            graphs[count] = g
+        return graphs[count]
+
+    with torch.cuda.stream(stream):
+        for i in range(max(warmup, 3)):
+            step_fns[i % n]()
+        torch.cuda.synchronize()
+        full, rem = divmod(steps, chunk)
+        g_full = graph_of(chunk) if full else None
+        g_rem = graph_of(rem) if rem else None
+        # graph warm-up: brings the clocks up and pages everything in
+        t0 = time.time()
+        while time.time() - t0 < 0.5:
+            (g_full or g_rem).replay()
+            torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(full):
+            g_full.replay()
+        if g_rem is not None:
+            g_rem.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def timed_plain_steps(torch, step_fn, steps, warmup, dist=None):
+    """Same contract without graph capture (used where a step contains a collective or host copies)."""
+    for i in range(max(warmup, 3)):
+        step_fn(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step_fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+# ----------------------------------------------------------------------------------------------- CPU reference path
+def cpu_reference_gemv(seconds_budget: float, rows: int, K: int = 4096, M: int = 1, steps=None, warmup: int = 1):
+    """Times the reference CPU graph (oracle/_ref: MLAS behind restated element-wise kernels; falls back to the C
+    restatement) on a `rows`-row sample of the uint4 group-128 linear.  Returns (seconds per step, steps, cores, kind)."""
+    import numpy as np
+    from oracle import oracle as orc
+    rng = np.random.Generator(np.random.PCG64(0))
+    x = rng.standard_normal((M, K), dtype=np.float32).astype(np.float16).astype(np.float32)
+    q = rng.integers(0, 16, size=(rows, K), dtype=np.uint8)          # nibbles unpacked, as the graph sees them
+    scale = rng.uniform(0.002, 0.02, size=(rows, K // 128)).astype(np.float16).astype(np.float32)
+    zp = rng.integers(0, 16, size=(rows, K // 128), dtype=np.uint8)
+    if orc.have_ref():
+        graph = orc.RefLinearGraph(rows, K)
+        fn = lambda: graph(x, q, scale, zp, 128)
+        cores, kind = orc.ref_threads(), "reference"
+    else:
+        fn = lambda: orc.linear(x, q, scale, zp, 128, out_dtype=np.float32)
+        cores, kind = os.cpu_count() or 1, "port"
+    for _ in range(max(1, warmup)):
+        fn()
+    times = []
+    t_start = time.perf_counter()
+    i = 0
+    while True:
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+        i += 1
+        if steps is not None and i >= steps:
+            break
+        if steps is None and (time.perf_counter() - t_start > seconds_budget and i >= 5):
+            break
+    return sum(times) / len(times), len(times), cores, kind
+
+
+# ----------------------------------------------------------------------------------------------- workloads (ours)
+def run_decode_gemv(args, torch, sampler_index):
+    from nnfusion_b200.linear import DequantDot, default_context
+    N, K, M = 11008, 4096, 1
+    ncopies = 12
+    ctx = default_context(torch.cuda.current_device())
+    ops = [DequantDot(rand_device_weight(torch, N, K)) for _ in range(ncopies)]
+    x = torch.randn(M, K, device="cuda").to(torch.float16)
+    y = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    step_fns = [(lambda op=op: op(x, y)) for op in ops]
+    ctx.launch_count(reset=True)
+    with ClockSampler(sampler_index) as cs:
+        ms = timed_graph_steps(torch, step_fns, args.steps, args.warmup)
+    ctx.device_status()
+    bytes_step = linear_bytes(M, N, K)
+    value = bytes_step * args.steps / (ms * 1e-3) / 1e9
+
+    # end to end through the call a user of the generated runtime makes with host buffers (kernel_entry_host):
+    # pinned host x -> device, the fused linear, device y -> pinned host, every step, synchronising per step.
+    xh = torch.randn(M, K).to(torch.float16).pin_memory()
+    yh = torch.empty(M, N, dtype=torch.float16).pin_memory()
+    e2e_steps = min(args.steps, 2000)
+
+    def e2e_step(i):
+        x.copy_(xh, non_blocking=True)
+        ops[i % ncopies](x, y)
+        yh.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    ms_e2e = timed_plain_steps(torch, e2e_step, e2e_steps, args.warmup)
+    e2e_value = bytes_step * e2e_steps / (ms_e2e * 1e-3) / 1e9
+    peaks = measured_peaks()
+    out = {
+        "metric": "int4_g128_decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
+        "ms_per_step": ms / args.steps, "dtype": "f16", "scaling": "weak",
+        "config": {"workload": "decode_gemv: X f16 [1,4096], W u4-g128 [11008,4096], Y f16, f32 accumulate",
+                   "algorithmic_bytes_per_step": bytes_step,
+                   "l2": f"rotation over {ncopies} weight copies ({ncopies * bytes_step / 1e6:.0f} MB) larger than L2",
+                   "launch": "CUDA graph replay of the C-ABI calls"},
+        "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(value / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_DECODE_GEMV,
+                     "peak_source": f"of {peaks['source']}", "kernel": "dq_gemv_kernel<4,1,false,false,false>"},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": M * K * 2,
+                "d2h_bytes_per_step": M * N * 2, "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
+                "path": "pinned host x -> device, nnf_b200_linear, device y -> pinned host, stream sync, per step"},
+        "gpu_launches": args.steps, "clocks": cs.summary(),
+    }
+    return out, ops, x, y
+
+
+def extra_measurements(torch, budget_s=60.0):
+    """Other regimes of the same path at 1 GPU, reported beside the headline (each a few hundred ms of GPU time)."""
+    from nnfusion_b200.linear import DequantDot
+    peaks = measured_peaks()
+    also = {}
+    t_begin = time.time()
+
+    def gemv(name, M, N, K, ncopies, bits=4, group=128, xdt=torch.float16, sdt=torch.float16, dual=False, gain=False, steps=600):
+        if time.time() - t_begin > budget_s:
+            return
+        ops = []
+        for _ in range(ncopies):
+            w = rand_device_weight(torch, N, K, bits, group, sdt)
+            w2 = rand_device_weight(torch, N, K, bits, group, sdt) if dual else None
+            g = (torch.rand(K, device="cuda") + 0.5) if gain else None
+            ops.append(DequantDot(w, w2, gain=g))
+        x = torch.randn(M, K, device="cuda").to(xdt)
+        y = torch.empty(M, N, device="cuda", dtype=xdt)
+        ms = timed_graph_steps(torch, [(lambda op=op: op(x, y)) for op in ops], steps, 3)
+        b = linear_bytes(M, N, K, bits, group, x.element_size(), 2 if sdt == torch.float16 else 4)
+        if dual:
+            b += b - M * K * x.element_size() - M * N * x.element_size()
+        gbs = b * steps / (ms * 1e-3) / 1e9
+        also[name] = {"us": round(ms * 1e3 / steps, 2), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
+
+    def gemm(name, M, N, K, dual=False, steps=20):
+        if time.time() - t_begin > budget_s:
+            return
+        w = rand_device_weight(torch, N, K)
+        w2 = rand_device_weight(torch, N, K) if dual else None
+        op = DequantDot(w, w2)
+        x = torch.randn(M, K, device="cuda").to(torch.float16)
+        y = torch.empty(M, N, device="cuda", dtype=torch.float16)
+        ms = timed_plain_steps(torch, lambda i: op(x, y), steps, 5)
+        tf = 2.0 * M * N * K * (2 if dual else 1) * steps / (ms * 1e-3) / 1e12
+        also[name] = {"us": round(ms * 1e3 / steps, 1), "TFLOP/s": round(tf, 1),
+                      "frac_of_bf16_burst_peak": round(tf / peaks["bf16_tflops"], 4),
+                      "frac_of_bf16_sustained_peak": round(tf / peaks["bf16_tflops_sustained"], 4)}
+
+    gemv("decode_gemv_down_4096x11008", 1, 4096, 11008, 12)
+    gemv("config1_u8_perchannel_f32_m16_4096x4096", 16, 4096, 4096, 12, bits=8, group=4096, xdt=torch.float32, sdt=torch.float32)
+    gemv("mlp70b_gate_up_silu_m1_28672x8192", 1, 28672, 8192, 2, dual=True, steps=100)
+    gemv("mlp70b_down_m1_8192x28672", 1, 8192, 28672, 3, steps=150)
+    for M in (256, 1024, 4096):
+        gemm(f"prefill_gemm_up_m{M}_11008x4096", M, 11008, 4096)
+    gemm("prefill_gemm_down_m4096_4096x11008", 4096, 4096, 11008)
+    return also
+
+
+def run_prefill_gemm(args, torch, sampler_index):
+    from nnfusion_b200.linear import DequantDot, default_context
+    M, N, K = 4096, 11008, 4096
+    ctx = default_context(torch.cuda.current_device())
+    op = DequantDot(rand_device_weight(torch, N, K))
+    x = torch.randn(M, K, device="cuda").to(torch.float16)
+    y = torch.empty(M, N, device="cuda", dtype=torch.float16)
+    with ClockSampler(sampler_index) as cs:
+        ms = timed_plain_steps(torch, lambda i: op(x, y), args.steps, args.warmup)
+    ctx.device_status()
+    tf = 2.0 * M * N * K * args.steps / (ms * 1e-3) / 1e12
+    peaks = measured_peaks()
+    xh = torch.randn(M, K).to(torch.float16).pin_memory()
+    yh = torch.empty(M, N, dtype=torch.float16).pin_memory()
+
+    def e2e_step(i):
+        x.copy_(xh, non_blocking=True)
+        op(x, y)
+        yh.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = min(args.steps, 50)
+    ms_e2e = timed_plain_steps(torch, e2e_step, e2e_steps, 3)
+    return {
+        "metric": "int4_g128_prefill_gemm_tflops", "value": round(tf, 1), "unit": "TFLOP/s",
+        "ms_per_step": ms / args.steps, "dtype": "f16", "scaling": "weak",
+        "config": {"workload": "prefill_gemm: X f16 [4096,4096], W u4-g128 [11008,4096], Y f16, f32 accumulate",
+                   "l2": "x (33.6 MB) + y (90 MB) + weights (23 MB) per step exceed L2"},
+        "roofline": {"bound": "tensor", "achieved": round(tf, 1), "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": round(tf / peaks["bf16_tflops_sustained"], 4), "traffic": None,
+                     "peak_source": f"of {peaks['source']} (sustained)", "kernel": "dq_gemm_kernel<4,false>"},
+        "e2e": {"value": round(2.0 * M * N * K * e2e_steps / (ms_e2e * 1e-3) / 1e12, 1), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2},
+        "gpu_launches": args.steps, "clocks": cs.summary(),
+    }
+
+
+def run_mlp70b(args, torch, sampler_index, rank, world, dist):
+    """LLaMA-70B-shaped SwiGLU MLP, M = 1 decode, sharded over `world` GPUs."""
+    from nnfusion_b200.linear import default_context
+    from nnfusion_b200.tp import ShardedMLP, mlp_shapes
+    hidden, inter, M = 8192, 28672, 1
+    (n_gu, k_gu), (n_d, k_d) = mlp_shapes(hidden, inter, world)
+    ctx = default_context(torch.cuda.current_device())
+    # per-rank bytes per step must exceed L2 or the weights must rotate
+    per_rank = 2 * (linear_bytes(M, n_gu, k_gu) - M * k_gu * 2 - M * n_gu * 2) + linear_bytes(M, n_d, k_d)
+    ncopies = max(1, int(L2_BYTES * 2.2 // per_rank) + 1)
+    group = dist.group.WORLD if world > 1 else None
+    mlps = [ShardedMLP(rand_device_weight(torch, n_gu, k_gu), rand_device_weight(torch, n_gu, k_gu),
+                       rand_device_weight(torch, n_d, k_d), group=group) for _ in range(ncopies)]
+    x = torch.randn(M, hidden, device="cuda").to(torch.float16)
+    ctx.launch_count(reset=True)
+    with ClockSampler(sampler_index) as cs:
+        ms = timed_plain_steps(torch, lambda i: mlps[i % ncopies](x), args.steps, args.warmup, dist if world > 1 else None)
+    ctx.device_status()
+    full = 2 * (linear_bytes(M, inter, hidden) - M * hidden * 2 - M * inter * 2) + M * hidden * 2 + 2 * M * inter * 2 + \
+        linear_bytes(M, hidden, inter) - M * inter * 2
+    value = full * args.steps / (ms * 1e-3) / 1e9
+    peaks = measured_peaks()
+    xh = torch.randn(M, hidden).to(torch.float16).pin_memory()
+    yh = torch.empty(M, hidden, dtype=torch.float16).pin_memory()
+
+    def e2e_step(i):
+        x.copy_(xh, non_blocking=True)
+        y = mlps[i % ncopies](x)
+        yh.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = min(args.steps, 500)
+    ms_e2e = timed_plain_steps(torch, e2e_step, e2e_steps, 3, dist if world > 1 else None)
+    return {
+        "metric": "int4_g128_decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
+        "ms_per_step": ms / args.steps, "dtype": "f16", "scaling": "strong",
+        "config": {"workload": "mlp70b_decode: X f16 [1,8192], gate/up u4-g128 [28672,8192] column-sharded, down [8192,28672] "
+                               "row-sharded, NCCL all-reduce of f16 [1,8192]",
+                   "algorithmic_bytes_per_step": full, "parallelism": f"tp{world}",
+                   "l2": f"{ncopies} weight copies per rank in rotation ({ncopies * per_rank / 1e6:.0f} MB per rank) larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": round(value / world, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(value / world / peaks["hbm_gbs"], 4), "traffic": None,
+                     "peak_source": f"of {peaks['source']}, per GPU", "kernel": "dq_gemv_kernel (gate/up fused SiLU*mul, down)"},
+        "e2e": {"value": round(full * e2e_steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
+                "h2d_bytes_per_step": M * hidden * 2, "d2h_bytes_per_step": M * hidden * 2},
+        "gpu_launches": 2 * args.steps,
+        "clocks": cs.summary(),
+    }
+
+
+# ----------------------------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", default="auto", choices=["auto", "decode_gemv", "mlp70b_decode", "prefill_gemm"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements at 1 GPU")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    workload = args.workload
+    if workload == "auto":
+        workload = "decode_gemv" if max(world, args.gpus) == 1 else "mlp70b_decode"
+
+    if args.impl == "reference":
+        # The reference's CPU path, rank 0 only; other ranks leave without work.
+        if rank != 0:
+            return 0
+        steps = args.steps if args.steps is not None else 20
+        warmup = args.warmup if args.warmup is not None else 3
+        if workload == "prefill_gemm":
+            M, K, rows, full_rows = 4096, 4096, 344, 11008
+        elif workload == "mlp70b_decode":
+            M, K, rows, full_rows = 1, 8192, 896, 28672
+        else:
+            M, K, rows, full_rows = 1, 4096, 1376, 11008
+        sec, n, cores, kind = cpu_reference_gemv(0.0, rows, K, M, steps=steps, warmup=warmup)
+        if workload == "prefill_gemm":
+            value, unit, metric = 2.0 * M * rows * K / sec / 1e12, "TFLOP/s", "int4_g128_prefill_gemm_tflops"
+        else:
+            value, unit, metric = linear_bytes(M, rows, K) / sec / 1e9, "GB/s", "int4_g128_decode_gemv_hbm_gbs"
+        sample = (f"{rows} of {full_rows} weight rows per step (same K, same M); Convert/Subtract/Multiply restated, "
+                  f"Dot = reference MLAS SGEMM" if kind == "reference" else f"{rows} of {full_rows} rows, C restatement")
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": n,
+            "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload + " (CPU reference path)"},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+        return 0
+
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: this benchmark has no CPU path for --impl ours"}))
+        return 2
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        if workload == "decode_gemv":
+            steps_default, warmup_default = 2400, 240
+        elif workload == "prefill_gemm":
+            steps_default, warmup_default = 50, 5
+        else:
+            steps_default, warmup_default = 400, 40
+        args.steps = args.steps if args.steps is not None else steps_default
+        args.warmup = max(3, args.warmup if args.warmup is not None else warmup_default)
+
+        if workload == "decode_gemv":
+            out, *_ = run_decode_gemv(args, torch, local_rank)
+        elif workload == "prefill_gemm":
+            out = run_prefill_gemm(args, torch, local_rank)
+        else:
+            out = run_mlp70b(args, torch, local_rank, rank, world, dist)
+        if rank == 0:
+            out.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+                        "vs_baseline": None, "data": "synthetic", "impl": "ours"})
+            if world == 1:
+                # the reference's CPU path on this box's host cores, bounded sample
+                if workload == "prefill_gemm":
+                    sec, n, cores, kind = cpu_reference_gemv(10.0, 344, 4096, 4096)
+                    v, unit = 2.0 * 4096 * 344 * 4096 / sec / 1e12, "TFLOP/s"
+                    sample = "344 of 11008 weight rows, M = 4096, ~10 s"
+                elif workload == "mlp70b_decode":
+                    sec, n, cores, kind = cpu_reference_gemv(10.0, 896, 8192, 1)
+                    v, unit = linear_bytes(1, 896, 8192) / sec / 1e9, "GB/s"
+                    sample = "896 of 28672 gate rows (K = 8192), ~10 s"
+                else:
+                    sec, n, cores, kind = cpu_reference_gemv(10.0, 1376, 4096, 1)
+                    v, unit = linear_bytes(1, 1376, 4096) / sec / 1e9, "GB/s"
+                    sample = "1376 of 11008 weight rows per call (dequant graph + MLAS SGEMM), ~10 s of calls"
+                out["cpu_baseline"] = {"value": v, "unit": unit, "cores": cores, "kind": kind, "sample": sample,
+                                       "calls": n, "ms_per_call": sec * 1e3}
+                if not args.no_extras:
+                    out["also"] = extra_measurements(torch)
+            order = ["metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                     "vs_baseline", "dtype", "data", "config", "roofline", "cpu_baseline", "e2e", "gpu_launches", "clocks"]
+            line = {k: out[k] for k in order if k in out}
+            line.update({k: v for k, v in out.items() if k not in line})
+            print(json.dumps(line))
+    finally:
+        if dist is not None:
+            dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
