@@ -182,6 +182,32 @@ NNF_B200_API int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200
                     const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
                     const void* bias, void* y, void* workspace, size_t workspace_bytes);
 
+/* Size of the scratch array built into the library for nnf_b200_linear_static_scratch. */
+#define NNF_B200_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+
+/* nnf_b200_linear for callers that cannot hand over a workspace because they cannot
+ * allocate device memory any more: code inside a stream capture, loops whose memory
+ * budget is frozen after start-up, processes held to a fixed GPU quota.  It has no
+ * counterpart in the reference (whose kernels get their scratch planned into the
+ * generated runtime's pool).  It serves the small-M kernel (M <= 16), the one whose
+ * split-K path needs scratch, and takes that scratch from an array of
+ * NNF_B200_STATIC_SCRATCH_BYTES that is part of the library's device image: every GPU
+ * that loads the library holds it until the process ends.  It needs no context and
+ * calls no allocator.  Shapes whose split-K scratch exceeds the array are refused with
+ * NNF_B200_EWORKSPACE (the text in errbuf names both sizes).
+ * The first call made while a given device is current fetches the array's device
+ * address, raises the kernel's shared-memory limit and looks up the tensor-map encoder:
+ * make that call outside of any stream capture.  Every call uses the same array and
+ * finds in it what the previous call left; the counters that must start at zero are
+ * cleared on `stream` by each call.  Two calls that overlap on the GPU (for instance
+ * on two streams of one process) race on the array: serialise them.  Each process
+ * has its own copy of the array.
+ * errbuf (may be NULL) receives a message of at most errbuf_len bytes on failure. */
+NNF_B200_API int nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, const void* x,
+                                                const nnf_b200_qweight* w, const nnf_b200_qweight* w2,
+                                                const void* gain, const void* bias, void* y, char* errbuf,
+                                                size_t errbuf_len);
+
 /* Reads (and clears) the device-side status word: 0, or NNF_B200_ETIMEDOUT when a
  * bounded wait inside a kernel gave up since the last query.  Synchronises the
  * stream; meant for tests and debugging, not for the hot path. */

@@ -17,12 +17,13 @@ PROLOGUE_NONE, PROLOGUE_RMSNORM = 0, 1
 EPILOGUE_NONE, EPILOGUE_BIAS, EPILOGUE_SILU_MUL = 0, 1, 2
 KERNEL_AUTO, KERNEL_GEMV, KERNEL_GEMM = 0, 1, 2
 FLAG_EXACT_ZP = 1
+STATIC_SCRATCH_BYTES = 4 * 1024 * 1024
 
 # Every symbol include/nnf_b200.h declares.
 EXPORTS = (
     "nnf_b200_init", "nnf_b200_free", "nnf_b200_strerror", "nnf_b200_last_error", "nnf_b200_sm_count",
     "nnf_b200_linear_workspace_bytes", "nnf_b200_workspace_reset", "nnf_b200_linear",
-    "nnf_b200_launch_count", "nnf_b200_pack_u4", "nnf_b200_device_status", "nnf_b200_linear_plan",
+    "nnf_b200_launch_count", "nnf_b200_pack_u4", "nnf_b200_device_status", "nnf_b200_linear_plan", "nnf_b200_linear_static_scratch",
 )
 
 
@@ -68,6 +69,8 @@ def load() -> ctypes.CDLL:
     L.nnf_b200_linear.argtypes = [vp, vp, ctypes.POINTER(LinearDesc), vp, ctypes.POINTER(QWeight),
                                   ctypes.POINTER(QWeight), vp, vp, vp, vp, sz]
     L.nnf_b200_device_status.argtypes = [vp, vp]
+    L.nnf_b200_linear_static_scratch.argtypes = [vp, ctypes.POINTER(LinearDesc), vp, ctypes.POINTER(QWeight),
+                                                 ctypes.POINTER(QWeight), vp, vp, vp, ctypes.c_char_p, sz]
     L.nnf_b200_linear_plan.argtypes = [vp, ctypes.POINTER(LinearDesc), ctypes.POINTER(ctypes.c_int32 * 8)]
     L.nnf_b200_launch_count.argtypes = [vp, ctypes.c_int]
     L.nnf_b200_launch_count.restype = ctypes.c_uint64

@@ -929,3 +929,201 @@ int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     return NNF_B200_OK;
 }
 } // namespace nnf
+
+// ------------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the split-K small-M linear.
+//
+// Who needs it: code that runs where device memory can no longer be requested -- inside a section that is being
+// captured into a CUDA graph, in a real-time or safety-certified loop whose memory budget is frozen after start-up,
+// or in a process that shares the GPU under a hard quota and must not grow.  Such a caller cannot obtain the split-K
+// workspace that nnf_b200_linear expects from it.  Here the workspace is a fixed array that lives in the library's
+// own device image, so every GPU that loads the library carries NNF_B200_STATIC_SCRATCH_BYTES of it until the process
+// exits, and nothing is ever allocated or freed.
+//
+// The array's name is only a host-side handle in host code; the device address is fetched with
+// cudaGetSymbolAddress once per device, by the first call made while that device is current.  That first call also
+// raises the kernel's shared-memory limit and looks up the driver's tensor-map encoder, so it should be made
+// outside of any stream capture.  All calls share the one array (and it keeps what the previous call left): calls
+// that overlap on the GPU race on it; the tile counters are cleared on the stream at the start of every call.
+namespace
+{
+static __device__ __align__(256) unsigned char g_static_scratch[NNF_B200_STATIC_SCRATCH_BYTES];
+static __device__ int g_static_status;
+
+struct StaticDeviceState
+{
+    bool ready = false;
+    void* scratch = nullptr;
+    int* status = nullptr;
+    void* encode_tiled = nullptr;
+    int sm_count = 0;
+    int smem_optin = 0;
+};
+StaticDeviceState g_static_state[64];
+
+void put_message(char* buf, size_t len, const char* msg)
+{
+    if (buf && len)
+        snprintf(buf, len, "%s", msg);
+}
+} // namespace
+
+extern "C" __attribute__((visibility("default"))) int
+nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, const void* x,
+                               const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
+                               const void* bias, void* y, char* errbuf, size_t errbuf_len)
+{
+    using namespace nnf;
+    put_message(errbuf, errbuf_len, "");
+    if (!desc || !x || !y || !w || !w->wq || !w->scale || !w->zp)
+    {
+        put_message(errbuf, errbuf_len, "null descriptor, activations, output or weight set");
+        return NNF_B200_EINVAL;
+    }
+    const nnf_b200_linear_desc& d = *desc;
+    const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
+    if (d.M < 1 || d.N < 1 || d.K < 1 || (d.w_bits != 4 && d.w_bits != 8) || d.group_size < 0 ||
+        (dual && (!w2 || !w2->wq || !w2->scale || !w2->zp)) || (!dual && w2) ||
+        ((d.prologue == NNF_B200_PROLOGUE_RMSNORM) != (gain != nullptr)) ||
+        ((d.epilogue == NNF_B200_EPILOGUE_BIAS) != (bias != nullptr)))
+    {
+        put_message(errbuf, errbuf_len, "malformed descriptor or operands that do not match it");
+        return NNF_B200_EINVAL;
+    }
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(w->wq) & 15u) ||
+        (dual && (reinterpret_cast<uintptr_t>(w2->wq) & 15u)) || (gain && (reinterpret_cast<uintptr_t>(gain) & 15u)))
+    {
+        put_message(errbuf, errbuf_len, "x, wq and gain must be 16-byte aligned");
+        return NNF_B200_EALIGN;
+    }
+
+    // ---- once per device, with that device current
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    {
+        put_message(errbuf, errbuf_len, "no current CUDA device");
+        return NNF_B200_ECUDA;
+    }
+    StaticDeviceState& st = g_static_state[dev];
+    if (!st.ready)
+    {
+        void* sp = nullptr;
+        void* tp = nullptr;
+        if (cudaGetSymbolAddress(&sp, g_static_scratch) != cudaSuccess || !sp ||
+            cudaGetSymbolAddress(&tp, g_static_status) != cudaSuccess || !tp)
+        {
+            put_message(errbuf, errbuf_len, "cudaGetSymbolAddress failed for the built-in scratch array");
+            return NNF_B200_ECUDA;
+        }
+        int major = 0;
+        if (cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
+        {
+            put_message(errbuf, errbuf_len, "device attributes unavailable, or not an sm_100 device");
+            return NNF_B200_ENOTSUP;
+        }
+        st.encode_tiled = load_encode_tiled();
+        if (!st.encode_tiled)
+        {
+            put_message(errbuf, errbuf_len, "cuTensorMapEncodeTiled entry point not found");
+            return NNF_B200_ECUDA;
+        }
+        st.scratch = sp;
+        st.status = static_cast<int*>(tp);
+        st.ready = true;
+    }
+
+    // ---- launch shape; the only kernel served here is the small-M one, which is the one that needs scratch
+    nnf_b200_ctx shape_ctx; // plain host struct, used only to carry the device's SM count and shared-memory limit
+    shape_ctx.device = dev;
+    shape_ctx.sm_count = st.sm_count;
+    shape_ctx.smem_optin = st.smem_optin;
+    GemvPlan plan;
+    std::string why;
+    int rc = gemv_plan(&shape_ctx, d, &plan, &why);
+    if (rc != NNF_B200_OK)
+    {
+        put_message(errbuf, errbuf_len, why.c_str());
+        return rc;
+    }
+    if (plan.workspace_bytes > (size_t)NNF_B200_STATIC_SCRATCH_BYTES)
+    {
+        char msg[160];
+        snprintf(msg, sizeof msg, "this shape needs %zu bytes of scratch; the built-in array holds %d",
+                 plan.workspace_bytes, (int)NNF_B200_STATIC_SCRATCH_BYTES);
+        put_message(errbuf, errbuf_len, msg);
+        return NNF_B200_EWORKSPACE;
+    }
+
+    const int ue = (d.w_bits == 4) ? 128 : 64;
+    const int row_bytes = (d.w_bits == 4) ? d.K / 2 : d.K;
+    alignas(64) CUtensorMap t0, t1;
+    if (!encode_tensor_map_2d(st.encode_tiled, &t0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->wq, (uint64_t)row_bytes,
+                              (uint64_t)d.N, (uint64_t)row_bytes, 128, 16, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_tensor_map_2d(st.encode_tiled, &t1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, dual ? w2->wq : w->wq,
+                              (uint64_t)row_bytes, (uint64_t)d.N, (uint64_t)row_bytes, 128, 16,
+                              CU_TENSOR_MAP_SWIZZLE_128B))
+    {
+        put_message(errbuf, errbuf_len, "cuTensorMapEncodeTiled failed for the weight tensor");
+        return NNF_B200_ECUDA;
+    }
+
+    GemvParams p{};
+    p.scale[0] = w->scale;
+    p.zp[0] = static_cast<const uint8_t*>(w->zp);
+    if (dual)
+    {
+        p.scale[1] = w2->scale;
+        p.zp[1] = static_cast<const uint8_t*>(w2->zp);
+    }
+    p.x = x;
+    p.gain = static_cast<const float*>(gain);
+    p.bias = static_cast<const float*>(bias);
+    p.y = y;
+    p.status = st.status;
+    p.M = d.M, p.N = d.N, p.K = d.K;
+    p.group = d.group_size > 0 ? d.group_size : d.K;
+    p.G = d.K / p.group;
+    p.zp_row_bytes = (d.w_bits == 4) ? (p.G + 1) / 2 : p.G;
+    p.units = d.K / ue;
+    p.slices = plan.slices;
+    p.row_tiles = plan.row_tiles;
+    p.splits = plan.splits;
+    p.ctas_per_split = plan.ctas_per_split;
+    p.x_f32 = d.x_dtype == NNF_B200_F32;
+    p.y_f32 = d.y_dtype == NNF_B200_F32;
+    p.scale_f32 = d.scale_dtype == NNF_B200_F32;
+    p.rmsnorm = d.prologue == NNF_B200_PROLOGUE_RMSNORM;
+    p.has_bias = bias != nullptr;
+    p.eps = d.rms_eps;
+    p.depth = plan.depth;
+    p.slot_floats = (int)plan.slot_floats;
+    const size_t scale_bytes = (size_t)d.N * p.G * (p.scale_f32 ? 4 : 2);
+    const size_t zp_bytes = (size_t)d.N * p.zp_row_bytes;
+    auto word_ok = [](const void* ptr, size_t bytes) {
+        return (reinterpret_cast<uintptr_t>(ptr) & 3u) == 0 && (bytes & 3u) == 0;
+    };
+    p.fast_params = word_ok(w->scale, scale_bytes) && word_ok(w->zp, zp_bytes) &&
+                    (!dual || (word_ok(w2->scale, scale_bytes) && word_ok(w2->zp, zp_bytes)));
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (plan.splits > 1)
+    {
+        // The array keeps the previous call's contents: the per-tile arrival counters have to start at zero.
+        const size_t cnt = ((size_t)plan.row_tiles * sizeof(unsigned) + 255) / 256 * 256;
+        if (cudaMemsetAsync(st.scratch, 0, cnt, s) != cudaSuccess)
+        {
+            put_message(errbuf, errbuf_len, "cudaMemsetAsync on the built-in scratch array failed");
+            return NNF_B200_ECUDA;
+        }
+        p.ws_count = static_cast<unsigned*>(st.scratch);
+        p.ws_slots = reinterpret_cast<float*>(static_cast<char*>(st.scratch) + cnt);
+    }
+    cudaError_t e = dispatch(d.w_bits, plan, p, t0, t1, plan.splits * plan.ctas_per_split, s);
+    if (e != cudaSuccess)
+    {
+        put_message(errbuf, errbuf_len, cudaGetErrorString(e));
+        return NNF_B200_ECUDA;
+    }
+    return NNF_B200_OK;
+}
