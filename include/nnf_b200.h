@@ -186,8 +186,8 @@ NNF_B200_API int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200
 #define NNF_B200_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
 
 /* nnf_b200_linear for callers that cannot hand over a workspace because they cannot
- * allocate device memory any more: code inside a stream capture, loops whose memory
- * budget is frozen after start-up, processes held to a fixed GPU quota.  It has no
+ * allocate device memory any more: loops whose memory budget is frozen after
+ * start-up, processes held to a fixed GPU quota.  It has no
  * counterpart in the reference (whose kernels get their scratch planned into the
  * generated runtime's pool).  It serves the small-M kernel (M <= 16), the one whose
  * split-K path needs scratch, and takes that scratch from an array of

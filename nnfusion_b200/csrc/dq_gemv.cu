@@ -933,8 +933,8 @@ int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
 // ------------------------------------------------------------------------------------------------------------------
 // Allocation-free variant of the split-K small-M linear.
 //
-// Who needs it: code that runs where device memory can no longer be requested -- inside a section that is being
-// captured into a CUDA graph, in a real-time or safety-certified loop whose memory budget is frozen after start-up,
+// Who needs it: code that runs where device memory can no longer be requested -- in a real-time or
+// safety-certified loop whose memory budget is frozen after start-up,
 // or in a process that shares the GPU under a hard quota and must not grow.  Such a caller cannot obtain the split-K
 // workspace that nnf_b200_linear expects from it.  Here the workspace is a fixed array that lives in the library's
 // own device image, so every GPU that loads the library carries NNF_B200_STATIC_SCRATCH_BYTES of it until the process

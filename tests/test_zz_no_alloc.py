@@ -1,5 +1,5 @@
-"""The allocation-free entry point, for callers that can no longer ask CUDA for memory (inside a stream capture,
-with a frozen memory budget, under a fixed GPU quota): it takes its split-K scratch from an array built into the
+"""The allocation-free entry point, for callers that can no longer ask CUDA for memory (a memory budget frozen
+after start-up, a fixed GPU quota): it takes its split-K scratch from an array built into the
 library instead of from a caller-provided workspace.  Its result must equal that of the regular entry point.
 
 Collected last on purpose (file name): a run that stops at the first failure has then already run every other test.
