@@ -151,7 +151,8 @@ NNF_B200_API int nnf_b200_sm_count(const nnf_b200_ctx* ctx);
  * pool (src/nnfusion/core/kernels/kernel_emitter.cpp:282-319).  The scratch must
  * be zero-filled once before its first use (nnf_b200_workspace_reset); every
  * call leaves it zeroed again.  Calls that share one scratch buffer must not
- * overlap on the device. */
+ * overlap on the device.  ctx may be NULL (a 148-SM device is assumed), for sizing
+ * at code-generation time. */
 NNF_B200_API size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc);
 
 /* Launch shape the library would use for a descriptor, for tuning and reporting:
