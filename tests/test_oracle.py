@@ -149,3 +149,16 @@ def test_reference_graph_vs_oracle_config1_small():
     np.testing.assert_array_equal(graph.wdq, orc.c_dequant(w.q, w.scale, w.zp, 512))
     y = orc.linear(x, w.q, w.scale, w.zp, 512)
     assert orc.max_rel_err(y, r) < 2e-6
+
+
+def test_oracle_against_committed_mlas_fixture():
+    """Outputs of the reference's MLAS path, generated by tests/golden/make_golden.py and committed."""
+    import os
+    from tests.golden import make_golden as mg
+    fx = np.load(os.path.join(os.path.dirname(mg.__file__), "mlas_linear_small.npz"))
+    for name, (kind, kw) in mg.CASES.items():
+        x, w = mg.inputs(kind, kw)
+        y = orc.linear(x.astype(np.float32), w.q, w.scale, w.zp, w.group, out_dtype=np.float32)
+        assert orc.max_rel_err(y, fx[name]) < 2e-6, name
+        y2 = orc.linear(x.astype(np.float32), w.q, w.scale, w.zp, w.group, out_dtype=np.float32, naive_dot=True)
+        assert orc.max_rel_err(y2, fx[name]) < 2e-6, name
