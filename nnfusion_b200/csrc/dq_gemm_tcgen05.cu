@@ -42,9 +42,12 @@ struct Cfg
     static constexpr int BN = 128;              // weight rows per CTA  (UMMA M, TMEM lanes)
     static constexpr int BX = DUAL ? 128 : 256; // batch rows per CTA   (UMMA N, accumulator columns per set)
     static constexpr int BK = 64;               // k-block: one 128-byte swizzle row of fp16
-    static constexpr int XSTAGES = DUAL ? 6 : 5;
+    // One ring index for the x tile in shared memory and the converted weights in tensor memory: the MMA thread
+    // then has a single barrier to wait for and a single one to release per k-block.
+    static constexpr int STAGES = DUAL ? 4 : 5;
+    static constexpr int XSTAGES = STAGES;
     static constexpr int WSTAGES = 3;
-    static constexpr int ASTAGES = DUAL ? 4 : 8;
+    static constexpr int ASTAGES = STAGES;
     static constexpr int KB_PER_CHUNK = (WBITS == 4) ? 4 : 2; // k-blocks per 128-byte raw chunk
     static constexpr int RAW_BYTES = (WBITS == 4) ? 32 : 64;  // raw bytes per row and k-block
     static constexpr int DQ_GROUPS = 2;                       // groups of 4 warps alternating k-blocks
@@ -55,7 +58,7 @@ struct Cfg
     static constexpr int A_COL0 = SETS * BX;     // first TMEM column of the A stages
     static constexpr int A_STAGE_COLS = BK / 2;  // 64 fp16 per lane = 32 columns
     static constexpr int TMEM_COLS = 512;
-    static constexpr int NUM_BARRIERS = 2 * XSTAGES + 2 * SETS * WSTAGES + 2 * SETS * ASTAGES + 1;
+    static constexpr int NUM_BARRIERS = 2 * STAGES + 2 * SETS * WSTAGES + 1;
     static constexpr size_t SMEM_BYTES =
         1024 + (size_t)XSTAGES * X_STAGE_BYTES + (size_t)SETS * WSTAGES * W_STAGE_BYTES + NUM_BARRIERS * 8 + 64;
     static_assert(A_COL0 + SETS * ASTAGES * A_STAGE_COLS <= TMEM_COLS, "tensor memory budget");
@@ -73,6 +76,7 @@ struct GemmParams
     int group, G, zp_row_bytes;
     int y_f32, scale_f32, has_bias;
     int m_tiles;
+    int fast_store; // fp16 y, N a multiple of 8, y 16-byte aligned: the tile is written in 16-byte pieces
 };
 
 constexpr uint32_t kGemmSpin = 1u << 22;
@@ -84,6 +88,7 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     {
         if (mbar_try_wait(bar, parity))
             return true;
+        __nanosleep(40); // a waiting role should not compete with the working ones for issue slots and power
         if ((i & 255u) == 255u && *abort_flag)
             return false;
     }
@@ -114,14 +119,12 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const uint32_t bar0 = smem_u32(bars);
-    auto full_x = [&](int s) { return bar0 + 8u * s; };
-    auto empty_x = [&](int s) { return bar0 + 8u * (C::XSTAGES + s); };
-    auto full_w = [&](int set, int s) { return bar0 + 8u * (2 * C::XSTAGES + set * C::WSTAGES + s); };
-    auto empty_w = [&](int set, int s) { return bar0 + 8u * (2 * C::XSTAGES + SETS * C::WSTAGES + set * C::WSTAGES + s); };
-    auto full_a = [&](int set, int s) { return bar0 + 8u * (2 * C::XSTAGES + 2 * SETS * C::WSTAGES + set * C::ASTAGES + s); };
-    auto empty_a = [&](int set, int s) {
-        return bar0 + 8u * (2 * C::XSTAGES + 2 * SETS * C::WSTAGES + SETS * C::ASTAGES + set * C::ASTAGES + s);
-    };
+    // full(s): the x tile has landed (TMA transaction bytes) and every conversion thread has stored its row of
+    // the stage (SETS * 128 arrivals); empty(s): the MMAs that read the stage have completed (tcgen05.commit).
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto empty = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+    auto full_w = [&](int set, int s) { return bar0 + 8u * (2 * C::STAGES + set * C::WSTAGES + s); };
+    auto empty_w = [&](int set, int s) { return bar0 + 8u * (2 * C::STAGES + SETS * C::WSTAGES + set * C::WSTAGES + s); };
     const uint32_t acc_full = bar0 + 8u * (C::NUM_BARRIERS - 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -133,24 +136,17 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     // ---------------------------------------------------------------- set-up
     if (tid == 0)
     {
-        for (int s = 0; s < C::XSTAGES; s++)
+        for (int s = 0; s < C::STAGES; s++)
         {
-            mbar_init(full_x(s), 1);
-            mbar_init(empty_x(s), 1);
+            mbar_init(full(s), SETS * 128 + 1);
+            mbar_init(empty(s), 1);
         }
         for (int set = 0; set < SETS; set++)
-        {
             for (int s = 0; s < C::WSTAGES; s++)
             {
                 mbar_init(full_w(set, s), 1);
                 mbar_init(empty_w(set, s), 4 * C::DQ_GROUPS * 32);
             }
-            for (int s = 0; s < C::ASTAGES; s++)
-            {
-                mbar_init(full_a(set, s), 128);
-                mbar_init(empty_a(set, s), 1);
-            }
-        }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -175,11 +171,11 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
             {
                 const int s = kb % C::XSTAGES;
                 const uint32_t ph = (uint32_t)(kb / C::XSTAGES) & 1u;
-                ok = wait_or_abort(empty_x(s), ph ^ 1u, abort_flag);
+                ok = wait_or_abort(empty(s), ph ^ 1u, abort_flag);
                 if (!ok)
                     break;
-                mbar_arrive_expect_tx(full_x(s), C::X_STAGE_BYTES);
-                tma_load_2d(smem_u32(xs + (size_t)s * C::X_STAGE_BYTES), &tmap_x, full_x(s), kb * C::BK, m0);
+                mbar_arrive_expect_tx(full(s), C::X_STAGE_BYTES);
+                tma_load_2d(smem_u32(xs + (size_t)s * C::X_STAGE_BYTES), &tmap_x, full(s), kb * C::BK, m0);
             }
         }
     }
@@ -218,10 +214,8 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
             bool ok = true;
             for (int kb = 0; kb < KB && ok; kb++)
             {
-                const int sx = kb % C::XSTAGES, sa = kb % C::ASTAGES;
-                ok = wait_or_abort(full_x(sx), (uint32_t)(kb / C::XSTAGES) & 1u, abort_flag);
-                for (int set = 0; set < SETS && ok; set++)
-                    ok = wait_or_abort(full_a(set, sa), (uint32_t)(kb / C::ASTAGES) & 1u, abort_flag);
+                const int sx = kb % C::STAGES, sa = sx;
+                ok = wait_or_abort(full(sx), (uint32_t)(kb / C::STAGES) & 1u, abort_flag);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
@@ -236,10 +230,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                         tcgen05_mma_ts(d_tmem, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
                                        (kb | kk) != 0 ? 1u : 0u);
                 }
-                tcgen05_commit(empty_x(sx)); // arrives when the MMAs above have consumed the stage
-#pragma unroll
-                for (int set = 0; set < SETS; set++)
-                    tcgen05_commit(empty_a(set, sa));
+                tcgen05_commit(empty(sx)); // arrives when the MMAs above have consumed the stage
             }
             tcgen05_commit(acc_full);
         }
@@ -348,7 +339,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
         // Hand the converted k-block to the tensor core: wait for the A stage, store to tensor memory.
         auto stage = [&](int kb, const uint32_t (&a)[32]) -> bool {
             const int sa = kb % C::ASTAGES;
-            if (!wait_or_abort(empty_a(set, sa), ((uint32_t)(kb / C::ASTAGES) & 1u) ^ 1u, abort_flag))
+            if (!wait_or_abort(empty(sa), ((uint32_t)(kb / C::ASTAGES) & 1u) ^ 1u, abort_flag))
                 return false;
             tcgen05_fence_after();
             tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS), a);
@@ -357,7 +348,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
         auto publish = [&](int kb) {
             tcgen05_wait_st();
             tcgen05_fence_before();
-            mbar_arrive(full_a(set, kb % C::ASTAGES));
+            mbar_arrive(full(kb % C::ASTAGES));
         };
         // Two register buffers: while the tensor-memory store of one k-block drains, the next one is converted.
         uint32_t a0[32], a1[32];
@@ -383,40 +374,65 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
         }
 
         // ------------------------------------------------------------ epilogue
+        // D holds y transposed (lane = weight row n, column = batch row m).  With fp16 output the tile is turned
+        // around through shared memory (the x ring is idle by now) so that y is written in 16-byte pieces along n;
+        // otherwise every value is stored on its own.
         if (ok)
             ok = wait_or_abort(acc_full, 0u, abort_flag);
         if (ok)
-        {
             tcgen05_fence_after();
-            // column blocks of 32 batch rows, dealt over the warps that share this TMEM lane quarter
-            constexpr int PEERS = C::DQ_WARPS / 4;   // warps per quarter
+        {
+            constexpr int PEERS = C::DQ_WARPS / 4;   // warps per TMEM lane quarter
             const int peer = warp >> 2;              // 0 .. PEERS-1
             const int nrow = n0 + r;
             const float bias = (p.has_bias && nrow < p.N) ? __ldg(p.bias + nrow) : 0.f;
-            for (int cb = peer; cb < C::BX / 32; cb += PEERS)
+            __half* stage_t = reinterpret_cast<__half*>(xs); // [BX][128] halves, row m = 256 bytes
+            if (ok)
             {
-                uint32_t d0[32], d1[32];
-                tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(cb * 32), d0);
-                if (DUAL)
-                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::BX + cb * 32), d1);
-                tcgen05_wait_ld();
-#pragma unroll
-                for (int jx = 0; jx < 32; jx++)
+                for (int cb = peer; cb < C::BX / 32; cb += PEERS)
                 {
-                    const int m = m0 + cb * 32 + jx;
-                    float v = __uint_as_float(d0[jx]);
+                    uint32_t d0[32], d1[32];
+                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(cb * 32), d0);
                     if (DUAL)
+                        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::BX + cb * 32), d1);
+                    tcgen05_wait_ld();
+#pragma unroll
+                    for (int jx = 0; jx < 32; jx++)
                     {
-                        const float u = __uint_as_float(d1[jx]);
-                        v = v * (1.0f / (1.0f + expf(-v))) * u;
+                        const int ml = cb * 32 + jx, m = m0 + ml;
+                        float v = __uint_as_float(d0[jx]);
+                        if (DUAL)
+                        {
+                            const float u = __uint_as_float(d1[jx]);
+                            v = v * (1.0f / (1.0f + expf(-v))) * u;
+                        }
+                        v += bias;
+                        if (p.fast_store)
+                            stage_t[ml * 128 + r] = __float2half_rn(v);
+                        else if (m < p.M && nrow < p.N)
+                        {
+                            if (p.y_f32)
+                                static_cast<float*>(p.y)[(size_t)m * p.N + nrow] = v;
+                            else
+                                static_cast<__half*>(p.y)[(size_t)m * p.N + nrow] = __float2half_rn(v);
+                        }
                     }
-                    v += bias;
-                    if (m < p.M && nrow < p.N)
+                }
+            }
+            if (p.fast_store)
+            {
+                // all conversion warps (and only they) meet here, whether or not they got this far unharmed
+                asm volatile("bar.sync 1, %0;" ::"n"(C::DQ_WARPS * 32) : "memory");
+                if (!*abort_flag)
+                {
+                    const int t = warp * 32 + lane; // 0 .. DQ_WARPS*32-1
+                    for (int c = t; c < C::BX * 16; c += C::DQ_WARPS * 32)
                     {
-                        if (p.y_f32)
-                            static_cast<float*>(p.y)[(size_t)m * p.N + nrow] = v;
-                        else
-                            static_cast<__half*>(p.y)[(size_t)m * p.N + nrow] = __float2half_rn(v);
+                        const int ml = c >> 4, nc = (c & 15) * 8;
+                        const int m = m0 + ml, n = n0 + nc;
+                        if (m < p.M && n < p.N)
+                            *reinterpret_cast<uint4*>(static_cast<__half*>(p.y) + (size_t)m * p.N + n) =
+                                *reinterpret_cast<const uint4*>(stage_t + ml * 128 + nc);
                     }
                 }
             }
@@ -519,6 +535,7 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     p.scale_f32 = d.scale_dtype == NNF_B200_F32;
     p.has_bias = bias != nullptr;
     p.m_tiles = (d.M + bx - 1) / bx;
+    p.fast_store = !p.y_f32 && d.N % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0;
     const int n_tiles = (d.N + 127) / 128;
 
     // x: fp16 [M][K], boxes of BX rows x 64 elements (the tensor map is not cached: x moves between calls)
