@@ -5,21 +5,24 @@
 // followed by the cuBLAS Dot (src/nnfusion/core/kernels/cuda_gpu/kernels/dot.cpp:27-372): the
 // weights are read once, at their packed size, and never materialised in fp32.
 //
-// The kernel is HBM-bound and, next to that, bound by instruction issue; its shape follows from both:
+// The kernel is HBM-bound and, next to that, bound by instruction issue and by the latency of whatever sits between
+// the start of the CTA and its first arithmetic; its shape follows from all three:
 //   * a weight row is cut into 128-byte "slices" (256 uint4 / 128 uint8 elements).  Warp w of a CTA owns slice
-//     (first slice of the CTA's K range + w) for the whole launch, so the activations it needs are loaded and
-//     converted once and live in registers as mma B fragments;
-//   * CTAs are persistent: CTA c of a K split walks over the 16-row tiles c, c + P, c + 2P ...  The weight tiles
-//     arrive by TMA (one thread issues a 16-row x 128-byte box per warp and tile, 128-byte swizzle, completion
-//     counted on an mbarrier per ring slot) into a shared-memory ring several tiles deep, which holds the bytes in
-//     flight that an HBM-bound kernel needs without spending registers or load instructions on them; scales and
-//     zero-points are prefetched two tiles ahead in registers;
+//     (first slice of the CTA's K range + w) for the whole launch, so the activations it needs are loaded once and
+//     live in registers as mma B fragments (fp16 activations are only permuted, never converted);
+//   * CTAs are persistent: CTA c of a K split walks over the 16-row tiles c, c + P, c + 2P ...  A warp of its own
+//     asks for the data with bulk copies (cp.async.bulk, no tensor map to fetch first): one per weight row and tile
+//     for the CTA's K range, two for the tile's scales and zero-points, all counted on one mbarrier per ring slot.
+//     Rows sit 64 bytes (mod 128) apart in shared memory, which keeps the 16-byte fragment loads free of bank
+//     conflicts.  The ring is as deep as shared memory allows, for small problems deep enough to hold the CTA's
+//     whole share, so that every byte is requested at once; nothing on the critical path is a dependent global load;
 //   * nibbles/bytes become exact fp16 integers with one LOP3/PRMT per pair (the 0x6400 / 0x5400 exponent trick)
 //     and feed mma.sync.m16n8k16 with W as the 16-row operand and up to 8 batch rows as the 8-column operand (the
 //     contraction index is permuted identically on both sides, so nothing is shuffled); accumulation is fp32 and
 //     the group scale multiplies the fp32 sum of each 64-byte unit, i.e. sum((q - zp) * x) * scale;
-//   * the partial sums of the CTA's warps are added in shared memory in a fixed order, once per two tiles; with
-//     split-K each split stores its tile sums into its own workspace slot and the split that arrives last (a
+//   * warps never meet inside a batch of tiles: each keeps its partial sums in shared memory and hands its ring slot
+//     back through an mbarrier.  Once per batch the partial sums of the CTA's warps are added in a fixed order;
+//     with split-K each split stores its tile sums into its own workspace slot and the split that arrives last (a
 //     counter per tile) adds the slots in a fixed order, so results are bitwise repeatable.  Nothing ever waits on
 //     another CTA, and every mbarrier wait is bounded.
 #include <cuda.h>
@@ -36,12 +39,12 @@ namespace
 using namespace nnf::ptx;
 
 constexpr int kMaxWarps = 16;
-constexpr int kBatch = 8;            // row tiles whose results are kept in shared memory between flushes
+constexpr int kBatch = 8;            // most row tiles between two reductions over the warps
 constexpr int kMaxDepth = 8;         // deepest load ring
-constexpr int kTileBytes = 16 * 128; // one warp's weight tile: 16 rows x 128 bytes
 
 struct GemvParams
 {
+    const uint8_t* wq[2];
     const void* scale[2];
     const uint8_t* zp[2];
     const void* x;
@@ -57,8 +60,12 @@ struct GemvParams
     int slices; // ceil(units / 2)
     int row_tiles, splits, ctas_per_split;
     int x_f32, y_f32, scale_f32, rmsnorm, has_bias;
-    int fast_params; // scale / zero-point tensors may be read as aligned 32-bit words
     int depth;       // ring depth in row tiles
+    int batch;       // row tiles between two reductions over the warps (<= kBatch)
+    int tq;          // accumulator column pairs kept: 1, 2 or 4, at least ceil(min(M, 8) / 2); 4 when M > 8
+    int row_bytes;   // bytes of one packed weight row
+    int bulk_params; // scales / zero-points of a tile arrive by bulk copy in shared memory
+    int scale_tile_bytes, zp_tile_bytes, pset_bytes; // per tile and weight set
     float eps;
     int slot_floats;
 };
@@ -71,12 +78,30 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// Same, starting a sum: the addend is zero.
+__device__ __forceinline__ void mma16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1)
+{
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 
-template <uint32_t MASK, uint32_t ORV>
-__device__ __forceinline__ uint32_t and_or(uint32_t w)
+// (w & MASK) | orv.  The OR-ed constant comes in a register that the caller fills once (see held_constant): with
+// two immediates the compiler re-creates one of them in front of every use.
+template <uint32_t MASK>
+__device__ __forceinline__ uint32_t and_or(uint32_t w, uint32_t orv)
 {
     uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "n"(MASK), "n"(ORV)); // (a & b) | c
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w), "n"(MASK), "r"(orv)); // (a & b) | c
+    return r;
+}
+// A constant the compiler cannot see through, so that it stays in its register.
+__device__ __forceinline__ uint32_t held_constant(uint32_t v)
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %1;" : "=r"(r) : "r"(v));
     return r;
 }
 
@@ -92,6 +117,53 @@ __device__ __forceinline__ uint32_t pack_h2(__half a, __half b)
     return (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
 }
 
+// Untiled bulk copy global -> shared: both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void named_barrier(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Compile with -DNNF_TRACE to record, per CTA, the time at which thread 0 and thread 256 pass the marked points.
+#ifdef NNF_TRACE
+__device__ unsigned long long g_nnf_trace[3 * 2048 * 16];
+#define NNF_TRACE_POINT(i)                                                                                         \
+    do                                                                                                             \
+    {                                                                                                              \
+        if ((threadIdx.x == 0 || threadIdx.x == 256) && blockIdx.x < 2048)                                         \
+        {                                                                                                          \
+            unsigned long long t_;                                                                                 \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                 \
+            g_nnf_trace[((threadIdx.x ? 2048 : 0) + blockIdx.x) * 16 + (i)] = t_;                                  \
+        }                                                                                                          \
+    } while (0)
+#define NNF_TRACE_PRODUCER(i)                                                                                      \
+    do                                                                                                             \
+    {                                                                                                              \
+        if ((threadIdx.x & 31) == 0 && blockIdx.x < 2048)                                                          \
+        {                                                                                                          \
+            unsigned long long t_;                                                                                 \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                 \
+            g_nnf_trace[(4096 + blockIdx.x) * 16 + (i)] = t_;                                                      \
+        }                                                                                                          \
+    } while (0)
+__device__ int g_nnf_debug; // ablation switches for timing experiments (only with -DNNF_ABLATE)
+#ifdef NNF_ABLATE
+#define NNF_DEBUG(bit) (g_nnf_debug & (bit))
+#else
+#define NNF_DEBUG(bit) false
+#endif
+#else
+#define NNF_TRACE_POINT(i)
+#define NNF_TRACE_PRODUCER(i)
+#define NNF_DEBUG(bit) false
+#endif
+
 template <int WBITS>
 struct Fmt
 {
@@ -100,22 +172,19 @@ struct Fmt
     static constexpr int NF = LE / 2;                  // half2 fragments per chunk
 };
 
-// Shared-memory footprint, shared by host and device.
-template <int MB, bool DUAL>
-struct Smem
+// Shared-memory footprint, shared by host and device.  All sizes in bytes.
+struct SmemLayout
 {
-    static constexpr int SETS = DUAL ? 2 : 1;
-    static constexpr int TILE_F = SETS * MB * 128; // floats of one tile result: [set][mb][lane][4]
-    static constexpr int MPAD = 8 * MB;
-    __host__ __device__ static size_t ring_bytes(int warps, int depth)
+    size_t ring, pring, bars, red, ss, flags, total;
+    __host__ __device__ SmemLayout(int sets, int mb, int warps, int depth, int batch, int tq, int pset_bytes)
     {
-        return (size_t)depth * SETS * warps * kTileBytes;
-    }
-    __host__ __device__ static size_t total_bytes(int warps, int depth)
-    {
-        return 1024 /* alignment slack */ + ring_bytes(warps, depth) + 8 * kMaxDepth +
-               sizeof(float) * ((size_t)2 * warps * 2 * TILE_F + kBatch * TILE_F + warps * MPAD + MPAD) +
-               sizeof(int) * kBatch;
+        ring = (size_t)depth * sets * 16 * (warps * 128 + 64);
+        pring = (size_t)depth * sets * pset_bytes;
+        bars = 8 * 2 * kMaxDepth;
+        red = sizeof(float) * (size_t)warps * batch * sets * mb * 8 * tq * 4;
+        ss = sizeof(float) * ((size_t)warps * 8 * mb + 8 * mb);
+        flags = sizeof(int) * kBatch;
+        total = ring + pring + bars + red + ss + flags;
     }
 };
 
@@ -125,36 +194,42 @@ struct Smem
 //                fp32 sum afterwards, acc - (C1 + zp * C2), with C1 = sum(offset_k * x_k), C2 = sum(x_k) over the
 //                64-byte unit.  Same fp32 accumulation, about 40 % fewer unpack instructions.
 template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT>
-__global__ void __launch_bounds__(kMaxWarps * 32, 1)
-    dq_gemv_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap0,
-                   const __grid_constant__ CUtensorMap tmap1)
+__global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
+    dq_gemv_kernel(const GemvParams p)
 {
     using F = Fmt<WBITS>;
-    using S = Smem<MB, DUAL>;
-    constexpr int SETS = S::SETS;
+    constexpr int SETS = DUAL ? 2 : 1;
     constexpr int XS = XSPLIT ? 2 : 1;
     constexpr int NF = F::NF;
-    constexpr int TILE_F = S::TILE_F;
-    constexpr int MPAD = S::MPAD;
+    constexpr int MPAD = 8 * MB;
 
-    extern __shared__ uint8_t smem_raw[];
-    const int nthreads = blockDim.x;
-    const int nwarps = nthreads >> 5;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const int nwarps = (blockDim.x >> 5) - 1; // arithmetic warps; the last warp of the CTA only asks for data
+    const int nthreads = nwarps * 32;
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int tq = p.tq;
+    const int tq_shift = tq >> 1;                        // tq is 1, 2 or 4
+    const int pt_shift = 5 + tq_shift + (MB == 2 ? 1 : 0);
+    const int per_tile = 1 << pt_shift; // MB * 8 * tq * 4 floats: one warp's partial sums of one tile and weight set
+    NNF_TRACE_POINT(0);
 
-    // ring (1024-byte aligned: the TMA 128-byte swizzle is a function of the shared-memory address):
-    //   [depth][SETS][nwarps] tiles of 16 rows x 128 bytes
-    uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + S::ring_bytes(nwarps, p.depth)); // [kMaxDepth]
-    float* red = reinterpret_cast<float*>(full_bar + kMaxDepth);                             // [2][nwarps][2*TILE_F]
-    float* res = red + 2 * nwarps * 2 * TILE_F;                                              // [kBatch][TILE_F]
-    float* ss_w = res + kBatch * TILE_F;                                                     // [nwarps][MPAD]
-    float* ss_cta = ss_w + nwarps * MPAD;                                                    // [MPAD]
-    int* last_flag = reinterpret_cast<int*>(ss_cta + MPAD);                                  // [kBatch]
-    const uint32_t ring_s = smem_u32(ring);
-    const uint32_t bar_s = smem_u32(full_bar);
+    // ring: [depth][SETS][16 rows] of (nwarps * 128 + 64) bytes, warp w's 128 bytes of a row at w * 128; then per
+    // slot and set the tile's scales and zero-points
+    const SmemLayout lay(SETS, MB, nwarps, p.depth, p.batch, tq, p.pset_bytes);
+    // (pointers stay derived from the array itself, never from an integer, so that every access below is compiled
+    // as a shared-memory access with a 32-bit address rather than as a generic one)
+    uint8_t* ring = smem_raw;
+    uint8_t* pring = ring + lay.ring;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(pring + lay.pring); // full[kMaxDepth], empty[kMaxDepth]
+    float* red = reinterpret_cast<float*>(bars + 2 * kMaxDepth);     // [nwarps][batch][SETS][per_tile]
+    float* ss_w = red + lay.red / sizeof(float);                     // [nwarps][MPAD]
+    float* ss_cta = ss_w + nwarps * MPAD;                            // [MPAD]
+    int* last_flag = reinterpret_cast<int*>(ss_cta + MPAD);          // [kBatch]
+    const uint32_t ring_s = smem_u32(ring), pring_s = smem_u32(pring);
+    const int row_stride = nwarps * 128 + 64; // shared-memory bytes between two rows of a tile
+    const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * kMaxDepth;
 
     const int split = blockIdx.x / p.ctas_per_split;
     const int cta_in_split = blockIdx.x - split * p.ctas_per_split;
@@ -167,34 +242,81 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                            ? (p.row_tiles - cta_in_split + p.ctas_per_split - 1) / p.ctas_per_split
                            : 0;
 
-    // ---------------------------------------------------------------- TMA producer (thread 0)
-    // One 16-row x 128-byte box per (weight set, slice) and row tile, all counted on the slot's barrier.
-    auto produce = [&](int step) {
-        if (step < nsteps)
+    // ---------------------------------------------------------------- producer (last warp of the CTA)
+    // Per row tile: for every row that exists the CTA's K range of the packed weights, and the tile's quantisation
+    // parameters, all counted on the slot's barrier.  expect() is called by one lane, copy() by the whole warp.
+    const int seg_bytes = min(my_slices * 128, p.row_bytes - slice0 * 128);
+    auto tile_rows = [&](int step) { return min(16, p.N - (cta_in_split + step * p.ctas_per_split) * 16); };
+    auto expect = [&](int step) {
+        uint32_t bytes = (uint32_t)(SETS * tile_rows(step) * seg_bytes);
+        if (p.bulk_params)
+            bytes += (uint32_t)(SETS * (p.scale_tile_bytes + p.zp_tile_bytes));
+        mbar_arrive_expect_tx(full_s + 8 * (step % p.depth), bytes);
+    };
+    auto copy = [&](int step) {
+        const int slot = step % p.depth;
+        const uint32_t bar = full_s + 8 * slot;
+        const int tile = cta_in_split + step * p.ctas_per_split;
+        const int rows = tile_rows(step);
+        for (int c = lane; c < SETS * 16; c += 32)
         {
-            const int slot = step % p.depth;
-            const uint32_t bar = bar_s + 8 * slot;
-            const int row0 = (cta_in_split + step * p.ctas_per_split) * 16;
-            mbar_arrive_expect_tx(bar, (uint32_t)(SETS * my_slices * kTileBytes));
-            for (int w = 0; w < my_slices; w++)
-            {
-                tma_load_2d(ring_s + (uint32_t)(((slot * SETS + 0) * nwarps + w) * kTileBytes), &tmap0, bar,
-                            (slice0 + w) * 128, row0);
-                if (DUAL)
-                    tma_load_2d(ring_s + (uint32_t)(((slot * SETS + 1) * nwarps + w) * kTileBytes), &tmap1, bar,
-                                (slice0 + w) * 128, row0);
-            }
+            const int s = c >> 4, r = c & 15;
+            if (r < rows)
+                bulk_load(ring_s + (uint32_t)(((slot * SETS + s) * 16 + r) * row_stride),
+                          p.wq[s] + (size_t)(tile * 16 + r) * p.row_bytes + (size_t)slice0 * 128, (uint32_t)seg_bytes,
+                          bar);
+        }
+        if (p.bulk_params && lane >= 32 - 2 * SETS)
+        {
+            const int c = lane - (32 - 2 * SETS), s = c >> 1;
+            const uint32_t pd = pring_s + (uint32_t)((slot * SETS + s) * p.pset_bytes);
+            if (c & 1)
+                bulk_load(pd + (uint32_t)p.scale_tile_bytes, p.zp[s] + (size_t)tile * p.zp_tile_bytes,
+                          (uint32_t)p.zp_tile_bytes, bar);
+            else
+                bulk_load(pd, static_cast<const char*>(p.scale[s]) + (size_t)tile * p.scale_tile_bytes,
+                          (uint32_t)p.scale_tile_bytes, bar);
         }
     };
-    if (tid == 0)
+    if (warp == nwarps)
     {
-        for (int i = 0; i < p.depth; i++)
-            mbar_init(bar_s + 8 * i, 1);
-        fence_barrier_init();
-        // Weights do not depend on the activations: start streaming before anybody touches x.  (The arrive on
-        // the barrier waits for this thread's earlier loads, so nothing is loaded ahead of it.)
-        for (int i = 0; i < p.depth; i++)
-            produce(i);
+        // A warp of its own: asking for data never waits for anybody's activation loads, and the arithmetic warps
+        // never wait for the requests to be issued.  The first ring-full leaves at once; slots are then refilled
+        // as the arithmetic warps hand them back.
+        NNF_TRACE_PRODUCER(0);
+        if (lane == 0)
+        {
+            for (int i = 0; i < p.depth; i++)
+            {
+                mbar_init(full_s + 8 * i, 1);
+                mbar_init(empty_s + 8 * i, (uint32_t)nwarps);
+            }
+            fence_barrier_init();
+            for (int i = 0; i < p.depth && i < nsteps; i++)
+                expect(i);
+        }
+        NNF_TRACE_PRODUCER(1);
+        __syncwarp();
+        asm volatile("bar.arrive 2, %0;" ::"r"(nthreads + 32) : "memory"); // barriers are ready
+        NNF_TRACE_PRODUCER(2);
+        for (int i = 0; i < p.depth && i < nsteps; i++)
+            copy(i);
+        NNF_TRACE_PRODUCER(3);
+        bool gave_up = false;
+        for (int st = p.depth; st < nsteps; st++)
+        {
+            if (lane == 0)
+            {
+                if (!mbar_wait(empty_s + 8 * (st % p.depth), (uint32_t)(st / p.depth - 1) & 1u))
+                    gave_up = true;
+                expect(st);
+            }
+            __syncwarp();
+            copy(st);
+        }
+        if (gave_up)
+            atomicExch(p.status, 1);
+        return;
     }
 
     int unit_of[2], grp_of[2];
@@ -209,46 +331,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
         unit_of[l] = u;
         grp_of[l] = (u * F::UE) / p.group;
     }
-    // Can the (scale, zero-point) of both halves of the slice be taken from one aligned 32-bit word per row?
-    bool fast = p.fast_params != 0;
-    {
-        const int g0 = grp_of[0], g1 = grp_of[1];
-        const bool same = g1 == g0, pair = (g1 == g0 + 1) && !(g0 & 1);
-        const bool sc_ok = p.scale_f32 ? same : (same || (pair && !(p.G & 1)));
-        const bool zp_ok = (WBITS == 4) ? (same || pair) : (same || (pair && !(p.G & 3)));
-        fast = fast && sc_ok && zp_ok;
-    }
-
-    // ---------------------------------------------------------------- quantisation parameters of one row tile
-    struct PReg
-    {
-        uint32_t sw[SETS][2]; // word holding the scale(s) of row g / g+8
-        uint32_t zw[SETS][2]; // word holding the zero-point(s)
-    };
-    auto row_of = [&](int step, int h) { return min((cta_in_split + step * p.ctas_per_split) * 16 + g + 8 * h, p.N - 1); };
-    auto load_params = [&](PReg& r, int step) {
-        if (fast && has_slice && step < nsteps)
+    // Byte offsets of this lane's scales / zero-points inside a slot's parameter block: rows g and g + 8 of the
+    // tile, groups of the two units of the slice.
+    const int sbytes = p.scale_f32 ? 4 : 2;
+    int soff[2][2], zoff[2][2];
+#pragma unroll
+    for (int l = 0; l < 2; l++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
         {
-#pragma unroll
-            for (int h = 0; h < 2; h++)
-            {
-                const int row = row_of(step, h);
-                const size_t sidx = (size_t)row * p.G + grp_of[0];
-                const size_t zoff = (WBITS == 4) ? (size_t)row * p.zp_row_bytes + (grp_of[0] >> 1) : sidx;
-#pragma unroll
-                for (int s = 0; s < SETS; s++)
-                {
-                    const char* sp = static_cast<const char*>(p.scale[s]);
-                    r.sw[s][h] = __ldg(reinterpret_cast<const uint32_t*>(
-                        p.scale_f32 ? sp + sidx * 4 : sp + ((sidx * 2) & ~(size_t)3)));
-                    r.zw[s][h] = __ldg(reinterpret_cast<const uint32_t*>(p.zp[s] + (zoff & ~(size_t)3)));
-                }
-            }
+            soff[l][h] = ((g + 8 * h) * p.G + grp_of[l]) * sbytes;
+            zoff[l][h] = p.scale_tile_bytes + (g + 8 * h) * p.zp_row_bytes + (WBITS == 4 ? grp_of[l] >> 1 : grp_of[l]);
         }
-    };
-    PReg pr[3]; // tiles step, step + 1, step + 2
-    load_params(pr[0], 0);
-    load_params(pr[1], 1);
 
     // ---------------------------------------------------------------- activations -> B fragments in registers
     uint32_t xf[2][MB][XS][NF];
@@ -257,6 +351,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
 #pragma unroll
     for (int mb = 0; mb < MB; mb++)
         ss_local[mb] = 0.f;
+    const bool plain = !XSPLIT && !p.x_f32 && !p.rmsnorm; // fp16 activations used as they are
 #pragma unroll
     for (int l = 0; l < 2; l++)
     {
@@ -265,99 +360,122 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
         for (int mb = 0; mb < MB; mb++)
         {
             const int m = g + 8 * mb;
-            float xv[F::LE];
-            if (unit_ok[l] && m < p.M)
+            const bool live = unit_ok[l] && m < p.M;
+            if (plain)
             {
-                if (p.x_f32)
-                {
-                    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) +
-                                                                       (size_t)m * p.K + k0);
+                // Element order inside a fragment mirrors the order the weight unpacking produces:
+                // uint4 word i yields pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7); uint8 word i yields (b0,b1) (b2,b3).
+                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __half*>(p.x) +
+                                                                 (size_t)m * p.K + k0);
 #pragma unroll
-                    for (int j = 0; j < F::LE / 4; j++)
+                for (int j = 0; j < F::LE / 8; j++)
+                {
+                    const uint4 v = live ? __ldg(src + j) : make_uint4(0u, 0u, 0u, 0u);
+                    if (WBITS == 4)
                     {
-                        float4 v = __ldg(src + j);
-                        xv[4 * j + 0] = v.x, xv[4 * j + 1] = v.y, xv[4 * j + 2] = v.z, xv[4 * j + 3] = v.w;
+                        xf[l][mb][0][4 * j + 0] = __byte_perm(v.x, v.z, 0x5410);
+                        xf[l][mb][0][4 * j + 1] = __byte_perm(v.x, v.z, 0x7632);
+                        xf[l][mb][0][4 * j + 2] = __byte_perm(v.y, v.w, 0x5410);
+                        xf[l][mb][0][4 * j + 3] = __byte_perm(v.y, v.w, 0x7632);
                     }
-                }
-                else
-                {
-                    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __half*>(p.x) +
-                                                                     (size_t)m * p.K + k0);
-#pragma unroll
-                    for (int j = 0; j < F::LE / 8; j++)
+                    else
                     {
-                        uint4 v = __ldg(src + j);
-                        const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-                        for (int q = 0; q < 4; q++)
-                        {
-                            float2 f = __half22float2(h[q]);
-                            xv[8 * j + 2 * q] = f.x, xv[8 * j + 2 * q + 1] = f.y;
-                        }
-                    }
-                }
-                if (p.rmsnorm)
-                {
-                    const float4* gsrc = reinterpret_cast<const float4*>(p.gain + k0);
-#pragma unroll
-                    for (int j = 0; j < F::LE / 4; j++)
-                    {
-                        float4 gv = __ldg(gsrc + j);
-                        float* e = xv + 4 * j;
-                        ss_local[mb] += e[0] * e[0] + e[1] * e[1] + e[2] * e[2] + e[3] * e[3];
-                        e[0] *= gv.x, e[1] *= gv.y, e[2] *= gv.z, e[3] *= gv.w;
+                        xf[l][mb][0][4 * j + 0] = v.x, xf[l][mb][0][4 * j + 1] = v.y;
+                        xf[l][mb][0][4 * j + 2] = v.z, xf[l][mb][0][4 * j + 3] = v.w;
                     }
                 }
             }
             else
             {
+                float xv[F::LE];
+                if (live)
+                {
+                    if (p.x_f32)
+                    {
+                        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.x) +
+                                                                           (size_t)m * p.K + k0);
+#pragma unroll
+                        for (int j = 0; j < F::LE / 4; j++)
+                        {
+                            float4 v = __ldg(src + j);
+                            xv[4 * j + 0] = v.x, xv[4 * j + 1] = v.y, xv[4 * j + 2] = v.z, xv[4 * j + 3] = v.w;
+                        }
+                    }
+                    else
+                    {
+                        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __half*>(p.x) +
+                                                                         (size_t)m * p.K + k0);
+#pragma unroll
+                        for (int j = 0; j < F::LE / 8; j++)
+                        {
+                            uint4 v = __ldg(src + j);
+                            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                            for (int q = 0; q < 4; q++)
+                            {
+                                float2 f = __half22float2(h[q]);
+                                xv[8 * j + 2 * q] = f.x, xv[8 * j + 2 * q + 1] = f.y;
+                            }
+                        }
+                    }
+                    if (p.rmsnorm)
+                    {
+                        const float4* gsrc = reinterpret_cast<const float4*>(p.gain + k0);
+#pragma unroll
+                        for (int j = 0; j < F::LE / 4; j++)
+                        {
+                            float4 gv = __ldg(gsrc + j);
+                            float* e = xv + 4 * j;
+                            ss_local[mb] += e[0] * e[0] + e[1] * e[1] + e[2] * e[2] + e[3] * e[3];
+                            e[0] *= gv.x, e[1] *= gv.y, e[2] *= gv.z, e[3] *= gv.w;
+                        }
+                    }
+                }
+                else
+                {
+#pragma unroll
+                    for (int j = 0; j < F::LE; j++)
+                        xv[j] = 0.f;
+                }
+                __half hi[F::LE], lo[F::LE];
 #pragma unroll
                 for (int j = 0; j < F::LE; j++)
-                    xv[j] = 0.f;
-            }
-            __half hi[F::LE], lo[F::LE];
-            float se = 0.f, so = 0.f; // sums of what the tensor core will see, even / odd element positions
-#pragma unroll
-            for (int j = 0; j < F::LE; j++)
-            {
-                hi[j] = __float2half_rn(xv[j]);
-                float seen = __half2float(hi[j]);
-                if (XSPLIT)
                 {
-                    lo[j] = __float2half_rn(xv[j] - seen);
-                    seen += __half2float(lo[j]);
+                    hi[j] = __float2half_rn(xv[j]);
+                    if (XSPLIT)
+                        lo[j] = __float2half_rn(xv[j] - __half2float(hi[j]));
                 }
-                if (j & 1)
-                    so += seen;
-                else
-                    se += seen;
-            }
 #pragma unroll
-            for (int f = 0; f < NF; f++)
-            {
-                // Element order inside a fragment mirrors the order the weight unpacking produces:
-                // uint4 word i yields pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7); uint8 word i yields (b0,b1) (b2,b3).
-                const int e0 = (WBITS == 4) ? 8 * (f >> 2) + (f & 3) : 2 * f;
-                const int e1 = (WBITS == 4) ? e0 + 4 : e0 + 1;
-                xf[l][mb][0][f] = pack_h2(hi[e0], hi[e1]);
-                if (XSPLIT)
-                    xf[l][mb][XS - 1][f] = pack_h2(lo[e0], lo[e1]);
+                for (int f = 0; f < NF; f++)
+                {
+                    const int e0 = (WBITS == 4) ? 8 * (f >> 2) + (f & 3) : 2 * f;
+                    const int e1 = (WBITS == 4) ? e0 + 4 : e0 + 1;
+                    xf[l][mb][0][f] = pack_h2(hi[e0], hi[e1]);
+                    if (XSPLIT)
+                        xf[l][mb][XS - 1][f] = pack_h2(lo[e0], lo[e1]);
+                }
             }
             if (!EXACT)
             {
-                // uint4: even positions carry offset 1024 (bits 0-3 of a half), odd positions 64 (bits 4-7);
-                // uint8: every position carries 1024.
-                float a1 = (WBITS == 4) ? 1024.f * se + 64.f * so : 1024.f * (se + so);
-                float a2 = se + so;
-                a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
-                a2 += __shfl_xor_sync(0xffffffffu, a2, 1);
-                a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
-                a2 += __shfl_xor_sync(0xffffffffu, a2, 2);
-                // every lane of quad g now holds the unit sums of batch row g; fetch those of rows 2t, 2t+1
-                c1[l][mb][0] = __shfl_sync(0xffffffffu, a1, (2 * t) * 4);
-                c1[l][mb][1] = __shfl_sync(0xffffffffu, a1, (2 * t + 1) * 4);
-                c2[l][mb][0] = __shfl_sync(0xffffffffu, a2, (2 * t) * 4);
-                c2[l][mb][1] = __shfl_sync(0xffffffffu, a2, (2 * t + 1) * 4);
+                // C1 and C2 of the unit for every batch row, summed by the tensor core exactly as it will sum the
+                // products: rows 0-7 of the left operand hold the offsets the unpacking leaves in place (uint4:
+                // 1024 on even fragments, 64 on odd ones; uint8: 1024), rows 8-15 hold ones.  Every lane ends up
+                // with the sums of accumulator columns 2t and 2t+1.
+                constexpr uint32_t off_even = 0x64006400u, off_odd = (WBITS == 4) ? 0x54005400u : 0x64006400u;
+                constexpr uint32_t ones = 0x3C003C00u;
+                float d[4];
+#pragma unroll
+                for (int f = 0; f < NF; f += 2)
+#pragma unroll
+                    for (int xsn = 0; xsn < XS; xsn++)
+                    {
+                        if (f == 0 && xsn == 0)
+                            mma16816_first(d, off_even, ones, off_odd, ones, xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
+                        else
+                            mma16816(d, off_even, ones, off_odd, ones, xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
+                    }
+                c1[l][mb][0] = d[0], c1[l][mb][1] = d[1];
+                c2[l][mb][0] = d[2], c2[l][mb][1] = d[3];
             }
         }
     }
@@ -376,7 +494,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 ss_w[warp * MPAD + g + 8 * mb] = v;
         }
     }
-    __syncthreads(); // barrier initialisation and ss_w visible to everybody
+    NNF_TRACE_POINT(2);
+    asm volatile("bar.sync 2, %0;" ::"r"(nthreads + 32) : "memory"); // ring barriers initialised, ss_w visible
+    NNF_TRACE_POINT(3);
     if (p.rmsnorm)
     {
         if (tid < MPAD)
@@ -386,42 +506,41 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 v += ss_w[w * MPAD + tid];
             ss_cta[tid] = v;
         }
-        __syncthreads();
+        named_barrier(1, nthreads);
     }
 
     // ---------------------------------------------------------------- arithmetic on one landed row tile
+    auto row_of = [&](int step, int h) { return min((cta_in_split + step * p.ctas_per_split) * 16 + g + 8 * h, p.N - 1); };
     float tot[SETS][MB][4];
-    auto compute = [&](int step, int slot, const PReg& prm) {
+    const uint32_t k6400 = held_constant(0x64006400u), k5400 = held_constant(0x54005400u);
+    auto compute = [&](int step, int slot) {
 #pragma unroll
         for (int s = 0; s < SETS; s++)
         {
             // (scale, zero-point) of rows g / g+8 for both halves of the slice
             float sc[2][2];
             uint32_t zq[2][2];
-            if (fast)
+            if (NNF_DEBUG(8))
             {
 #pragma unroll
-                for (int h = 0; h < 2; h++)
-                {
-                    const int row = row_of(step, h);
-                    const uint32_t sidx_lo = (uint32_t)row * (uint32_t)p.G + (uint32_t)grp_of[0];
-                    const uint32_t zoff_lo =
-                        (WBITS == 4) ? (uint32_t)row * (uint32_t)p.zp_row_bytes + (uint32_t)(grp_of[0] >> 1) : sidx_lo;
+                for (int l = 0; l < 2; l++)
 #pragma unroll
-                    for (int l = 0; l < 2; l++)
+                    for (int h = 0; h < 2; h++)
+                        sc[l][h] = 1.f, zq[l][h] = 0;
+            }
+            else if (p.bulk_params)
+            {
+                const uint8_t* pb = pring + (size_t)(slot * SETS + s) * p.pset_bytes;
+#pragma unroll
+                for (int l = 0; l < 2; l++)
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
                     {
-                        const int dg = grp_of[l] - grp_of[0];
-                        if (p.scale_f32)
-                            sc[l][h] = __uint_as_float(prm.sw[s][h]);
-                        else
-                            sc[l][h] = __half2float(
-                                __ushort_as_half((unsigned short)(prm.sw[s][h] >> (16 * ((sidx_lo + dg) & 1)))));
-                        if (WBITS == 4)
-                            zq[l][h] = (prm.zw[s][h] >> (8 * (zoff_lo & 3) + 4 * (grp_of[l] & 1))) & 0xF;
-                        else
-                            zq[l][h] = (prm.zw[s][h] >> (8 * ((zoff_lo + dg) & 3))) & 0xFF;
+                        sc[l][h] = p.scale_f32 ? *reinterpret_cast<const float*>(pb + soff[l][h])
+                                               : __half2float(*reinterpret_cast<const __half*>(pb + soff[l][h]));
+                        const uint32_t zb = pb[zoff[l][h]];
+                        zq[l][h] = (WBITS == 4) ? (zb >> (4 * (grp_of[l] & 1))) & 0xF : zb;
                     }
-                }
             }
             else
             {
@@ -444,15 +563,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                     }
                 }
             }
-            // this warp's tile: row r at r*128, 16-byte chunk c stored at chunk (c ^ (r & 7))
-            const uint8_t* wt = ring + (size_t)((slot * SETS + s) * nwarps + warp) * kTileBytes;
+            // this warp's 128 bytes of row r of the tile
+            const uint8_t* wt = ring + (size_t)((slot * SETS + s) * 16) * row_stride + warp * 128;
             uint32_t wq[2][2][4]; // [unit][row half][word]
 #pragma unroll
             for (int l = 0; l < 2; l++)
 #pragma unroll
                 for (int h = 0; h < 2; h++)
                 {
-                    const uint4 v = *reinterpret_cast<const uint4*>(wt + (g + 8 * h) * 128 + ((4 * l + t) ^ g) * 16);
+                    const uint4 v = *reinterpret_cast<const uint4*>(wt + (g + 8 * h) * row_stride + (4 * l + t) * 16);
                     wq[l][h][0] = v.x, wq[l][h][1] = v.y, wq[l][h][2] = v.z, wq[l][h][3] = v.w;
                 }
             uint32_t zA[2][2], zB[2][2]; // fp16x2 constants holding (offset + zero-point)
@@ -470,15 +589,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
             // four independent accumulation chains: (unit, word parity)
             float acc[2][2][MB][4];
 #pragma unroll
-            for (int l = 0; l < 2; l++)
-#pragma unroll
-                for (int e = 0; e < 2; e++)
-#pragma unroll
-                    for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-                        for (int c = 0; c < 4; c++)
-                            acc[l][e][mb][c] = 0.f;
-#pragma unroll
             for (int w4 = 0; w4 < 4; w4++)
 #pragma unroll
                 for (int l = 0; l < 2; l++)
@@ -488,13 +598,17 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                     for (int h = 0; h < 2; h++)
                     {
                         const uint32_t w = wq[l][h][w4];
-                        if (WBITS == 4)
+                        if (NNF_DEBUG(2))
+                        {
+                            a[h][0] = a[h][1] = a[h][2] = a[h][3] = w;
+                        }
+                        else if (WBITS == 4)
                         {
                             const uint32_t w8 = w >> 8;
-                            a[h][0] = and_or<0x000F000Fu, 0x64006400u>(w);  // 1024 + (n0, n4)
-                            a[h][1] = and_or<0x00F000F0u, 0x54005400u>(w);  //   64 + (n1, n5)
-                            a[h][2] = and_or<0x000F000Fu, 0x64006400u>(w8); // 1024 + (n2, n6)
-                            a[h][3] = and_or<0x00F000F0u, 0x54005400u>(w8); //   64 + (n3, n7)
+                            a[h][0] = and_or<0x000F000Fu>(w, k6400);  // 1024 + (n0, n4)
+                            a[h][1] = and_or<0x00F000F0u>(w, k5400);  //   64 + (n1, n5)
+                            a[h][2] = and_or<0x000F000Fu>(w8, k6400); // 1024 + (n2, n6)
+                            a[h][3] = and_or<0x00F000F0u>(w8, k5400); //   64 + (n3, n7)
                             if (EXACT)
                             {
                                 a[h][0] = hsub2_u32(a[h][0], zA[l][h]);
@@ -523,8 +637,22 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                         for (int mb = 0; mb < MB; mb++)
 #pragma unroll
                             for (int xsn = 0; xsn < XS; xsn++)
-                                mma16816(acc[l][w4 & 1][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
-                                         xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
+                            {
+                                if (NNF_DEBUG(1))
+                                {
+                                    const float z = __uint_as_float((a[0][q] ^ a[1][q] ^ a[0][q + 1] ^ a[1][q + 1]) & 0x3FFFFFFFu);
+                                    if (w4 < 2 && q == 0 && xsn == 0)
+                                        acc[l][w4 & 1][mb][0] = acc[l][w4 & 1][mb][1] = acc[l][w4 & 1][mb][2] = acc[l][w4 & 1][mb][3] = z;
+                                    else
+                                        acc[l][w4 & 1][mb][q] += z;
+                                }
+                                else if (w4 < 2 && q == 0 && xsn == 0) // first product of this chain
+                                    mma16816_first(acc[l][w4 & 1][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
+                                                   xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
+                                else
+                                    mma16816(acc[l][w4 & 1][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
+                                             xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
+                            }
                     }
                 }
 #pragma unroll
@@ -533,6 +661,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 for (int c = 0; c < 4; c++)
                 {
                     float v = 0.f;
+                    if (NNF_DEBUG(4))
+                    {
+                        tot[s][mb][c] = acc[0][0][mb][c] + acc[0][1][mb][c] + acc[1][0][mb][c] + acc[1][1][mb][c];
+                        continue;
+                    }
 #pragma unroll
                     for (int l = 0; l < 2; l++)
                     {
@@ -568,43 +701,67 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
         else
             static_cast<__half*>(p.y)[(size_t)m * p.N + n] = __float2half_rn(v);
     };
-    // Index o in [0, MB*128) of a tile result <-> (row in tile, batch row m).
-    auto decode = [&](int o, int& row, int& m) {
-        const int mb = o >> 7, ln = (o >> 2) & 31, c = o & 3;
-        row = (ln >> 2) + 8 * (c >> 1);
-        m = 8 * mb + 2 * (ln & 3) + (c & 1);
+    // Index e in [0, per_tile) of a warp's partial sums = ((mb * 8 + g) * tq + t) * 4 + c  <->  row of the tile,
+    // batch row m, and the index o of the same value in a workspace slot ([mb][lane][c], all 32 lanes).
+    auto decode = [&](int e, int& row, int& m, int& o) {
+        const int c = e & 3, r1 = e >> 2;
+        const int tt = r1 & (tq - 1), r2 = r1 >> tq_shift;
+        const int gg = r2 & 7, mb = r2 >> 3;
+        row = gg + 8 * (c >> 1);
+        m = 8 * mb + 2 * tt + (c & 1);
+        o = ((mb * 32 + gg * 4 + tt) << 2) + c;
+    };
+    const int warp_stride = p.batch * SETS * per_tile; // floats between two warps' partial sums
+    auto sum_warps = [&](int j, int s, int e) -> float {
+        const float* r = red + (j * SETS + s) * per_tile + e;
+        float v = 0.f;
+        for (int w = 0; w < nwarps; w++)
+            v += r[w * warp_stride];
+        return v;
     };
 
-    // Flush the tile results held in shared memory for steps [first, first + count).
+    // Add up the warps' partial sums of tiles [first, first + count) and write the results out.
     auto flush = [&](int first, int count) {
-        __syncthreads();
+        named_barrier(1, nthreads);
         if (p.splits == 1)
         {
-            for (int idx = tid; idx < count * MB * 128; idx += nthreads)
+            for (int idx = tid; idx < count * per_tile; idx += nthreads)
             {
-                const int j = idx / (MB * 128), o = idx - j * (MB * 128);
-                int row, m;
-                decode(o, row, m);
+                const int j = idx >> pt_shift, e = idx & (per_tile - 1);
+                int row, m, o;
+                decode(e, row, m, o);
                 const int n = (cta_in_split + (first + j) * p.ctas_per_split) * 16 + row;
                 if (m < p.M && n < p.N)
-                {
-                    const float* r = res + j * TILE_F;
-                    store_y(m, n, finish(r[o], DUAL ? r[MB * 128 + o] : 0.f, p.rmsnorm ? ss_cta[m] : 0.f, n));
-                }
+                    store_y(m, n, finish(sum_warps(j, 0, e), DUAL ? sum_warps(j, 1, e) : 0.f,
+                                         p.rmsnorm ? ss_cta[m] : 0.f, n));
             }
         }
         else
         {
-            // 1. publish this split's partial sums (and its share of the sum of squares)
-            for (int idx = tid; idx < count * p.slot_floats; idx += nthreads)
+            // 1. publish this split's sums (and its share of the sum of squares)
+            for (int idx = tid; idx < count * per_tile; idx += nthreads)
             {
-                const int j = idx / p.slot_floats, o = idx - j * p.slot_floats;
+                const int j = idx >> pt_shift, e = idx & (per_tile - 1);
+                int row, m, o;
+                decode(e, row, m, o);
+                if (m >= p.M)
+                    continue;
                 const int rt = cta_in_split + (first + j) * p.ctas_per_split;
-                const float v = (o < TILE_F) ? res[j * TILE_F + o] : (p.rmsnorm ? ss_cta[o - TILE_F] : 0.f);
-                __stcg(p.ws_slots + ((size_t)split * p.row_tiles + rt) * p.slot_floats + o, v);
+                float* slot = p.ws_slots + ((size_t)split * p.row_tiles + rt) * p.slot_floats;
+                __stcg(slot + o, sum_warps(j, 0, e));
+                if (DUAL)
+                    __stcg(slot + MB * 128 + o, sum_warps(j, 1, e));
             }
+            if (p.rmsnorm)
+                for (int idx = tid; idx < count * MPAD; idx += nthreads)
+                {
+                    const int j = idx / MPAD, mm = idx - j * MPAD;
+                    const int rt = cta_in_split + (first + j) * p.ctas_per_split;
+                    __stcg(p.ws_slots + ((size_t)split * p.row_tiles + rt) * p.slot_floats + SETS * MB * 128 + mm,
+                           ss_cta[mm]);
+                }
             __threadfence();
-            __syncthreads();
+            named_barrier(1, nthreads);
             // 2. one arrival per tile; the last split to arrive owns the tile's final sum
             if (tid < count)
             {
@@ -614,16 +771,16 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 if (last_flag[tid])
                     p.ws_count[rt] = 0u; // leave the counter zeroed for the next call
             }
-            __syncthreads();
+            named_barrier(1, nthreads);
             __threadfence();
             // 3. fixed-order sum over the splits
-            for (int idx = tid; idx < count * MB * 128; idx += nthreads)
+            for (int idx = tid; idx < count * per_tile; idx += nthreads)
             {
-                const int j = idx / (MB * 128), o = idx - j * (MB * 128);
+                const int j = idx >> pt_shift, e = idx & (per_tile - 1);
                 if (!last_flag[j])
                     continue;
-                int row, m;
-                decode(o, row, m);
+                int row, m, o;
+                decode(e, row, m, o);
                 const int rt = cta_in_split + (first + j) * p.ctas_per_split;
                 const int n = rt * 16 + row;
                 if (m < p.M && n < p.N)
@@ -636,79 +793,64 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                         if (DUAL)
                             a1 += __ldcg(slot + MB * 128 + o);
                         if (p.rmsnorm)
-                            ssum += __ldcg(slot + TILE_F + m);
+                            ssum += __ldcg(slot + SETS * MB * 128 + m);
                     }
                     store_y(m, n, finish(a0, a1, ssum, n));
                 }
             }
         }
-        __syncthreads();
+        named_barrier(1, nthreads);
     };
 
-    // ---------------------------------------------------------------- main loop: two row tiles per barrier
+    // ---------------------------------------------------------------- main loop
+    // Inside a batch the warps only meet through the ring's barriers: full (bytes have landed) and empty (every warp
+    // has taken what it needs from the slot, so the producer may ask for the tile that lands there next).
     int slot = 0;
     uint32_t parity = 0;
     bool timed_out = false;
-    for (int step = 0; step < nsteps; step += 6)
+    for (int first = 0; first < nsteps; first += p.batch)
     {
-        // unrolled by 6 = lcm(2 tiles per barrier, 3 parameter registers) so that every register index is static
-#pragma unroll
-        for (int pair = 0; pair < 3; pair++)
+        const int count = min(p.batch, nsteps - first);
+        for (int j = 0; j < count; j++)
         {
-            const int st = step + 2 * pair;
-            if (st < nsteps)
+            const int st = first + j;
+            if (!mbar_wait(full_s + 8 * slot, parity))
+                timed_out = true;
+            if (st < 5)
+                NNF_TRACE_POINT(4 + 2 * st);
+            float4* my = reinterpret_cast<float4*>(red + warp * warp_stride + j * SETS * per_tile);
+            if (has_slice)
+                compute(st, slot);
+            else
             {
-                const int pair_n = min(2, nsteps - st);
-                float* my = red + (((st >> 1) & 1) * nwarps + warp) * 2 * TILE_F;
 #pragma unroll
-                for (int j = 0; j < 2; j++)
-                {
-                    if (j < pair_n)
-                    {
-                        constexpr int kRegs = 3;
-                        const int ri = (2 * pair + j) % kRegs;
-                        load_params(pr[(ri + 2) % kRegs], st + j + 2); // two tiles ahead, in registers
-                        if (has_slice)
-                        {
-                            if (!mbar_wait(bar_s + 8 * slot, parity))
-                                timed_out = true;
-                            compute(st + j, slot, pr[ri]);
+                for (int s = 0; s < SETS; s++)
 #pragma unroll
-                            for (int s = 0; s < SETS; s++)
+                    for (int mb = 0; mb < MB; mb++)
 #pragma unroll
-                                for (int mb = 0; mb < MB; mb++)
-                                    reinterpret_cast<float4*>(my + j * TILE_F)[(s * MB + mb) * 32 + lane] =
-                                        make_float4(tot[s][mb][0], tot[s][mb][1], tot[s][mb][2], tot[s][mb][3]);
-                        }
-                        else
-                        {
-#pragma unroll
-                            for (int q = 0; q < SETS * MB; q++)
-                                reinterpret_cast<float4*>(my + j * TILE_F)[q * 32 + lane] =
-                                    make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
-                        if (++slot == p.depth)
-                            slot = 0, parity ^= 1;
-                    }
-                }
-                __syncthreads(); // every warp has read its tiles of this pair: the slots may be refilled
-                if (tid == 0)
-                    for (int j = 0; j < pair_n; j++)
-                        produce(st + j + p.depth); // lands in the slot of tile st + j
-                const float* rb = red + ((st >> 1) & 1) * nwarps * 2 * TILE_F;
-                for (int o = tid; o < pair_n * TILE_F; o += nthreads)
-                {
-                    const int j = o / TILE_F, oo = o - j * TILE_F;
-                    float v = 0.f;
-                    for (int w = 0; w < nwarps; w++)
-                        v += rb[w * 2 * TILE_F + j * TILE_F + oo];
-                    res[((st + j) % kBatch) * TILE_F + oo] = v;
-                }
-                const int last = st + pair_n - 1;
-                if ((last % kBatch) == kBatch - 1 || last == nsteps - 1)
-                    flush(last - (last % kBatch), (last % kBatch) + 1);
+                        for (int c = 0; c < 4; c++)
+                            tot[s][mb][c] = 0.f;
             }
+            if (t < tq)
+            {
+#pragma unroll
+                for (int s = 0; s < SETS; s++)
+#pragma unroll
+                    for (int mb = 0; mb < MB; mb++)
+                        my[(s * MB + mb) * 8 * tq + g * tq + t] =
+                            make_float4(tot[s][mb][0], tot[s][mb][1], tot[s][mb][2], tot[s][mb][3]);
+            }
+            if (st < 5)
+                NNF_TRACE_POINT(5 + 2 * st);
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(empty_s + 8 * slot);
+            if (++slot == p.depth)
+                slot = 0, parity ^= 1;
         }
+        NNF_TRACE_POINT(14);
+        flush(first, count);
+        NNF_TRACE_POINT(15);
     }
     if (timed_out)
         atomicExch(p.status, 1);
@@ -729,22 +871,14 @@ cudaError_t ensure_smem(size_t smem)
 }
 
 template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT>
-cudaError_t launch(const GemvParams& p, const CUtensorMap& t0, const CUtensorMap& t1, int warps, int grid,
-                   size_t smem, cudaStream_t stream)
+cudaError_t launch(const GemvParams& p, int warps, int grid, size_t smem, cudaStream_t stream)
 {
     cudaError_t e = ensure_smem<WBITS, MB, XSPLIT, DUAL, EXACT>(smem);
     if (e != cudaSuccess)
         return e;
     (void)cudaGetLastError(); // do not inherit a stale error left behind by an unrelated earlier call
-    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT><<<grid, warps * 32, smem, stream>>>(p, t0, t1);
+    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT><<<grid, (warps + 1) * 32, smem, stream>>>(p);
     return cudaGetLastError();
-}
-
-size_t smem_for(int mb, bool dual, int warps, int depth)
-{
-    if (mb == 1)
-        return dual ? Smem<1, true>::total_bytes(warps, depth) : Smem<1, false>::total_bytes(warps, depth);
-    return dual ? Smem<2, true>::total_bytes(warps, depth) : Smem<2, false>::total_bytes(warps, depth);
 }
 
 #define NNF_GEMV_FOR_EACH_VARIANT(X)                                                                              \
@@ -763,17 +897,104 @@ size_t smem_for(int mb, bool dual, int warps, int depth)
     X(8, 2, true, false)                                                                                          \
     X(8, 2, true, true)
 
-cudaError_t dispatch(int wbits, const nnf::GemvPlan& plan, const GemvParams& p, const CUtensorMap& t0,
-                     const CUtensorMap& t1, int grid, cudaStream_t stream)
+cudaError_t dispatch(int wbits, const nnf::GemvPlan& plan, const GemvParams& p, int grid, cudaStream_t stream)
 {
 #define NNF_X(WB, MBV, XSP, DU)                                                                                   \
     if (wbits == WB && plan.mb == MBV && plan.xsplit == XSP && plan.dual == DU)                                   \
         return plan.exact                                                                                         \
-                   ? launch<WB, MBV, XSP, DU, true>(p, t0, t1, plan.warps, grid, plan.smem_bytes, stream)         \
-                   : launch<WB, MBV, XSP, DU, false>(p, t0, t1, plan.warps, grid, plan.smem_bytes, stream);
+                   ? launch<WB, MBV, XSP, DU, true>(p, plan.warps, grid, plan.smem_bytes, stream)                 \
+                   : launch<WB, MBV, XSP, DU, false>(p, plan.warps, grid, plan.smem_bytes, stream);
     NNF_GEMV_FOR_EACH_VARIANT(NNF_X)
 #undef NNF_X
     return cudaErrorInvalidValue;
+}
+
+// Ring depth and batch length for a CTA of `warps` warps that walks over at most `steps` row tiles, within `cap`
+// bytes of shared memory.  Bytes in flight come first (about 96 KB per SM cover the HBM latency at full rate), then
+// the batch length, which only sets how often the warps meet.
+bool choose_ring(int sets, int mb, int warps, int tq, int pset_bytes, int steps, int cap, int* depth, int* batch)
+{
+    const int want_d = std::min(kMaxDepth, std::max(1, steps)), want_b = std::min(kBatch, std::max(1, steps));
+    const size_t slot_bytes = (size_t)sets * 16 * (warps * 128 + 64) + (size_t)sets * pset_bytes;
+    const size_t target = std::min((size_t)want_d * slot_bytes, (size_t)96 * 1024);
+    int best_d = 0, best_b = 0;
+    int last_b = 0;
+    for (int b : {want_b, 4, 2, 1})
+    {
+        if (b > want_b || b == last_b)
+            continue;
+        last_b = b;
+        for (int d = want_d; d >= 1; d--)
+        {
+            if ((int)SmemLayout(sets, mb, warps, d, b, tq, pset_bytes).total + 1024 > cap)
+                continue;
+            if (d > best_d)
+                best_d = d, best_b = b;
+            if ((size_t)d * slot_bytes >= target)
+            {
+                *depth = d, *batch = b;
+                return true;
+            }
+            break; // the deepest ring for this batch length is too shallow: try a shorter batch
+        }
+    }
+    *depth = best_d, *batch = best_b;
+    return best_d > 0;
+}
+
+// Everything the kernel needs to know that does not depend on where the operands live.
+void fill_params(GemvParams& p, const nnf_b200_linear_desc& d, const nnf::GemvPlan& plan, const void* x,
+                 const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias, void* y,
+                 int* status, void* workspace)
+{
+    const int ue = (d.w_bits == 4) ? 128 : 64;
+    p.wq[0] = static_cast<const uint8_t*>(w->wq);
+    p.scale[0] = w->scale;
+    p.zp[0] = static_cast<const uint8_t*>(w->zp);
+    p.row_bytes = (d.w_bits == 4) ? d.K / 2 : d.K;
+    if (plan.dual)
+    {
+        p.wq[1] = static_cast<const uint8_t*>(w2->wq);
+        p.scale[1] = w2->scale;
+        p.zp[1] = static_cast<const uint8_t*>(w2->zp);
+    }
+    p.x = x;
+    p.gain = static_cast<const float*>(gain);
+    p.bias = static_cast<const float*>(bias);
+    p.y = y;
+    p.status = status;
+    p.M = d.M, p.N = d.N, p.K = d.K;
+    p.group = d.group_size > 0 ? d.group_size : d.K;
+    p.G = d.K / p.group;
+    p.zp_row_bytes = (d.w_bits == 4) ? (p.G + 1) / 2 : p.G;
+    p.units = d.K / ue;
+    p.slices = plan.slices;
+    p.row_tiles = plan.row_tiles;
+    p.splits = plan.splits;
+    p.ctas_per_split = plan.ctas_per_split;
+    p.x_f32 = d.x_dtype == NNF_B200_F32;
+    p.y_f32 = d.y_dtype == NNF_B200_F32;
+    p.scale_f32 = d.scale_dtype == NNF_B200_F32;
+    p.rmsnorm = d.prologue == NNF_B200_PROLOGUE_RMSNORM;
+    p.has_bias = bias != nullptr;
+    p.eps = d.rms_eps;
+    p.depth = plan.depth;
+    p.batch = plan.batch;
+    p.tq = plan.tq;
+    p.scale_tile_bytes = plan.scale_tile_bytes;
+    p.zp_tile_bytes = plan.zp_tile_bytes;
+    p.pset_bytes = plan.pset_bytes;
+    p.slot_floats = (int)plan.slot_floats;
+    // Bulk copies of the quantisation parameters need whole tiles inside the tensors and 16-byte aligned sources.
+    auto ok16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+    p.bulk_params = plan.pset_bytes > 0 && ok16(w->scale) && ok16(w->zp) &&
+                    (!plan.dual || (ok16(w2->scale) && ok16(w2->zp)));
+    if (plan.splits > 1)
+    {
+        const size_t cnt = ((size_t)plan.row_tiles * sizeof(unsigned) + 255) / 256 * 256;
+        p.ws_count = static_cast<unsigned*>(workspace);
+        p.ws_slots = reinterpret_cast<float*>(static_cast<char*>(workspace) + cnt);
+    }
 }
 } // namespace
 
@@ -800,6 +1021,7 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
     }
     GemvPlan pl;
     pl.mb = d.M > 8 ? 2 : 1;
+    pl.tq = d.M > 4 ? 4 : (d.M > 2 ? 2 : 1);
     pl.dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
     pl.exact = (d.flags & NNF_B200_FLAG_EXACT_ZP) != 0;
     // fp32 activations are carried as fp16 hi + lo where the register budget allows it
@@ -807,12 +1029,16 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
     pl.row_tiles = (d.N + 15) / 16;
     const int units = d.K / ue;
     pl.slices = (units + 1) / 2;
+    const int G = d.K / group;
+    pl.scale_tile_bytes = 16 * G * (d.scale_dtype == NNF_B200_F32 ? 4 : 2);
+    pl.zp_tile_bytes = 16 * ((d.w_bits == 4) ? (G + 1) / 2 : G);
+    // whole tiles of parameters only: a ragged last tile makes the kernel read them with plain loads
+    pl.pset_bytes = (d.N % 16 == 0) ? pl.scale_tile_bytes + pl.zp_tile_bytes : 0;
     const int sms = ctx ? ctx->sm_count : 148;
     const int smem_cap = ctx ? ctx->smem_optin : 227 * 1024;
     const int sets = pl.dual ? 2 : 1;
     // Warps per CTA: one per slice of the CTA's K range; split K when a row has more slices than that.  The
-    // widest CTA whose reduction buffers and a ring of at least two tiles fit in shared memory is taken.
-    int resident = 1;
+    // widest CTA whose partial sums and a useful ring fit in shared memory is taken.
     bool fits = false;
     for (int max_warps : {16, 12, 8, 6, 4, 2, 1})
     {
@@ -827,32 +1053,29 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
             pl.splits = std::min(d.split_k, pl.slices);
         }
         pl.warps = (pl.slices + pl.splits - 1) / pl.splits;
-        // CTAs per SM by registers (the kernel is compiled for at most 128 per thread: 512 threads per SM), then
-        // the deepest ring that lets that many CTAs share the SM's shared memory.
-        resident = std::max(1, 512 / (pl.warps * 32));
-        for (int depth = kMaxDepth; depth >= 2 && !fits; depth--)
+        // CTAs per SM by registers (the kernel is compiled for at most 120 per thread: 544 threads per SM, one
+        // warp of each CTA being its producer), then the ring that lets that many CTAs share the shared memory.
+        for (int resident = std::max(1, 544 / ((pl.warps + 1) * 32)); resident >= 1 && !fits; resident = resident > 1 ? 1 : 0)
         {
-            pl.depth = depth;
-            fits = (int)smem_for(pl.mb, pl.dual, pl.warps, depth) + 1024 <= smem_cap / resident;
-        }
-        if (!fits && resident > 1)
-        {
-            resident = 1;
-            pl.depth = 2;
-            fits = (int)smem_for(pl.mb, pl.dual, pl.warps, 2) + 1024 <= smem_cap;
+            int per_split = std::max(1, (sms * resident) / pl.splits);
+            per_split = std::min(per_split, pl.row_tiles);
+            const int steps = (pl.row_tiles + per_split - 1) / per_split;
+            if (choose_ring(sets, pl.mb, pl.warps, pl.tq, pl.pset_bytes, steps, smem_cap / resident, &pl.depth,
+                            &pl.batch))
+            {
+                fits = true;
+                pl.ctas_per_split = per_split;
+            }
         }
         if (fits || d.split_k > 0)
             break;
     }
-    pl.smem_bytes = smem_for(pl.mb, pl.dual, pl.warps, pl.depth);
-    if (!fits || (int)pl.smem_bytes > smem_cap)
+    if (!fits)
     {
         *why = "shared memory: the launch shape does not fit";
         return NNF_B200_ENOTSUP;
     }
-    int per_split = std::max(1, (sms * resident) / pl.splits);
-    per_split = std::min(per_split, pl.row_tiles);
-    pl.ctas_per_split = per_split;
+    pl.smem_bytes = SmemLayout(sets, pl.mb, pl.warps, pl.depth, pl.batch, pl.tq, pl.pset_bytes).total;
     pl.slot_floats = (size_t)sets * pl.mb * 128 + 8 * pl.mb;
     pl.workspace_bytes = 0;
     if (pl.splits > 1)
@@ -864,63 +1087,15 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
     return NNF_B200_OK;
 }
 
-int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan,
+int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan_in,
                 const void* x, const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
                 const void* bias, void* y, void* workspace)
 {
+    const GemvPlan& plan = plan_in;
     GemvParams p{};
-    const int ue = (d.w_bits == 4) ? 128 : 64;
-    const int row_bytes = (d.w_bits == 4) ? d.K / 2 : d.K;
-    p.scale[0] = w->scale;
-    p.zp[0] = static_cast<const uint8_t*>(w->zp);
-    if (plan.dual)
-    {
-        p.scale[1] = w2->scale;
-        p.zp[1] = static_cast<const uint8_t*>(w2->zp);
-    }
-    // Weight tensor maps: bytes [N][row_bytes], boxes of 16 rows x 128 bytes, 128-byte swizzle.
-    const CUtensorMap* t0 = weight_tensor_map(ctx, w->wq, d.N, row_bytes, 128, 16);
-    const CUtensorMap* t1 = plan.dual ? weight_tensor_map(ctx, w2->wq, d.N, row_bytes, 128, 16) : t0;
-    if (!t0 || !t1)
-        return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
-    p.x = x;
-    p.gain = static_cast<const float*>(gain);
-    p.bias = static_cast<const float*>(bias);
-    p.y = y;
-    p.status = ctx->dev_status;
-    p.M = d.M, p.N = d.N, p.K = d.K;
-    p.group = d.group_size > 0 ? d.group_size : d.K;
-    p.G = d.K / p.group;
-    p.zp_row_bytes = (d.w_bits == 4) ? (p.G + 1) / 2 : p.G;
-    p.units = d.K / ue;
-    p.slices = plan.slices;
-    p.row_tiles = plan.row_tiles;
-    p.splits = plan.splits;
-    p.ctas_per_split = plan.ctas_per_split;
-    p.x_f32 = d.x_dtype == NNF_B200_F32;
-    p.y_f32 = d.y_dtype == NNF_B200_F32;
-    p.scale_f32 = d.scale_dtype == NNF_B200_F32;
-    p.rmsnorm = d.prologue == NNF_B200_PROLOGUE_RMSNORM;
-    p.has_bias = bias != nullptr;
-    p.eps = d.rms_eps;
-    p.depth = plan.depth;
-    p.slot_floats = (int)plan.slot_floats;
-    // Reading the quantisation parameters as aligned 32-bit words must stay inside the tensors.
-    const size_t scale_bytes = (size_t)d.N * p.G * (p.scale_f32 ? 4 : 2);
-    const size_t zp_bytes = (size_t)d.N * p.zp_row_bytes;
-    auto word_ok = [](const void* ptr, size_t bytes) {
-        return (reinterpret_cast<uintptr_t>(ptr) & 3u) == 0 && (bytes & 3u) == 0;
-    };
-    p.fast_params = word_ok(w->scale, scale_bytes) && word_ok(w->zp, zp_bytes) &&
-                    (!plan.dual || (word_ok(w2->scale, scale_bytes) && word_ok(w2->zp, zp_bytes)));
-    if (plan.splits > 1)
-    {
-        const size_t cnt = ((size_t)plan.row_tiles * sizeof(unsigned) + 255) / 256 * 256;
-        p.ws_count = static_cast<unsigned*>(workspace);
-        p.ws_slots = reinterpret_cast<float*>(static_cast<char*>(workspace) + cnt);
-    }
+    fill_params(p, d, plan, x, w, w2, gain, bias, y, ctx->dev_status, workspace);
     const int grid = plan.splits * plan.ctas_per_split;
-    cudaError_t e = dispatch(d.w_bits, plan, p, *t0, *t1, grid, stream);
+    cudaError_t e = dispatch(d.w_bits, plan, p, grid, stream);
     if (e != cudaSuccess)
         return set_error(ctx, NNF_B200_ECUDA,
                          std::string("dq_gemv launch: ") + cudaGetErrorString(e) + " (grid " + std::to_string(grid) +
@@ -929,7 +1104,6 @@ int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     return NNF_B200_OK;
 }
 } // namespace nnf
-
 // ------------------------------------------------------------------------------------------------------------------
 // Allocation-free variant of the split-K small-M linear.
 //
@@ -942,8 +1116,8 @@ int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
 //
 // The array's name is only a host-side handle in host code; the device address is fetched with
 // cudaGetSymbolAddress once per device, by the first call made while that device is current.  That first call also
-// raises the kernel's shared-memory limit and looks up the driver's tensor-map encoder, so it should be made
-// outside of any stream capture.  All calls share the one array (and it keeps what the previous call left): calls
+// raises the kernel's shared-memory limit and queries device attributes, so it should be made outside of any stream
+// capture.  All calls share the one array (and it keeps what the previous call left): calls
 // that overlap on the GPU race on it; the tile counters are cleared on the stream at the start of every call.
 namespace
 {
@@ -955,7 +1129,6 @@ struct StaticDeviceState
     bool ready = false;
     void* scratch = nullptr;
     int* status = nullptr;
-    void* encode_tiled = nullptr;
     int sm_count = 0;
     int smem_optin = 0;
 };
@@ -967,6 +1140,17 @@ void put_message(char* buf, size_t len, const char* msg)
         snprintf(buf, len, "%s", msg);
 }
 } // namespace
+
+#ifdef NNF_TRACE
+extern "C" __attribute__((visibility("default"))) int nnf_debug_set(int v)
+{
+    return (int)cudaMemcpyToSymbol(g_nnf_debug, &v, sizeof v);
+}
+extern "C" __attribute__((visibility("default"))) int nnf_debug_trace_read(unsigned long long* out, int n)
+{
+    return (int)cudaMemcpyFromSymbol(out, g_nnf_trace, (size_t)n * sizeof(unsigned long long));
+}
+#endif
 
 extern "C" __attribute__((visibility("default"))) int
 nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, const void* x,
@@ -1023,12 +1207,6 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
             put_message(errbuf, errbuf_len, "device attributes unavailable, or not an sm_100 device");
             return NNF_B200_ENOTSUP;
         }
-        st.encode_tiled = load_encode_tiled();
-        if (!st.encode_tiled)
-        {
-            put_message(errbuf, errbuf_len, "cuTensorMapEncodeTiled entry point not found");
-            return NNF_B200_ECUDA;
-        }
         st.scratch = sp;
         st.status = static_cast<int*>(tp);
         st.ready = true;
@@ -1056,56 +1234,8 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
         return NNF_B200_EWORKSPACE;
     }
 
-    const int ue = (d.w_bits == 4) ? 128 : 64;
-    const int row_bytes = (d.w_bits == 4) ? d.K / 2 : d.K;
-    alignas(64) CUtensorMap t0, t1;
-    if (!encode_tensor_map_2d(st.encode_tiled, &t0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->wq, (uint64_t)row_bytes,
-                              (uint64_t)d.N, (uint64_t)row_bytes, 128, 16, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !encode_tensor_map_2d(st.encode_tiled, &t1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, dual ? w2->wq : w->wq,
-                              (uint64_t)row_bytes, (uint64_t)d.N, (uint64_t)row_bytes, 128, 16,
-                              CU_TENSOR_MAP_SWIZZLE_128B))
-    {
-        put_message(errbuf, errbuf_len, "cuTensorMapEncodeTiled failed for the weight tensor");
-        return NNF_B200_ECUDA;
-    }
-
     GemvParams p{};
-    p.scale[0] = w->scale;
-    p.zp[0] = static_cast<const uint8_t*>(w->zp);
-    if (dual)
-    {
-        p.scale[1] = w2->scale;
-        p.zp[1] = static_cast<const uint8_t*>(w2->zp);
-    }
-    p.x = x;
-    p.gain = static_cast<const float*>(gain);
-    p.bias = static_cast<const float*>(bias);
-    p.y = y;
-    p.status = st.status;
-    p.M = d.M, p.N = d.N, p.K = d.K;
-    p.group = d.group_size > 0 ? d.group_size : d.K;
-    p.G = d.K / p.group;
-    p.zp_row_bytes = (d.w_bits == 4) ? (p.G + 1) / 2 : p.G;
-    p.units = d.K / ue;
-    p.slices = plan.slices;
-    p.row_tiles = plan.row_tiles;
-    p.splits = plan.splits;
-    p.ctas_per_split = plan.ctas_per_split;
-    p.x_f32 = d.x_dtype == NNF_B200_F32;
-    p.y_f32 = d.y_dtype == NNF_B200_F32;
-    p.scale_f32 = d.scale_dtype == NNF_B200_F32;
-    p.rmsnorm = d.prologue == NNF_B200_PROLOGUE_RMSNORM;
-    p.has_bias = bias != nullptr;
-    p.eps = d.rms_eps;
-    p.depth = plan.depth;
-    p.slot_floats = (int)plan.slot_floats;
-    const size_t scale_bytes = (size_t)d.N * p.G * (p.scale_f32 ? 4 : 2);
-    const size_t zp_bytes = (size_t)d.N * p.zp_row_bytes;
-    auto word_ok = [](const void* ptr, size_t bytes) {
-        return (reinterpret_cast<uintptr_t>(ptr) & 3u) == 0 && (bytes & 3u) == 0;
-    };
-    p.fast_params = word_ok(w->scale, scale_bytes) && word_ok(w->zp, zp_bytes) &&
-                    (!dual || (word_ok(w2->scale, scale_bytes) && word_ok(w2->zp, zp_bytes)));
+    fill_params(p, d, plan, x, w, w2, gain, bias, y, st.status, st.scratch);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (plan.splits > 1)
     {
@@ -1116,10 +1246,8 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
             put_message(errbuf, errbuf_len, "cudaMemsetAsync on the built-in scratch array failed");
             return NNF_B200_ECUDA;
         }
-        p.ws_count = static_cast<unsigned*>(st.scratch);
-        p.ws_slots = reinterpret_cast<float*>(static_cast<char*>(st.scratch) + cnt);
     }
-    cudaError_t e = dispatch(d.w_bits, plan, p, t0, t1, plan.splits * plan.ctas_per_split, s);
+    cudaError_t e = dispatch(d.w_bits, plan, p, plan.splits * plan.ctas_per_split, s);
     if (e != cudaSuccess)
     {
         put_message(errbuf, errbuf_len, cudaGetErrorString(e));

@@ -42,8 +42,11 @@ struct GemvPlan
     size_t slot_floats = 0;     // floats per (split, row tile) partial slot
     size_t workspace_bytes = 0; // 0 when splits == 1
     size_t smem_bytes = 0;      // dynamic shared memory of the launch
-    int units_cap = 0;          // 64-byte units per split (upper bound): sizes the staged activations
-    int ng_cap = 0;             // quantisation groups per warp (upper bound)
+    int batch = 1;              // row tiles between two reductions over the CTA's warps
+    int tq = 4;                 // accumulator column pairs that carry batch rows
+    int scale_tile_bytes = 0;   // scales of one 16-row tile
+    int zp_tile_bytes = 0;      // zero-points of one 16-row tile
+    int pset_bytes = 0;         // shared memory per ring slot and weight set for both (0: plain loads)
 };
 
 int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
