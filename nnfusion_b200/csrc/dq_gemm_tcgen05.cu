@@ -96,6 +96,20 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     return false;
 }
 
+// Same for the thread that issues the MMAs: it is the kernel's critical path, so it polls without backing off.
+__device__ __forceinline__ bool wait_hot(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    for (uint32_t i = 0; i < kGemmSpin; i++)
+    {
+        if (mbar_try_wait(bar, parity))
+            return true;
+        if ((i & 1023u) == 1023u && *abort_flag)
+            return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
 // UMMA shared-memory descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr)
 {
@@ -215,7 +229,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
             for (int kb = 0; kb < KB && ok; kb++)
             {
                 const int sx = kb % C::STAGES, sa = sx;
-                ok = wait_or_abort(full(sx), (uint32_t)(kb / C::STAGES) & 1u, abort_flag);
+                ok = wait_hot(full(sx), (uint32_t)(kb / C::STAGES) & 1u, abort_flag);
                 if (!ok)
                     break;
                 tcgen05_fence_after();
@@ -245,6 +259,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
         const int n = min(n0 + r, p.N - 1);          // rows past N read the last row's parameters, never stored
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int kb_per_group = p.group / C::BK;
+        const uint32_t wsm_s = smem_u32(wsm), xs_s = smem_u32(xs);
         bool ok = true;
 
         auto load_scale = [&](int gidx) -> float {
@@ -284,12 +299,12 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 if (!wait_or_abort(full_w(set, sw), (uint32_t)(chunk / C::WSTAGES) & 1u, abort_flag))
                     return false;
             // this row's raw bytes: 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
-            const uint8_t* row = wsm + (size_t)(set * C::WSTAGES + sw) * C::W_STAGE_BYTES + r * 128;
+            const uint32_t row = wsm_s + (uint32_t)((set * C::WSTAGES + sw) * C::W_STAGE_BYTES + r * 128);
             constexpr int NV = C::RAW_BYTES / 16;
             uint4 raw[NV];
 #pragma unroll
             for (int v = 0; v < NV; v++)
-                raw[v] = *reinterpret_cast<const uint4*>(row + (((j * NV + v) ^ (r & 7)) * 16));
+                raw[v] = lds128(row + (uint32_t)(((j * NV + v) ^ (r & 7)) * 16));
             if (j + C::DQ_GROUPS >= C::KB_PER_CHUNK || kb + C::DQ_GROUPS >= KB)
                 mbar_arrive(empty_w(set, sw)); // last read of this chunk by this thread
 
@@ -386,7 +401,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
             const int peer = warp >> 2;              // 0 .. PEERS-1
             const int nrow = n0 + r;
             const float bias = (p.has_bias && nrow < p.N) ? __ldg(p.bias + nrow) : 0.f;
-            __half* stage_t = reinterpret_cast<__half*>(xs); // [BX][128] halves, row m = 256 bytes
+            // the tile is staged in the x ring as [BX][128] halves, row m = 256 bytes
             if (ok)
             {
                 for (int cb = peer; cb < C::BX / 32; cb += PEERS)
@@ -408,7 +423,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                         }
                         v += bias;
                         if (p.fast_store)
-                            stage_t[ml * 128 + r] = __float2half_rn(v);
+                            sts16(xs_s + (uint32_t)((ml * 128 + r) * 2), __half_as_ushort(__float2half_rn(v)));
                         else if (m < p.M && nrow < p.N)
                         {
                             if (p.y_f32)
@@ -432,7 +447,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                         const int m = m0 + ml, n = n0 + nc;
                         if (m < p.M && n < p.N)
                             *reinterpret_cast<uint4*>(static_cast<__half*>(p.y) + (size_t)m * p.N + n) =
-                                *reinterpret_cast<const uint4*>(stage_t + ml * 128 + nc);
+                                lds128(xs_s + (uint32_t)((ml * 128 + nc) * 2));
                     }
                 }
             }

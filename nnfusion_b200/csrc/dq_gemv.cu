@@ -124,6 +124,27 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
                  : "memory");
 }
+template <int OFF>
+__device__ __forceinline__ uint4 lds128_at(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4+%5];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr), "n"(OFF));
+    return v;
+}
+__device__ __forceinline__ unsigned short lds_u16(uint32_t addr)
+{
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void named_barrier(int id, int threads)
 {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -152,16 +173,9 @@ __device__ unsigned long long g_nnf_trace[3 * 2048 * 16];
             g_nnf_trace[(4096 + blockIdx.x) * 16 + (i)] = t_;                                                      \
         }                                                                                                          \
     } while (0)
-__device__ int g_nnf_debug; // ablation switches for timing experiments (only with -DNNF_ABLATE)
-#ifdef NNF_ABLATE
-#define NNF_DEBUG(bit) (g_nnf_debug & (bit))
-#else
-#define NNF_DEBUG(bit) false
-#endif
 #else
 #define NNF_TRACE_POINT(i)
 #define NNF_TRACE_PRODUCER(i)
-#define NNF_DEBUG(bit) false
 #endif
 
 template <int WBITS>
@@ -193,7 +207,9 @@ struct SmemLayout
 // EXACT = false: the tensor core multiplies x by (offset + q) and the offset and zero-point are taken out of the
 //                fp32 sum afterwards, acc - (C1 + zp * C2), with C1 = sum(offset_k * x_k), C2 = sum(x_k) over the
 //                64-byte unit.  Same fp32 accumulation, about 40 % fewer unpack instructions.
-template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT>
+// FAST = true : the quantisation parameters of every tile arrive in shared memory and the scales are fp16 (the
+//                caller checks both); the inner loop then contains no choice that depends on the launch.
+template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT, bool FAST>
 __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     dq_gemv_kernel(const GemvParams p)
 {
@@ -513,6 +529,20 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     auto row_of = [&](int step, int h) { return min((cta_in_split + step * p.ctas_per_split) * 16 + g + 8 * h, p.N - 1); };
     float tot[SETS][MB][4];
     const uint32_t k6400 = held_constant(0x64006400u), k5400 = held_constant(0x54005400u);
+    // Shared-memory addresses that never change for this lane: its 16 bytes of rows g / g + 8 in slot 0 (unit 1
+    // sits 64 bytes further), and its scales / zero-points in slot 0's parameter block.
+    const uint32_t wrow[2] = {ring_s + (uint32_t)(warp * 128 + g * row_stride + t * 16),
+                              ring_s + (uint32_t)(warp * 128 + (g + 8) * row_stride + t * 16)};
+    uint32_t sa[2][2], za[2][2];
+#pragma unroll
+    for (int l = 0; l < 2; l++)
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+            sa[l][h] = pring_s + (uint32_t)soff[l][h], za[l][h] = pring_s + (uint32_t)zoff[l][h];
+    const int zsh[2] = {(WBITS == 4) ? 4 * (grp_of[0] & 1) : 0, (WBITS == 4) ? 4 * (grp_of[1] & 1) : 0};
+    const uint32_t wset_bytes = (uint32_t)(16 * row_stride);
+    const bool one_col = p.M == 1; // only accumulator column 0 carries a batch row
+
     auto compute = [&](int step, int slot) {
 #pragma unroll
         for (int s = 0; s < SETS; s++)
@@ -520,13 +550,17 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             // (scale, zero-point) of rows g / g+8 for both halves of the slice
             float sc[2][2];
             uint32_t zq[2][2];
-            if (NNF_DEBUG(8))
+            if (FAST)
             {
+                const uint32_t pb = (uint32_t)((slot * SETS + s) * p.pset_bytes);
 #pragma unroll
                 for (int l = 0; l < 2; l++)
 #pragma unroll
                     for (int h = 0; h < 2; h++)
-                        sc[l][h] = 1.f, zq[l][h] = 0;
+                    {
+                        sc[l][h] = __half2float(__ushort_as_half(lds_u16(sa[l][h] + pb)));
+                        zq[l][h] = (WBITS == 4) ? (lds_u8(za[l][h] + pb) >> zsh[l]) & 0xFu : lds_u8(za[l][h] + pb);
+                    }
             }
             else if (p.bulk_params)
             {
@@ -539,7 +573,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                         sc[l][h] = p.scale_f32 ? *reinterpret_cast<const float*>(pb + soff[l][h])
                                                : __half2float(*reinterpret_cast<const __half*>(pb + soff[l][h]));
                         const uint32_t zb = pb[zoff[l][h]];
-                        zq[l][h] = (WBITS == 4) ? (zb >> (4 * (grp_of[l] & 1))) & 0xF : zb;
+                        zq[l][h] = (WBITS == 4) ? (zb >> zsh[l]) & 0xFu : zb;
                     }
             }
             else
@@ -555,23 +589,21 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                         sc[l][h] = p.scale_f32 ? __ldg(static_cast<const float*>(p.scale[s]) + sidx)
                                                : __half2float(__ldg(static_cast<const __half*>(p.scale[s]) + sidx));
                         if (WBITS == 4)
-                            zq[l][h] = (__ldg(p.zp[s] + (size_t)row * p.zp_row_bytes + (grp_of[l] >> 1)) >>
-                                        (4 * (grp_of[l] & 1))) &
-                                       0xF;
+                            zq[l][h] = (__ldg(p.zp[s] + (size_t)row * p.zp_row_bytes + (grp_of[l] >> 1)) >> zsh[l]) & 0xFu;
                         else
                             zq[l][h] = __ldg(p.zp[s] + sidx);
                     }
                 }
             }
-            // this warp's 128 bytes of row r of the tile
-            const uint8_t* wt = ring + (size_t)((slot * SETS + s) * 16) * row_stride + warp * 128;
+            // this lane's 16 bytes of rows g / g+8, both units of the warp's slice
+            const uint32_t wb = (uint32_t)(slot * SETS + s) * wset_bytes;
             uint32_t wq[2][2][4]; // [unit][row half][word]
 #pragma unroll
             for (int l = 0; l < 2; l++)
 #pragma unroll
                 for (int h = 0; h < 2; h++)
                 {
-                    const uint4 v = *reinterpret_cast<const uint4*>(wt + (g + 8 * h) * row_stride + (4 * l + t) * 16);
+                    const uint4 v = l ? lds128_at<64>(wrow[h] + wb) : lds128_at<0>(wrow[h] + wb);
                     wq[l][h][0] = v.x, wq[l][h][1] = v.y, wq[l][h][2] = v.z, wq[l][h][3] = v.w;
                 }
             uint32_t zA[2][2], zB[2][2]; // fp16x2 constants holding (offset + zero-point)
@@ -586,8 +618,8 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                         zB[l][h] = (WBITS == 4) ? (0x5400u | (zq[l][h] << 4)) * 0x00010001u : zA[l][h]; // 64 + zp
                     }
             }
-            // four independent accumulation chains: (unit, word parity)
-            float acc[2][2][MB][4];
+            // one accumulation chain per unit (the units may belong to different quantisation groups)
+            float acc[2][MB][4];
 #pragma unroll
             for (int w4 = 0; w4 < 4; w4++)
 #pragma unroll
@@ -598,11 +630,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                     for (int h = 0; h < 2; h++)
                     {
                         const uint32_t w = wq[l][h][w4];
-                        if (NNF_DEBUG(2))
-                        {
-                            a[h][0] = a[h][1] = a[h][2] = a[h][3] = w;
-                        }
-                        else if (WBITS == 4)
+                        if (WBITS == 4)
                         {
                             const uint32_t w8 = w >> 8;
                             a[h][0] = and_or<0x000F000Fu>(w, k6400);  // 1024 + (n0, n4)
@@ -638,44 +666,43 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
 #pragma unroll
                             for (int xsn = 0; xsn < XS; xsn++)
                             {
-                                if (NNF_DEBUG(1))
-                                {
-                                    const float z = __uint_as_float((a[0][q] ^ a[1][q] ^ a[0][q + 1] ^ a[1][q + 1]) & 0x3FFFFFFFu);
-                                    if (w4 < 2 && q == 0 && xsn == 0)
-                                        acc[l][w4 & 1][mb][0] = acc[l][w4 & 1][mb][1] = acc[l][w4 & 1][mb][2] = acc[l][w4 & 1][mb][3] = z;
-                                    else
-                                        acc[l][w4 & 1][mb][q] += z;
-                                }
-                                else if (w4 < 2 && q == 0 && xsn == 0) // first product of this chain
-                                    mma16816_first(acc[l][w4 & 1][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
+                                if (w4 == 0 && q == 0 && xsn == 0) // first product of this chain
+                                    mma16816_first(acc[l][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
                                                    xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
                                 else
-                                    mma16816(acc[l][w4 & 1][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
+                                    mma16816(acc[l][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
                                              xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
                             }
                     }
                 }
+            float zf[2][2];
+#pragma unroll
+            for (int l = 0; l < 2; l++)
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+                    zf[l][h] = (float)zq[l][h];
+            auto finish_col = [&](int mb, int c) {
+                float u0 = acc[0][mb][c], u1 = acc[1][mb][c];
+                if (!EXACT)
+                {
+                    u0 -= fmaf(zf[0][c >> 1], c2[0][mb][c & 1], c1[0][mb][c & 1]);
+                    u1 -= fmaf(zf[1][c >> 1], c2[1][mb][c & 1], c1[1][mb][c & 1]);
+                }
+                tot[s][mb][c] = fmaf(sc[1][c >> 1], u1, sc[0][c >> 1] * u0);
+            };
 #pragma unroll
             for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-                for (int c = 0; c < 4; c++)
+            {
+                finish_col(mb, 0);
+                finish_col(mb, 2);
+                if (!one_col)
                 {
-                    float v = 0.f;
-                    if (NNF_DEBUG(4))
-                    {
-                        tot[s][mb][c] = acc[0][0][mb][c] + acc[0][1][mb][c] + acc[1][0][mb][c] + acc[1][1][mb][c];
-                        continue;
-                    }
-#pragma unroll
-                    for (int l = 0; l < 2; l++)
-                    {
-                        float u = acc[l][0][mb][c] + acc[l][1][mb][c];
-                        if (!EXACT)
-                            u -= fmaf((float)zq[l][c >> 1], c2[l][mb][c & 1], c1[l][mb][c & 1]);
-                        v = fmaf(sc[l][c >> 1], u, v);
-                    }
-                    tot[s][mb][c] = v;
+                    finish_col(mb, 1);
+                    finish_col(mb, 3);
                 }
+                else
+                    tot[s][mb][1] = tot[s][mb][3] = 0.f;
+            }
         }
     };
 
@@ -857,27 +884,27 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
 }
 
 // Raise the kernel's dynamic shared-memory limit (monotonically: the attribute is a plain setter).
-template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT>
+template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT, bool FAST>
 cudaError_t ensure_smem(size_t smem)
 {
     static size_t configured = 48 * 1024;
     if (smem <= configured)
         return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT>,
+    cudaError_t e = cudaFuncSetAttribute(dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT, FAST>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
         configured = smem;
     return e;
 }
 
-template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT>
+template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT, bool FAST>
 cudaError_t launch(const GemvParams& p, int warps, int grid, size_t smem, cudaStream_t stream)
 {
-    cudaError_t e = ensure_smem<WBITS, MB, XSPLIT, DUAL, EXACT>(smem);
+    cudaError_t e = ensure_smem<WBITS, MB, XSPLIT, DUAL, EXACT, FAST>(smem);
     if (e != cudaSuccess)
         return e;
     (void)cudaGetLastError(); // do not inherit a stale error left behind by an unrelated earlier call
-    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT><<<grid, (warps + 1) * 32, smem, stream>>>(p);
+    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT, FAST><<<grid, (warps + 1) * 32, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -901,9 +928,14 @@ cudaError_t dispatch(int wbits, const nnf::GemvPlan& plan, const GemvParams& p, 
 {
 #define NNF_X(WB, MBV, XSP, DU)                                                                                   \
     if (wbits == WB && plan.mb == MBV && plan.xsplit == XSP && plan.dual == DU)                                   \
-        return plan.exact                                                                                         \
-                   ? launch<WB, MBV, XSP, DU, true>(p, plan.warps, grid, plan.smem_bytes, stream)                 \
-                   : launch<WB, MBV, XSP, DU, false>(p, plan.warps, grid, plan.smem_bytes, stream);
+    {                                                                                                             \
+        if (plan.exact)                                                                                           \
+            return launch<WB, MBV, XSP, DU, true, false>(p, plan.warps, grid, plan.smem_bytes, stream);           \
+        /* the lean inner loop is built for fp16 activations only: fp32 ones pay for their second half anyway */  \
+        if (!XSP && p.bulk_params && !p.scale_f32)                                                                \
+            return launch<WB, MBV, false, DU, false, true>(p, plan.warps, grid, plan.smem_bytes, stream);         \
+        return launch<WB, MBV, XSP, DU, false, false>(p, plan.warps, grid, plan.smem_bytes, stream);              \
+    }
     NNF_GEMV_FOR_EACH_VARIANT(NNF_X)
 #undef NNF_X
     return cudaErrorInvalidValue;
@@ -1142,10 +1174,6 @@ void put_message(char* buf, size_t len, const char* msg)
 } // namespace
 
 #ifdef NNF_TRACE
-extern "C" __attribute__((visibility("default"))) int nnf_debug_set(int v)
-{
-    return (int)cudaMemcpyToSymbol(g_nnf_debug, &v, sizeof v);
-}
 extern "C" __attribute__((visibility("default"))) int nnf_debug_trace_read(unsigned long long* out, int n)
 {
     return (int)cudaMemcpyFromSymbol(out, g_nnf_trace, (size_t)n * sizeof(unsigned long long));
