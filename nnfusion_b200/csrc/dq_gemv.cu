@@ -151,6 +151,9 @@ __device__ __forceinline__ void named_barrier(int id, int threads)
 }
 
 // Compile with -DNNF_TRACE to record, per CTA, the time at which thread 0 and thread 256 pass the marked points.
+#ifndef NNF_TRACE_BASE
+#define NNF_TRACE_BASE 0 // first of the five row tiles whose times are recorded
+#endif
 #ifdef NNF_TRACE
 __device__ unsigned long long g_nnf_trace[3 * 2048 * 16];
 #define NNF_TRACE_POINT(i)                                                                                         \
@@ -244,7 +247,11 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     float* ss_cta = ss_w + nwarps * MPAD;                            // [MPAD]
     int* last_flag = reinterpret_cast<int*>(ss_cta + MPAD);          // [kBatch]
     const uint32_t ring_s = smem_u32(ring), pring_s = smem_u32(pring);
-    const int row_stride = nwarps * 128 + 64; // shared-memory bytes between two rows of a tile
+    // Shared-memory bytes between two rows of a tile.  When a CTA takes whole rows, a tile is one contiguous piece of
+    // memory and arrives with a single copy, rows back to back (the fragment loads then pay a two-way bank conflict,
+    // which is cheap next to sixteen separate copies).
+    const bool whole_rows = p.splits == 1 && p.row_bytes == nwarps * 128;
+    const int row_stride = whole_rows ? nwarps * 128 : nwarps * 128 + 64;
     const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * kMaxDepth;
 
     const int split = blockIdx.x / p.ctas_per_split;
@@ -274,13 +281,24 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         const uint32_t bar = full_s + 8 * slot;
         const int tile = cta_in_split + step * p.ctas_per_split;
         const int rows = tile_rows(step);
-        for (int c = lane; c < SETS * 16; c += 32)
+        if (whole_rows)
         {
-            const int s = c >> 4, r = c & 15;
-            if (r < rows)
-                bulk_load(ring_s + (uint32_t)(((slot * SETS + s) * 16 + r) * row_stride),
-                          p.wq[s] + (size_t)(tile * 16 + r) * p.row_bytes + (size_t)slice0 * 128, (uint32_t)seg_bytes,
-                          bar);
+            if (lane < SETS)
+                bulk_load(ring_s + (uint32_t)((slot * SETS + lane) * 16 * row_stride),
+                          (lane == 0 ? p.wq[0] : p.wq[1]) + (size_t)(tile * 16) * p.row_bytes,
+                          (uint32_t)(rows * p.row_bytes), bar);
+        }
+        else
+        {
+            for (int c = lane; c < SETS * 16; c += 32)
+            {
+                const int s = c >> 4, r = c & 15;
+                if (r < rows)
+                    bulk_load(ring_s + (uint32_t)(((slot * SETS + s) * 16 + r) * row_stride),
+                              (s == 0 ? p.wq[0] : p.wq[1]) + (size_t)(tile * 16 + r) * p.row_bytes +
+                                  (size_t)slice0 * 128,
+                              (uint32_t)seg_bytes, bar);
+            }
         }
         if (p.bulk_params && lane >= 32 - 2 * SETS)
         {
