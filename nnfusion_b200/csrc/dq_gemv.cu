@@ -59,6 +59,8 @@ struct GemvParams
     int units;  // 64-byte units per weight row
     int slices; // ceil(units / 2)
     int row_tiles, splits, ctas_per_split;
+    int slices_lo, slices_rem; // slices / splits and its remainder
+    int steps_lo, steps_rem;   // row_tiles / ctas_per_split and its remainder
     int x_f32, y_f32, scale_f32, rmsnorm, has_bias;
     int depth;       // ring depth in row tiles
     int batch;       // row tiles between two reductions over the warps (<= kBatch)
@@ -156,25 +158,25 @@ __device__ __forceinline__ void named_barrier(int id, int threads)
 #endif
 #ifdef NNF_TRACE
 __device__ unsigned long long g_nnf_trace[3 * 2048 * 16];
+#define NNF_CTA_ID (blockIdx.y * gridDim.x + blockIdx.x)
+#define NNF_TRACE_WRITE(row, i)                                                                                    \
+    do                                                                                                             \
+    {                                                                                                              \
+        unsigned long long t_;                                                                                     \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                     \
+        g_nnf_trace[((row) + NNF_CTA_ID) * 16 + (i)] = t_;                                                         \
+    } while (0)
 #define NNF_TRACE_POINT(i)                                                                                         \
     do                                                                                                             \
     {                                                                                                              \
-        if ((threadIdx.x == 0 || threadIdx.x == 256) && blockIdx.x < 2048)                                         \
-        {                                                                                                          \
-            unsigned long long t_;                                                                                 \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                 \
-            g_nnf_trace[((threadIdx.x ? 2048 : 0) + blockIdx.x) * 16 + (i)] = t_;                                  \
-        }                                                                                                          \
+        if ((threadIdx.x == 0 || threadIdx.x == 256) && NNF_CTA_ID < 2048)                                         \
+            NNF_TRACE_WRITE(threadIdx.x ? 2048 : 0, i);                                                            \
     } while (0)
 #define NNF_TRACE_PRODUCER(i)                                                                                      \
     do                                                                                                             \
     {                                                                                                              \
-        if ((threadIdx.x & 31) == 0 && blockIdx.x < 2048)                                                          \
-        {                                                                                                          \
-            unsigned long long t_;                                                                                 \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                 \
-            g_nnf_trace[(4096 + blockIdx.x) * 16 + (i)] = t_;                                                      \
-        }                                                                                                          \
+        if ((threadIdx.x & 31) == 0 && NNF_CTA_ID < 2048)                                                          \
+            NNF_TRACE_WRITE(4096, i);                                                                              \
     } while (0)
 #else
 #define NNF_TRACE_POINT(i)
@@ -254,16 +256,13 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     const int row_stride = whole_rows ? nwarps * 128 : nwarps * 128 + 64;
     const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * kMaxDepth;
 
-    const int split = blockIdx.x / p.ctas_per_split;
-    const int cta_in_split = blockIdx.x - split * p.ctas_per_split;
-    const int sb = p.slices / p.splits, sr = p.slices % p.splits; // K ranges differ by at most one slice
-    const int my_slices = sb + (split < sr ? 1 : 0);
-    const int slice0 = split * sb + min(split, sr);
+    // grid = (CTAs per split, splits); quotients come from the host: nothing here waits for an integer division
+    const int split = blockIdx.y, cta_in_split = blockIdx.x;
+    const int my_slices = p.slices_lo + (split < p.slices_rem ? 1 : 0); // K ranges differ by at most one slice
+    const int slice0 = split * p.slices_lo + min(split, p.slices_rem);
     const int slice = slice0 + warp;
     const bool has_slice = warp < my_slices;
-    const int nsteps = (cta_in_split < p.row_tiles)
-                           ? (p.row_tiles - cta_in_split + p.ctas_per_split - 1) / p.ctas_per_split
-                           : 0;
+    const int nsteps = p.steps_lo + (cta_in_split < p.steps_rem ? 1 : 0);
 
     // ---------------------------------------------------------------- producer (last warp of the CTA)
     // Per row tile: for every row that exists the CTA's K range of the packed weights, and the tile's quantisation
@@ -318,16 +317,14 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         // never wait for the requests to be issued.  The first ring-full leaves at once; slots are then refilled
         // as the arithmetic warps hand them back.
         NNF_TRACE_PRODUCER(0);
-        if (lane == 0)
+        if (lane < p.depth)
         {
-            for (int i = 0; i < p.depth; i++)
-            {
-                mbar_init(full_s + 8 * i, 1);
-                mbar_init(empty_s + 8 * i, (uint32_t)nwarps);
-            }
+            // lane i owns ring slot i: barrier operations take tens of nanoseconds each, so they run side by side
+            mbar_init(full_s + 8 * lane, 1);
+            mbar_init(empty_s + 8 * lane, (uint32_t)nwarps);
             fence_barrier_init();
-            for (int i = 0; i < p.depth && i < nsteps; i++)
-                expect(i);
+            if (lane < nsteps)
+                expect(lane);
         }
         NNF_TRACE_PRODUCER(1);
         __syncwarp();
@@ -916,13 +913,14 @@ cudaError_t ensure_smem(size_t smem)
 }
 
 template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT, bool FAST>
-cudaError_t launch(const GemvParams& p, int warps, int grid, size_t smem, cudaStream_t stream)
+cudaError_t launch(const GemvParams& p, int warps, int /*grid*/, size_t smem, cudaStream_t stream)
 {
     cudaError_t e = ensure_smem<WBITS, MB, XSPLIT, DUAL, EXACT, FAST>(smem);
     if (e != cudaSuccess)
         return e;
     (void)cudaGetLastError(); // do not inherit a stale error left behind by an unrelated earlier call
-    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT, FAST><<<grid, (warps + 1) * 32, smem, stream>>>(p);
+    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT, FAST>
+        <<<dim3(p.ctas_per_split, p.splits), (warps + 1) * 32, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -1022,6 +1020,8 @@ void fill_params(GemvParams& p, const nnf_b200_linear_desc& d, const nnf::GemvPl
     p.row_tiles = plan.row_tiles;
     p.splits = plan.splits;
     p.ctas_per_split = plan.ctas_per_split;
+    p.slices_lo = plan.slices / plan.splits, p.slices_rem = plan.slices % plan.splits;
+    p.steps_lo = plan.row_tiles / plan.ctas_per_split, p.steps_rem = plan.row_tiles % plan.ctas_per_split;
     p.x_f32 = d.x_dtype == NNF_B200_F32;
     p.y_f32 = d.y_dtype == NNF_B200_F32;
     p.scale_f32 = d.scale_dtype == NNF_B200_F32;
