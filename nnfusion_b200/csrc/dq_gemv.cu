@@ -39,7 +39,7 @@ namespace
 using namespace nnf::ptx;
 
 constexpr int kMaxWarps = 16;
-constexpr int kBatch = 8;            // most row tiles between two reductions over the warps
+constexpr int kBatch = 16;           // most row tiles between two reductions over the warps
 constexpr int kMaxDepth = 8;         // deepest load ring
 
 struct GemvParams
@@ -967,7 +967,7 @@ bool choose_ring(int sets, int mb, int warps, int tq, int pset_bytes, int steps,
     const size_t target = std::min((size_t)want_d * slot_bytes, (size_t)96 * 1024);
     int best_d = 0, best_b = 0;
     int last_b = 0;
-    for (int b : {want_b, 4, 2, 1})
+    for (int b : {want_b, 8, 4, 2, 1})
     {
         if (b > want_b || b == last_b)
             continue;
