@@ -34,7 +34,7 @@ if ROOT not in sys.path:
 L2_BYTES = 126e6
 # dram__bytes_read.sum + dram__bytes_write.sum of one dq_gemv_kernel launch on the decode_gemv workload
 # (ncu capture summarised in profiles/dq_gemv_decode_11008x4096.md).
-NCU_TRAFFIC_DECODE_GEMV = 23_493_888
+NCU_TRAFFIC_DECODE_GEMV = 23_483_392
 
 
 def measured_peaks():
@@ -256,7 +256,7 @@ def run_decode_gemv(args, torch, sampler_index):
                    "launch": "CUDA graph replay of the C-ABI calls"},
         "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(value / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_DECODE_GEMV,
-                     "peak_source": f"of {peaks['source']}", "kernel": "dq_gemv_kernel<4,1,false,false,false>"},
+                     "peak_source": f"of {peaks['source']}", "kernel": "dq_gemv_kernel<4,1,false,false,false,true>"},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": M * K * 2,
                 "d2h_bytes_per_step": M * N * 2, "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
                 "path": "pinned host x -> device, nnf_b200_linear, device y -> pinned host, stream sync, per step"},
