@@ -70,7 +70,13 @@ enum
     /* y = SiLU(x.W^T) * (x.W2^T) with a second weight set; replaces the fused
      * Sigmoid -> Multiply -> Multiply element-wise kernel
      * (src/nnfusion/core/kernels/cuda_gpu/kernels/elementwise_fused.cpp:42-189). */
-    NNF_B200_EPILOGUE_SILU_MUL = 2
+    NNF_B200_EPILOGUE_SILU_MUL = 2,
+    /* y = x.W^T + c with c an [M,N] tensor of y's element type, passed in the `bias`
+     * argument (it may be y itself).  cuda::MatMulAdd with its full-size addend
+     * (src/nnfusion/core/kernels/cuda_gpu/kernels/matmuladd.cpp:29-93; the operator's C is
+     * already broadcast to [M,N], src/nnfusion/core/operators/generic_op/generic_op_define/MatMulAdd.cpp:6-35):
+     * the residual connection of a decoder layer. */
+    NNF_B200_EPILOGUE_ADD = 3
 };
 
 enum
@@ -208,6 +214,43 @@ NNF_B200_API int nnf_b200_linear_static_scratch(void* stream, const nnf_b200_lin
                                                 const nnf_b200_qweight* w, const nnf_b200_qweight* w2,
                                                 const void* gain, const void* bias, void* y, char* errbuf,
                                                 size_t errbuf_len);
+
+/* ---- single-token (decode) attention over a key/value cache ---------------------------------------------
+ *
+ * out[h] = softmax(rot(q[h]) . K[kv(h)]^T * scale) . V[kv(h)] over cache rows 0 .. position, where row
+ * `position` is the new token: its key (through the rotary embedding) and value are written into the caches by
+ * the same call.  Stands in for the chain the reference runs for one decoding step of an attention layer:
+ * Slice / Negative / Concat / Multiply / Add (rotary embedding; element-wise emitters,
+ * src/nnfusion/core/kernels/cuda_gpu/kernels/elementwise.hpp:33-157), BatchMatMul with adj_y
+ * (src/nnfusion/core/kernels/cuda_gpu/kernels/batch_matmul.cpp:49-144; operator definition
+ * src/nnfusion/core/operators/generic_op/generic_op_define/BatchMatMul.cpp:6-50), Softmax
+ * (src/nnfusion/core/kernels/cuda_gpu/kernels/softmax.cpp:78-122) and a second BatchMatMul.
+ * Rotary embedding: element pairs (i, i + head_dim/2) of a head are rotated by position * base^(-2i/head_dim)
+ * ("rotate half": x*cos + concat(-x[half:], x[:half])*sin). */
+typedef struct nnf_b200_attn_desc
+{
+    int32_t heads;       /* query heads                                                     */
+    int32_t kv_heads;    /* key/value heads; heads must be a multiple (grouped queries)      */
+    int32_t head_dim;    /* 128                                                             */
+    int32_t capacity;    /* rows per head the caches can hold; position < capacity          */
+    int32_t position;    /* index of the new token = number of rows already in the caches   */
+    int32_t rotary;      /* non-zero: rotate q and the new key                              */
+    float rotary_base;   /* 0 -> 10000                                                      */
+    float softmax_scale; /* 0 -> 1/sqrt(head_dim)                                           */
+    int32_t splits;      /* ranges per head; 0 -> chosen by the library                     */
+    int32_t dtype;       /* NNF_B200_F16: q, k, v, caches and out                           */
+    int32_t reserved[4]; /* must be zero                                                    */
+} nnf_b200_attn_desc;
+
+/* Bytes of scratch the call needs (0 if none); zero-filled once before first use, left zeroed by every call.
+ * ctx may be NULL (a 148-SM device is assumed). */
+NNF_B200_API size_t nnf_b200_decode_attention_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_attn_desc* desc);
+
+/* q [heads][head_dim], k_new / v_new [kv_heads][head_dim], caches [kv_heads][capacity][head_dim],
+ * out [heads][head_dim]; all device pointers, 16-byte aligned.  Stream-ordered, never allocates. */
+NNF_B200_API int nnf_b200_decode_attention(nnf_b200_ctx* ctx, void* stream, const nnf_b200_attn_desc* desc,
+                                           const void* q, const void* k_new, const void* v_new, void* k_cache,
+                                           void* v_cache, void* out, void* workspace, size_t workspace_bytes);
 
 /* Reads (and clears) the device-side status word: 0, or NNF_B200_ETIMEDOUT when a
  * bounded wait inside a kernel gave up since the last query.  Synchronises the

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_PKG, "libnnf_b200.so")
 OK, EINVAL, ENOTSUP, ECUDA, EWORKSPACE, ETIMEDOUT, EALIGN = range(7)
 F32, F16 = 0, 1
 PROLOGUE_NONE, PROLOGUE_RMSNORM = 0, 1
-EPILOGUE_NONE, EPILOGUE_BIAS, EPILOGUE_SILU_MUL = 0, 1, 2
+EPILOGUE_NONE, EPILOGUE_BIAS, EPILOGUE_SILU_MUL, EPILOGUE_ADD = 0, 1, 2, 3
 KERNEL_AUTO, KERNEL_GEMV, KERNEL_GEMM = 0, 1, 2
 FLAG_EXACT_ZP = 1
 STATIC_SCRATCH_BYTES = 4 * 1024 * 1024
@@ -23,7 +23,8 @@ STATIC_SCRATCH_BYTES = 4 * 1024 * 1024
 EXPORTS = (
     "nnf_b200_init", "nnf_b200_free", "nnf_b200_strerror", "nnf_b200_last_error", "nnf_b200_sm_count",
     "nnf_b200_linear_workspace_bytes", "nnf_b200_workspace_reset", "nnf_b200_linear",
-    "nnf_b200_launch_count", "nnf_b200_pack_u4", "nnf_b200_device_status", "nnf_b200_linear_plan", "nnf_b200_linear_static_scratch",
+    "nnf_b200_launch_count", "nnf_b200_pack_u4", "nnf_b200_device_status", "nnf_b200_linear_plan",
+    "nnf_b200_linear_static_scratch", "nnf_b200_decode_attention_workspace_bytes", "nnf_b200_decode_attention",
 )
 
 
@@ -35,6 +36,15 @@ class LinearDesc(ctypes.Structure):
         ("prologue", ctypes.c_int32), ("epilogue", ctypes.c_int32), ("rms_eps", ctypes.c_float),
         ("kernel", ctypes.c_int32), ("split_k", ctypes.c_int32), ("flags", ctypes.c_int32),
         ("reserved", ctypes.c_int32 * 2),
+    ]
+
+
+class AttnDesc(ctypes.Structure):
+    _fields_ = [
+        ("heads", ctypes.c_int32), ("kv_heads", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("capacity", ctypes.c_int32), ("position", ctypes.c_int32), ("rotary", ctypes.c_int32),
+        ("rotary_base", ctypes.c_float), ("softmax_scale", ctypes.c_float),
+        ("splits", ctypes.c_int32), ("dtype", ctypes.c_int32), ("reserved", ctypes.c_int32 * 4),
     ]
 
 
@@ -75,5 +85,8 @@ def load() -> ctypes.CDLL:
     L.nnf_b200_launch_count.argtypes = [vp, ctypes.c_int]
     L.nnf_b200_launch_count.restype = ctypes.c_uint64
     L.nnf_b200_pack_u4.argtypes = [ctypes.c_char_p, sz, sz, ctypes.c_char_p]
+    L.nnf_b200_decode_attention_workspace_bytes.argtypes = [vp, ctypes.POINTER(AttnDesc)]
+    L.nnf_b200_decode_attention_workspace_bytes.restype = sz
+    L.nnf_b200_decode_attention.argtypes = [vp, vp, ctypes.POINTER(AttnDesc), vp, vp, vp, vp, vp, vp, vp, sz]
     _lib = L
     return L

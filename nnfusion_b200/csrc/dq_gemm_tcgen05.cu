@@ -75,6 +75,7 @@ struct GemmParams
     int M, N, K;
     int group, G, zp_row_bytes;
     int y_f32, scale_f32, has_bias;
+    int has_addend; // bias points at an [M,N] tensor of y's type instead of fp32 [N]
     int m_tiles;
     int fast_store; // fp16 y, N a multiple of 8, y 16-byte aligned: the tile is written in 16-byte pieces
 };
@@ -422,6 +423,9 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                             v = v * (1.0f / (1.0f + expf(-v))) * u;
                         }
                         v += bias;
+                        if (p.has_addend && m < p.M && nrow < p.N)
+                            v += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[(size_t)m * p.N + nrow]
+                                         : __half2float(reinterpret_cast<const __half*>(p.bias)[(size_t)m * p.N + nrow]);
                         if (p.fast_store)
                             sts16(xs_s + (uint32_t)((ml * 128 + r) * 2), __half_as_ushort(__float2half_rn(v)));
                         else if (m < p.M && nrow < p.N)
@@ -548,7 +552,8 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     p.zp_row_bytes = d.w_bits == 4 ? (p.G + 1) / 2 : p.G;
     p.y_f32 = d.y_dtype == NNF_B200_F32;
     p.scale_f32 = d.scale_dtype == NNF_B200_F32;
-    p.has_bias = bias != nullptr;
+    p.has_addend = d.epilogue == NNF_B200_EPILOGUE_ADD;
+    p.has_bias = bias != nullptr && !p.has_addend;
     p.m_tiles = (d.M + bx - 1) / bx;
     p.fast_store = !p.y_f32 && d.N % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0;
     const int n_tiles = (d.N + 127) / 128;

@@ -62,6 +62,7 @@ struct GemvParams
     int slices_lo, slices_rem; // slices / splits and its remainder
     int steps_lo, steps_rem;   // row_tiles / ctas_per_split and its remainder
     int x_f32, y_f32, scale_f32, rmsnorm, has_bias;
+    int has_addend; // bias points at an [M,N] tensor of y's type instead of fp32 [N]
     int depth;       // ring depth in row tiles
     int batch;       // row tiles between two reductions over the warps (<= kBatch)
     int tq;          // accumulator column pairs kept: 1, 2 or 4, at least ceil(min(M, 8) / 2); 4 when M > 8
@@ -722,7 +723,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     };
 
     // Final value of one output element from its summed parts.
-    auto finish = [&](float a0, float a1, float ssum, int n) -> float {
+    auto finish = [&](float a0, float a1, float ssum, int m, int n) -> float {
         float r = 1.f;
         if (p.rmsnorm)
             r = 1.0f / sqrtf(ssum / (float)p.K + p.eps);
@@ -735,6 +736,9 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         }
         if (p.has_bias)
             v += __ldg(p.bias + n);
+        if (p.has_addend)
+            v += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[(size_t)m * p.N + n]
+                         : __half2float(reinterpret_cast<const __half*>(p.bias)[(size_t)m * p.N + n]);
         return v;
     };
     auto store_y = [&](int m, int n, float v) {
@@ -775,7 +779,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                 const int n = (cta_in_split + (first + j) * p.ctas_per_split) * 16 + row;
                 if (m < p.M && n < p.N)
                     store_y(m, n, finish(sum_warps(j, 0, e), DUAL ? sum_warps(j, 1, e) : 0.f,
-                                         p.rmsnorm ? ss_cta[m] : 0.f, n));
+                                         p.rmsnorm ? ss_cta[m] : 0.f, m, n));
             }
         }
         else
@@ -837,7 +841,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                         if (p.rmsnorm)
                             ssum += __ldcg(slot + SETS * MB * 128 + m);
                     }
-                    store_y(m, n, finish(a0, a1, ssum, n));
+                    store_y(m, n, finish(a0, a1, ssum, m, n));
                 }
             }
         }
@@ -1026,7 +1030,8 @@ void fill_params(GemvParams& p, const nnf_b200_linear_desc& d, const nnf::GemvPl
     p.y_f32 = d.y_dtype == NNF_B200_F32;
     p.scale_f32 = d.scale_dtype == NNF_B200_F32;
     p.rmsnorm = d.prologue == NNF_B200_PROLOGUE_RMSNORM;
-    p.has_bias = bias != nullptr;
+    p.has_addend = d.epilogue == NNF_B200_EPILOGUE_ADD;
+    p.has_bias = bias != nullptr && !p.has_addend;
     p.eps = d.rms_eps;
     p.depth = plan.depth;
     p.batch = plan.batch;
@@ -1215,7 +1220,7 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
     if (d.M < 1 || d.N < 1 || d.K < 1 || (d.w_bits != 4 && d.w_bits != 8) || d.group_size < 0 ||
         (dual && (!w2 || !w2->wq || !w2->scale || !w2->zp)) || (!dual && w2) ||
         ((d.prologue == NNF_B200_PROLOGUE_RMSNORM) != (gain != nullptr)) ||
-        ((d.epilogue == NNF_B200_EPILOGUE_BIAS) != (bias != nullptr)))
+        ((d.epilogue == NNF_B200_EPILOGUE_BIAS || d.epilogue == NNF_B200_EPILOGUE_ADD) != (bias != nullptr)))
     {
         put_message(errbuf, errbuf_len, "malformed descriptor or operands that do not match it");
         return NNF_B200_EINVAL;

@@ -89,7 +89,7 @@ int validate(nnf_b200_ctx* ctx, const nnf_b200_linear_desc* d)
             return nnf::set_error(ctx, NNF_B200_EINVAL, "dtype fields must be NNF_B200_F32 or NNF_B200_F16");
     if (d->prologue != NNF_B200_PROLOGUE_NONE && d->prologue != NNF_B200_PROLOGUE_RMSNORM)
         return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown prologue");
-    if (d->epilogue < NNF_B200_EPILOGUE_NONE || d->epilogue > NNF_B200_EPILOGUE_SILU_MUL)
+    if (d->epilogue < NNF_B200_EPILOGUE_NONE || d->epilogue > NNF_B200_EPILOGUE_ADD)
         return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown epilogue");
     if (d->kernel < NNF_B200_KERNEL_AUTO || d->kernel > NNF_B200_KERNEL_GEMM)
         return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown kernel selector");
@@ -206,6 +206,41 @@ size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_l
     return nnf::gemm_workspace_bytes(ctx, *desc);
 }
 
+size_t nnf_b200_decode_attention_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_attn_desc* desc)
+{
+    std::string why;
+    if (!desc || nnf::attn_check(*desc, &why) != NNF_B200_OK)
+        return 0;
+    return nnf::attn_workspace_bytes(ctx, *desc);
+}
+
+int nnf_b200_decode_attention(nnf_b200_ctx* ctx, void* stream, const nnf_b200_attn_desc* desc, const void* q,
+                              const void* k_new, const void* v_new, void* k_cache, void* v_cache, void* out,
+                              void* workspace, size_t workspace_bytes)
+{
+    if (!ctx)
+        return NNF_B200_EINVAL;
+    if (!desc)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "null descriptor");
+    std::string why;
+    int rc = nnf::attn_check(*desc, &why);
+    if (rc != NNF_B200_OK)
+        return nnf::set_error(ctx, rc, why);
+    if (!q || !k_new || !v_new || !k_cache || !v_cache || !out)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "q, k_new, v_new, the caches and out must be non-null");
+    if (!aligned16(q) || !aligned16(k_new) || !aligned16(v_new) || !aligned16(k_cache) || !aligned16(v_cache) ||
+        !aligned16(out))
+        return nnf::set_error(ctx, NNF_B200_EALIGN, "attention operands must be 16-byte aligned");
+    const size_t need = nnf::attn_workspace_bytes(ctx, *desc);
+    if (need > 0 && (!workspace || workspace_bytes < need))
+        return nnf::set_error(ctx, NNF_B200_EWORKSPACE,
+                              "decode attention needs " + std::to_string(need) + " bytes of workspace");
+    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return nnf::set_error(ctx, NNF_B200_EALIGN, "workspace must be 256-byte aligned");
+    return nnf::attn_launch(ctx, static_cast<cudaStream_t>(stream), *desc, q, k_new, v_new, k_cache, v_cache, out,
+                            workspace);
+}
+
 int nnf_b200_linear_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc, int32_t out[8])
 {
     if (!desc || !out)
@@ -259,10 +294,11 @@ int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc*
         return nnf::set_error(ctx, NNF_B200_EINVAL, "RMSNorm prologue needs gain");
     if (d.prologue != NNF_B200_PROLOGUE_RMSNORM && gain)
         return nnf::set_error(ctx, NNF_B200_EINVAL, "gain given without the RMSNorm prologue");
-    if (d.epilogue == NNF_B200_EPILOGUE_BIAS && !bias)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "bias epilogue needs bias");
-    if (d.epilogue != NNF_B200_EPILOGUE_BIAS && bias)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "bias given without the bias epilogue");
+    const bool takes_bias = d.epilogue == NNF_B200_EPILOGUE_BIAS || d.epilogue == NNF_B200_EPILOGUE_ADD;
+    if (takes_bias && !bias)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "bias / add epilogue needs the bias argument");
+    if (!takes_bias && bias)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "bias given without a bias or add epilogue");
     if (!aligned16(x) || !aligned16(w->wq) || (dual && !aligned16(w2->wq)) || (gain && !aligned16(gain)))
         return nnf::set_error(ctx, NNF_B200_EALIGN, "x, wq and gain must be 16-byte aligned");
     if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u))

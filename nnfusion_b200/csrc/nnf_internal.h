@@ -68,4 +68,9 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
                 const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias,
                 void* y, void* workspace, size_t workspace_bytes);
 int gemm_configure(nnf_b200_ctx* ctx);
+
+int attn_check(const nnf_b200_attn_desc& d, std::string* why);
+size_t attn_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_attn_desc& d);
+int attn_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_attn_desc& d, const void* q, const void* k_new,
+                const void* v_new, void* k_cache, void* v_cache, void* out, void* workspace);
 } // namespace nnf

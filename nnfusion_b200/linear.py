@@ -116,8 +116,11 @@ class DequantDot:
     def __init__(self, weight: DeviceWeight, weight2: Optional[DeviceWeight] = None,
                  gain: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
                  eps: float = 1e-6, y_dtype: Optional[torch.dtype] = None, kernel: int = L.KERNEL_AUTO,
-                 split_k: int = 0, flags: int = 0, ctx: Optional[Context] = None):
+                 split_k: int = 0, flags: int = 0, ctx: Optional[Context] = None, add: bool = False):
         self.w, self.w2, self.gain, self.bias = weight, weight2, gain, bias
+        self.add = add  # y = x.W^T + addend, the addend ([M,N], y's dtype) being given at call time
+        if add and (bias is not None or weight2 is not None):
+            raise ValueError("the add epilogue excludes bias and the SiLU*mul epilogue")
         self.eps, self.y_dtype, self.kernel, self.split_k, self.flags = eps, y_dtype, kernel, split_k, flags
         self.ctx = ctx or default_context(weight.wq.device.index or 0)
         if weight2 is not None and (weight2.N, weight2.K, weight2.bits, weight2.group) != \
@@ -141,7 +144,8 @@ class DequantDot:
         d.scale_dtype = _DT[self.w.scale.dtype]
         d.prologue = L.PROLOGUE_RMSNORM if self.gain is not None else L.PROLOGUE_NONE
         d.epilogue = (L.EPILOGUE_SILU_MUL if self.w2 is not None
-                      else L.EPILOGUE_BIAS if self.bias is not None else L.EPILOGUE_NONE)
+                      else L.EPILOGUE_BIAS if self.bias is not None
+                      else L.EPILOGUE_ADD if self.add else L.EPILOGUE_NONE)
         d.rms_eps = self.eps
         d.kernel = self.kernel
         d.split_k = self.split_k
@@ -163,24 +167,31 @@ class DequantDot:
                 self._ws[key] = ws
         return self._ws[key]
 
-    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 addend: Optional[torch.Tensor] = None) -> torch.Tensor:
         if x.dim() != 2 or x.shape[1] != self.w.K or not x.is_contiguous():
             raise ValueError(f"x must be a contiguous [M, {self.w.K}] tensor")
         M = x.shape[0]
         d = self.desc(M, x.dtype)
         if out is None:
             out = torch.empty((M, self.w.N), dtype=self.y_dtype or x.dtype, device=x.device)
+        if self.add != (addend is not None):
+            raise ValueError("addend must be given exactly when the node was built with add=True")
+        if addend is not None and (addend.shape != out.shape or addend.dtype != out.dtype
+                                   or not addend.is_contiguous()):
+            raise ValueError("addend must be a contiguous [M, N] tensor of the output's dtype")
         ws = self.workspace(d)
-        self.run_raw(d, x.data_ptr(), out.data_ptr(), ws)
+        self.run_raw(d, x.data_ptr(), out.data_ptr(), ws, addend.data_ptr() if addend is not None else None)
         return out
 
-    def run_raw(self, d: L.LinearDesc, x_ptr: int, y_ptr: int, ws: Optional[torch.Tensor]) -> None:
+    def run_raw(self, d: L.LinearDesc, x_ptr: int, y_ptr: int, ws: Optional[torch.Tensor],
+                addend_ptr: Optional[int] = None) -> None:
         """The C-ABI call itself, on the current stream, with raw device addresses."""
         stream = torch.cuda.current_stream().cuda_stream
         rc = self.ctx.lib.nnf_b200_linear(
             self.ctx.handle, stream, ctypes.byref(d), x_ptr, ctypes.byref(self._abi_w),
             ctypes.byref(self._abi_w2) if self._abi_w2 is not None else None,
             self.gain.data_ptr() if self.gain is not None else None,
-            self.bias.data_ptr() if self.bias is not None else None,
+            self.bias.data_ptr() if self.bias is not None else addend_ptr,
             y_ptr, ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0)
         self.ctx.check(rc)
