@@ -304,10 +304,55 @@ def extra_measurements(torch, budget_s=60.0):
                       "frac_of_bf16_burst_peak": round(tf / peaks["bf16_tflops"], 4),
                       "frac_of_bf16_sustained_peak": round(tf / peaks["bf16_tflops_sustained"], 4)}
 
+    def layer7b(name, copies=2, steps=200):
+        """Configuration 4: one 7B-shaped decoder layer at decode time, 2048 cached rows, the token at position
+        2048.  Algorithmic bytes: packed weights + scales + zero-points of the 7 projections, both caches read
+        once, activations.  Rotation over `copies` layers (weights + caches 139 MB each) defeats L2."""
+        if time.time() - t_begin > budget_s:
+            return
+        from nnfusion_b200.decoder_layer import DecoderLayer
+        H, I, heads, pos = 4096, 11008, 32, 2048
+        layers = []
+        for _ in range(copies):
+            W = [rand_device_weight(torch, n, k) for n, k in ((H, H), (H, H), (H, H), (H, H), (I, H), (I, H), (H, I))]
+            g1, g2 = (torch.rand(H, device="cuda") * 0.2 + 0.9 for _ in range(2))
+            layer = DecoderLayer(*W, g1, g2, heads=heads, kv_heads=heads, capacity=pos + 1)
+            layer.attn.k_cache.normal_()
+            layer.attn.v_cache.normal_()
+            layers.append(layer)
+        x = torch.randn(1, H, device="cuda").to(torch.float16)
+        y = torch.empty_like(x)
+        ms = timed_graph_steps(torch, [(lambda l=l: l(x, pos, out=y)) for l in layers], steps, 3)
+        kv = 2 * heads * pos * 128 * 2
+        b = layers[0].weight_bytes + kv + 2 * (3 * H + H + H + 2 * H + I + I + H)
+        gbs = b * steps / (ms * 1e-3) / 1e9
+        also[name] = {"us": round(ms * 1e3 / steps, 2), "GB/s": round(gbs, 1), "launches_per_layer": layers[0].launches,
+                      "algorithmic_bytes": b, "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
+
+    def attention(name, copies=6, steps=600):
+        if time.time() - t_begin > budget_s:
+            return
+        from nnfusion_b200.attention import DecodeAttention
+        heads, pos = 32, 2048
+        ops = []
+        for _ in range(copies):
+            op = DecodeAttention(heads, heads, 128, pos + 1)
+            op.k_cache.normal_()
+            op.v_cache.normal_()
+            ops.append(op)
+        q, k, v = (torch.randn(heads * 128, device="cuda").to(torch.float16) for _ in range(3))
+        out = torch.empty((1, heads * 128), dtype=torch.float16, device="cuda")
+        ms = timed_graph_steps(torch, [(lambda op=op: op(q, k, v, pos, out=out)) for op in ops], steps, 3)
+        b = 2 * heads * (pos + 1) * 128 * 2 + 4 * heads * 128 * 2
+        gbs = b * steps / (ms * 1e-3) / 1e9
+        also[name] = {"us": round(ms * 1e3 / steps, 2), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
+
     gemv("decode_gemv_down_4096x11008", 1, 4096, 11008, 12)
     gemv("config1_u8_perchannel_f32_m16_4096x4096", 16, 4096, 4096, 12, bits=8, group=4096, xdt=torch.float32, sdt=torch.float32)
     gemv("mlp70b_gate_up_silu_m1_28672x8192", 1, 28672, 8192, 2, dual=True, steps=100)
     gemv("mlp70b_down_m1_8192x28672", 1, 8192, 28672, 3, steps=150)
+    attention("decode_attention_32x2048x128")
+    layer7b("layer7b_decode_pos2048")
     for M in (256, 1024, 4096):
         gemm(f"prefill_gemm_up_m{M}_11008x4096", M, 11008, 4096)
     gemm("prefill_gemm_down_m4096_4096x11008", 4096, 4096, 11008)

@@ -8,8 +8,8 @@
 // (src/nnfusion/core/kernels/cuda_gpu/kernels/softmax.cpp:78-122) and a second batched GEMM for P.V; the BERT-style
 // fused Attention op (src/nnfusion/core/kernels/cuda_gpu/kernels/attention.cpp:13-152) stops at 1024 positions.
 //
-// The kernel is HBM-bound: every cache row is read once (16-byte loads, 32 rows = 16 KB in flight per CTA, several
-// CTAs per SM).  The positions of a head are cut into `splits` contiguous ranges, one CTA each; a CTA keeps a running
+// The kernel is HBM-bound: every cache row is read once (16-byte loads into two register buffers of 32 rows each:
+// 32 KB in flight per CTA, four CTAs per SM).  The positions of a head are cut into `splits` contiguous ranges, one CTA each; a CTA keeps a running
 // maximum / sum / weighted value sum (fp32) over its range, stores them, takes a ticket, and the CTA that arrives last
 // for a head combines the ranges in a fixed order, so results are bitwise repeatable and nothing ever waits.
 #include <cuda_fp16.h>
@@ -53,7 +53,7 @@ __device__ __forceinline__ float rotate(const float* x, int d, int position, flo
     return d < 64 ? x[d] * cs - x[d + 64] * sn : x[d] * cs + x[d - 64] * sn;
 }
 
-__global__ void __launch_bounds__(kThreads) decode_attention_kernel(const AttnParams p)
+__global__ void __launch_bounds__(kThreads, 4) decode_attention_kernel(const AttnParams p)
 {
     __shared__ float q_s[kD];      // rotated q, already multiplied by the softmax scale
     __shared__ float raw_s[kD];    // staging for the rotary embedding
@@ -70,8 +70,30 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const AttnPa
     const int begin = split * p.chunk, end = min(begin + p.chunk, n_rows);
     const bool owns_new = begin <= p.position && p.position < end;
 
+    // ---- q first (a few bytes that everything waits for), then the first two passes of cache rows: nothing below
+    // depends on those until the scores
+    const float q_raw = __half2float(p.q[(size_t)head * kD + tid]);
+    const __half* kbase = p.k_cache + (size_t)kvh * p.capacity * kD + 8 * dg;
+    const __half* vbase = p.v_cache + (size_t)kvh * p.capacity * kD + 8 * dg;
+    const int my_row = warp * 2 + half; // row of this thread within a group of 8
+    // Two register buffers of one pass (32 rows) each.  Rows past the end of the range read as zeros; the new row
+    // is not in the cache yet and is patched in when it is used.
+    uint4 kraw[2][kRounds], vraw[2][kRounds];
+    auto load_pass = [&](uint4 (&kb)[kRounds], uint4 (&vb)[kRounds], int row0) {
+#pragma unroll
+        for (int r = 0; r < kRounds; r++)
+        {
+            const int row = row0 + r * 8 + my_row;
+            const bool live = row < end && row != p.position;
+            kb[r] = live ? __ldcs(reinterpret_cast<const uint4*>(kbase + (size_t)row * kD)) : make_uint4(0u, 0u, 0u, 0u);
+            vb[r] = live ? __ldcs(reinterpret_cast<const uint4*>(vbase + (size_t)row * kD)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    load_pass(kraw[0], vraw[0], begin);
+    load_pass(kraw[1], vraw[1], begin + kRowsPerPass);
+
     // ---- q (and, in the CTA whose range holds the new row, k) through the rotary embedding
-    raw_s[tid] = __half2float(p.q[(size_t)head * kD + tid]);
+    raw_s[tid] = q_raw;
     __syncthreads();
     q_s[tid] = (p.rotary ? rotate(raw_s, tid, p.position, p.log2_base) : raw_s[tid]) * p.scale;
     __syncthreads();
@@ -96,36 +118,19 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const AttnPa
 #pragma unroll
     for (int j = 0; j < 8; j++)
         acc[j] = 0.f;
-    const __half* kbase = p.k_cache + (size_t)kvh * p.capacity * kD + 8 * dg;
-    const __half* vbase = p.v_cache + (size_t)kvh * p.capacity * kD + 8 * dg;
-    for (int row0 = begin; row0 < end; row0 += kRowsPerPass)
-    {
-        uint4 kraw[kRounds], vraw[kRounds];
-        int rows[kRounds];
-#pragma unroll
-        for (int r = 0; r < kRounds; r++)
-        {
-            const int row = row0 + r * 8 + warp * 2 + half;
-            rows[r] = row;
-            if (row < end && row != p.position)
-            {
-                kraw[r] = __ldcs(reinterpret_cast<const uint4*>(kbase + (size_t)row * kD));
-                vraw[r] = __ldcs(reinterpret_cast<const uint4*>(vbase + (size_t)row * kD));
-            }
-            else if (row == p.position && row < end)
-            {
-                kraw[r] = *reinterpret_cast<const uint4*>(knew_s + 8 * dg);
-                vraw[r] = *reinterpret_cast<const uint4*>(p.v_new + (size_t)kvh * kD + 8 * dg);
-            }
-            else
-                kraw[r] = vraw[r] = make_uint4(0u, 0u, 0u, 0u);
-        }
+    auto consume = [&](uint4 (&kb)[kRounds], uint4 (&vb)[kRounds], int row0) {
         float s[kRounds];
         float m_pass = -INFINITY;
 #pragma unroll
         for (int r = 0; r < kRounds; r++)
         {
-            const __half2* kh = reinterpret_cast<const __half2*>(&kraw[r]);
+            const int row = row0 + r * 8 + my_row;
+            if (row == p.position && row < end)
+            {
+                kb[r] = *reinterpret_cast<const uint4*>(knew_s + 8 * dg);
+                vb[r] = *reinterpret_cast<const uint4*>(p.v_new + (size_t)kvh * kD + 8 * dg);
+            }
+            const __half2* kh = reinterpret_cast<const __half2*>(&kb[r]);
             float d = 0.f;
 #pragma unroll
             for (int j = 0; j < 4; j++)
@@ -138,7 +143,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const AttnPa
             d += __shfl_xor_sync(0xffffffffu, d, 4);
             d += __shfl_xor_sync(0xffffffffu, d, 2);
             d += __shfl_xor_sync(0xffffffffu, d, 1);
-            s[r] = rows[r] < end ? d : -INFINITY;
+            s[r] = row < end ? d : -INFINITY;
             m_pass = fmaxf(m_pass, s[r]);
         }
         // maximum of the pass over the whole CTA (every pass has at least one row)
@@ -159,7 +164,7 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const AttnPa
         {
             const float w = expf(s[r] - m_new); // 0 for rows past the end
             l_run += w;
-            const __half2* vh = reinterpret_cast<const __half2*>(&vraw[r]);
+            const __half2* vh = reinterpret_cast<const __half2*>(&vb[r]);
 #pragma unroll
             for (int j = 0; j < 4; j++)
             {
@@ -169,6 +174,20 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const AttnPa
             }
         }
         m_run = m_new;
+    };
+    // two passes per trip: while one buffer is consumed the other one's rows are on their way, and a buffer is
+    // asked to be refilled as soon as it has been consumed
+    for (int row0 = begin; row0 < end; row0 += 2 * kRowsPerPass)
+    {
+        consume(kraw[0], vraw[0], row0);
+        if (row0 + 2 * kRowsPerPass < end)
+            load_pass(kraw[0], vraw[0], row0 + 2 * kRowsPerPass);
+        if (row0 + kRowsPerPass < end)
+        {
+            consume(kraw[1], vraw[1], row0 + kRowsPerPass);
+            if (row0 + 3 * kRowsPerPass < end)
+                load_pass(kraw[1], vraw[1], row0 + 3 * kRowsPerPass);
+        }
     }
 
     // ---- sums over the CTA: the two rows of a warp, then the four warps (fixed order)
@@ -230,15 +249,18 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(const AttnPa
     p.out[(size_t)head * kD + tid] = __float2half_rn(o / l_all);
 }
 
-// Ranges per head: enough CTAs to fill the machine several times over (about 7 CTAs of this kernel fit on an SM),
-// at least 16 rows each.
+// Ranges per head: as many CTAs as the machine holds at once (four per SM), at least 16 rows each.
 int pick_splits(const nnf_b200_ctx* ctx, const nnf_b200_attn_desc& d)
 {
     const int sms = ctx ? ctx->sm_count : 148;
     const int rows = d.position + 1;
-    int splits = d.splits > 0 ? d.splits : std::max(1, (sms * 7) / d.heads);
-    splits = std::min(splits, std::max(1, rows / 16));
-    return std::min(splits, 1024);
+    if (d.splits > 0)
+        return std::min(std::min(d.splits, std::max(1, rows / 16)), 1024);
+    // ranges of whole passes (32 rows), as many as fill the machine once
+    const int target = std::max(1, (sms * 4) / d.heads); // four CTAs of this kernel fit on an SM
+    const int passes = std::max(1, (rows + target * kRowsPerPass / 2) / (target * kRowsPerPass));
+    const int chunk = passes * kRowsPerPass;
+    return std::min((rows + chunk - 1) / chunk, 1024);
 }
 } // namespace
 
@@ -285,7 +307,8 @@ int attn_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_attn_desc
     p.log2_base = log2f(d.rotary_base > 0.f ? d.rotary_base : 10000.f);
     p.splits = pick_splits(ctx, d);
     const int rows = d.position + 1;
-    p.chunk = (rows + p.splits - 1) / p.splits;
+    // whole passes per range; ranges left without rows store an empty partial result that the combine skips
+    p.chunk = ((rows + p.splits - 1) / p.splits + kRowsPerPass - 1) / kRowsPerPass * kRowsPerPass;
     if (p.splits > 1)
     {
         const size_t cnt = ((size_t)d.heads * sizeof(unsigned) + 255) / 256 * 256;

@@ -96,6 +96,19 @@ class DeviceWeight:
                             torch.from_numpy(np.ascontiguousarray(w.scale)).to(device),
                             torch.from_numpy(np.ascontiguousarray(w.zpq)).to(device))
 
+    @staticmethod
+    def stack_rows(parts: "list[DeviceWeight]") -> "DeviceWeight":
+        """Weights that read the same activations, concatenated along N (a constant-folding-time Concat):
+        q, k and v of an attention layer become one matrix and one launch."""
+        first = parts[0]
+        if any((p.K, p.bits, p.group, p.scale.dtype) != (first.K, first.bits, first.group, first.scale.dtype)
+               for p in parts):
+            raise ValueError("stacked weights must share K, bit width, group size and scale type")
+        return DeviceWeight(sum(p.N for p in parts), first.K, first.bits, first.group,
+                            torch.cat([p.wq for p in parts]).contiguous(),
+                            torch.cat([p.scale for p in parts]).contiguous(),
+                            torch.cat([p.zp for p in parts]).contiguous())
+
     def abi(self) -> L.QWeight:
         return L.QWeight(self.wq.data_ptr(), self.scale.data_ptr(), self.zp.data_ptr())
 
