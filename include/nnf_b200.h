@@ -252,6 +252,27 @@ NNF_B200_API int nnf_b200_decode_attention(nnf_b200_ctx* ctx, void* stream, cons
                                            const void* q, const void* k_new, const void* v_new, void* k_cache,
                                            void* v_cache, void* out, void* workspace, size_t workspace_bytes);
 
+/* ---- one-shot sum all-reduce of a small fp16 tensor over peer memory -------------------------------------
+ *
+ * out = sum over ranks of bufs[r], added in rank order in fp32 and rounded once, so that every rank gets the
+ * same bits.  Stands in for the NCCL call behind cuda::SuperScalerAllReduce
+ * (src/nnfusion/core/kernels/cuda_gpu/kernels/allreduce.cpp:18-98;
+ * src/tools/nnfusion/templates/super_scaler/super_scaler.cu:244-277) at the shard boundary of a tensor-parallel
+ * layer, where the tensor is a few KB per rank and a ring is all latency.
+ *
+ * bufs[r] / flags[r] (host arrays of `world` entries, world <= 8): rank r's addend buffer and flag words as mapped
+ * into THIS process (peer pointers for r != rank; memory every rank has mapped, e.g. from cuMemMap or CUDA IPC).
+ * Every rank calls with the same count and epoch.  Rules for the caller: flags start zeroed and are never written
+ * by anyone else; epoch starts at 1 and grows by one per call; the addend buffers alternate between two sets from
+ * call to call (a rank may be one call ahead of a peer that is still reading); the addend of this call must be
+ * complete in stream order before the call.  count: fp16 elements, a multiple of 8, bufs 16-byte aligned.
+ * A rank whose peers never call gives up after about 0.1 s, writes nothing, and nnf_b200_device_status then
+ * reports NNF_B200_ETIMEDOUT. */
+NNF_B200_API size_t nnf_b200_allreduce_flag_bytes(size_t count);
+NNF_B200_API int nnf_b200_allreduce_oneshot(nnf_b200_ctx* ctx, void* stream, int rank, int world,
+                                            const void* const* bufs, void* const* flags, size_t count, void* out,
+                                            uint32_t epoch);
+
 /* Reads (and clears) the device-side status word: 0, or NNF_B200_ETIMEDOUT when a
  * bounded wait inside a kernel gave up since the last query.  Synchronises the
  * stream; meant for tests and debugging, not for the hot path. */

@@ -25,6 +25,7 @@ EXPORTS = (
     "nnf_b200_linear_workspace_bytes", "nnf_b200_workspace_reset", "nnf_b200_linear",
     "nnf_b200_launch_count", "nnf_b200_pack_u4", "nnf_b200_device_status", "nnf_b200_linear_plan",
     "nnf_b200_linear_static_scratch", "nnf_b200_decode_attention_workspace_bytes", "nnf_b200_decode_attention",
+    "nnf_b200_allreduce_flag_bytes", "nnf_b200_allreduce_oneshot",
 )
 
 
@@ -88,5 +89,9 @@ def load() -> ctypes.CDLL:
     L.nnf_b200_decode_attention_workspace_bytes.argtypes = [vp, ctypes.POINTER(AttnDesc)]
     L.nnf_b200_decode_attention_workspace_bytes.restype = sz
     L.nnf_b200_decode_attention.argtypes = [vp, vp, ctypes.POINTER(AttnDesc), vp, vp, vp, vp, vp, vp, vp, sz]
+    L.nnf_b200_allreduce_flag_bytes.argtypes = [sz]
+    L.nnf_b200_allreduce_flag_bytes.restype = sz
+    L.nnf_b200_allreduce_oneshot.argtypes = [vp, vp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(vp),
+                                             ctypes.POINTER(vp), sz, vp, ctypes.c_uint32]
     _lib = L
     return L

@@ -69,6 +69,10 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
                 void* y, void* workspace, size_t workspace_bytes);
 int gemm_configure(nnf_b200_ctx* ctx);
 
+size_t allreduce_flag_bytes(size_t count);
+int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world, const void* const* bufs,
+                     void* const* flags, size_t count, void* out, uint32_t epoch);
+
 int attn_check(const nnf_b200_attn_desc& d, std::string* why);
 size_t attn_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_attn_desc& d);
 int attn_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_attn_desc& d, const void* q, const void* k_new,

@@ -1,0 +1,143 @@
+// One-shot sum all-reduce of a small fp16 tensor over peer memory (NVLink / NVSwitch), for the shard boundary of a
+// tensor-parallel layer at decode sizes (a few KB to a few hundred KB per rank).
+//
+// Stands in for the NCCL call behind the reference's only collective, cuda::SuperScalerAllReduce
+// (src/nnfusion/core/kernels/cuda_gpu/kernels/allreduce.cpp:18-98; the call itself in
+// src/tools/nnfusion/templates/super_scaler/super_scaler.cu:244-277), where a ring over a few kilobytes is all
+// latency.  Every rank keeps its addend in a buffer that all ranks have mapped (plain peer pointers; no multicast,
+// no TMA): a CTA tells every peer "my buffer holds call number `epoch`" with one flag store per peer, waits until every
+// peer has said the same to it, then reads its slice of all buffers with 16-byte peer loads, adds them in rank
+// order in fp32 (so every rank gets the same bits) and writes the sum to local memory.
+//
+// Flags are never reset: they only grow (one 32-bit word per CTA and sender on the receiving rank), a wait is
+// "flag >= epoch".  The caller alternates between two buffers from call to call: a rank may run one call ahead of a
+// peer that is still reading, never two (its next wait needs that peer's next flag).  Every wait is bounded; a wait
+// that gives up raises the context's device status word and the CTA writes nothing.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <string>
+
+#include "nnf_internal.h"
+
+namespace
+{
+constexpr int kMaxRanks = 8;
+constexpr int kArThreads = 256;
+constexpr uint32_t kArSpin = 1u << 21; // polls of about 50 ns each: gives up after roughly 0.1 s
+
+struct ArParams
+{
+    const uint4* bufs[kMaxRanks]; // this call's buffer of every rank (own included), as mapped on this rank
+    uint32_t* flags[kMaxRanks];   // flag words of every rank: [CTA][sender]
+    uint4* out;
+    int* status;
+    int rank, world;
+    uint32_t vecs; // 16-byte pieces (8 fp16) in the tensor
+    uint32_t epoch;
+};
+
+__device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(const ArParams p)
+{
+    __shared__ int ok_s;
+    const int tid = threadIdx.x;
+    if (tid == 0)
+        ok_s = 1;
+    __syncthreads();
+    // thread r talks to rank r: announce, then wait for its announcement
+    if (tid < p.world && tid != p.rank)
+    {
+        store_release_sys(p.flags[tid] + blockIdx.x * kMaxRanks + p.rank, p.epoch);
+        const uint32_t* mine = p.flags[p.rank] + blockIdx.x * kMaxRanks + tid;
+        bool seen = false;
+        for (uint32_t i = 0; i < kArSpin && !seen; i++)
+        {
+            seen = (int32_t)(load_acquire_sys(mine) - p.epoch) >= 0;
+            if (!seen)
+                __nanosleep(40);
+        }
+        if (!seen)
+        {
+            ok_s = 0;
+            atomicExch(p.status, 1);
+        }
+    }
+    __syncthreads();
+    if (!ok_s)
+        return;
+    const uint32_t v = blockIdx.x * kArThreads + tid;
+    if (v >= p.vecs)
+        return;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+        acc[j] = 0.f;
+    uint4 part[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; r++)
+        if (r < p.world)
+            part[r] = __ldcv(p.bufs[r] + v); // volatile-class load: never served from a stale line
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; r++)
+        if (r < p.world)
+        {
+            const __half2* h = reinterpret_cast<const __half2*>(&part[r]);
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+            {
+                const float2 f = __half22float2(h[j]);
+                acc[2 * j] += f.x, acc[2 * j + 1] += f.y;
+            }
+        }
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+    p.out[v] = o;
+}
+} // namespace
+
+namespace nnf
+{
+size_t allreduce_flag_bytes(size_t count)
+{
+    const size_t vecs = (count + 7) / 8;
+    const size_t ctas = (vecs + kArThreads - 1) / kArThreads;
+    return ctas * kMaxRanks * sizeof(uint32_t);
+}
+
+int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world, const void* const* bufs,
+                     void* const* flags, size_t count, void* out, uint32_t epoch)
+{
+    ArParams p{};
+    for (int r = 0; r < world; r++)
+    {
+        p.bufs[r] = static_cast<const uint4*>(bufs[r]);
+        p.flags[r] = static_cast<uint32_t*>(flags[r]);
+    }
+    p.out = static_cast<uint4*>(out);
+    p.status = ctx->dev_status;
+    p.rank = rank, p.world = world;
+    p.vecs = (uint32_t)(count / 8);
+    p.epoch = epoch;
+    const unsigned ctas = (p.vecs + kArThreads - 1) / kArThreads;
+    (void)cudaGetLastError();
+    oneshot_allreduce_kernel<<<ctas, kArThreads, 0, stream>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return set_error(ctx, NNF_B200_ECUDA, std::string("oneshot_allreduce launch: ") + cudaGetErrorString(e));
+    ctx->launches++;
+    return NNF_B200_OK;
+}
+} // namespace nnf

@@ -43,15 +43,78 @@ def mlp_shapes(hidden: int, inter: int, world: int) -> Tuple[Tuple[int, int], Tu
     return (inter // world, hidden), (hidden, inter // world)
 
 
+class PeerAllReduce:
+    """Sum all-reduce of a small fp16 tensor through ``nnf_b200_allreduce_oneshot``: every rank's addend lives in
+    memory that all ranks of the node have mapped (``torch.distributed._symmetric_memory``, i.e. ``cuMemMap`` of
+    exported handles -- plumbing only), the kernel reads the peers' copies directly.
+
+    ``addend(M)`` returns the view this rank must fill for the next call (two buffers alternate from call to call);
+    ``__call__`` reduces what was written there into ``out``.
+    """
+
+    def __init__(self, max_elems: int, group, ctx=None):
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib as L
+        from .linear import default_context
+
+        self.torch, self.ctypes = torch, ctypes
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.ctx = ctx or default_context(dev.index)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("the one-shot all-reduce serves up to 8 ranks of one node")
+        self.max_elems = (max_elems + 7) // 8 * 8
+        self.data_bytes = self.max_elems * 2
+        flag_bytes = int(self.ctx.lib.nnf_b200_allreduce_flag_bytes(self.max_elems))
+        self.flag_off = 2 * self.data_bytes
+        total = (self.flag_off + flag_bytes + 255) // 256 * 256
+        self.mem = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self.mem.zero_()                       # flags start at zero on every rank ...
+        torch.cuda.synchronize()
+        self.handle = symm_mem.rendezvous(self.mem, group)
+        dist.barrier(group)                    # ... before anybody's first flag store can arrive
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.epoch = 0
+        vp = ctypes.c_void_p
+        self._flags = (vp * self.world)(*[p + self.flag_off for p in self.ptrs])
+        self._bufs = [(vp * self.world)(*[p + half * self.data_bytes for p in self.ptrs]) for half in (0, 1)]
+
+    def addend(self, shape):
+        """The buffer this rank fills for the next call, viewed as fp16 ``shape``."""
+        n = 1
+        for d in shape:
+            n *= d
+        if n > self.max_elems or n % 8:
+            raise ValueError("tensor too large for this all-reduce, or not a multiple of 8 elements")
+        half = (self.epoch + 1) & 1
+        return self.mem[half * self.data_bytes: half * self.data_bytes + 2 * n].view(self.torch.float16).view(shape)
+
+    def __call__(self, out):
+        self.epoch += 1
+        half = self.epoch & 1
+        stream = self.torch.cuda.current_stream().cuda_stream
+        rc = self.ctx.lib.nnf_b200_allreduce_oneshot(self.ctx.handle, stream, self.rank, self.world, self._bufs[half],
+                                                     self._flags, out.numel(), out.data_ptr(), self.epoch)
+        self.ctx.check(rc)
+        return out
+
+
 class ShardedMLP:
     """This rank's part of y = down(SiLU(gate(x)) * up(x)), followed by the all-reduce.
 
     ``gate``/``up``/``down`` are device weights already sharded for this rank (``DeviceWeight``); ``group`` is the
     ``torch.distributed`` process group, or None for a single GPU.  ``gain`` enables the fused RMSNorm prologue of
-    the gate/up linear (small-M kernel only).
+    the gate/up linear (small-M kernel only).  ``reduce``: "nccl" (``torch.distributed.all_reduce``) or "peer" (the
+    one-shot kernel over peer memory, fp16 outputs of at most ``peer_max_rows`` rows).
     """
 
-    def __init__(self, gate, up, down, group=None, gain=None, eps: float = 1e-6):
+    def __init__(self, gate, up, down, group=None, gain=None, eps: float = 1e-6, reduce: str = "nccl",
+                 peer_max_rows: int = 16):
         import torch
 
         from .linear import DequantDot
@@ -63,6 +126,10 @@ class ShardedMLP:
         self.hidden = down.N
         self._h = {}
         self._y = {}
+        if reduce not in ("nccl", "peer"):
+            raise ValueError("reduce must be 'nccl' or 'peer'")
+        self.peer = PeerAllReduce(peer_max_rows * down.N, group) if (reduce == "peer" and group is not None) else None
+        self.peer_max_rows = peer_max_rows
 
     def buffers(self, M: int, dtype, device):
         key = (M, dtype)
@@ -74,6 +141,10 @@ class ShardedMLP:
     def __call__(self, x):
         h, y = self.buffers(x.shape[0], x.dtype, x.device)
         self.gate_up(x, out=h)      # [M, inter / world]: SiLU(gate) * up, local
+        if self.peer is not None and x.shape[0] <= self.peer_max_rows and x.dtype == self.torch.float16:
+            part = self.peer.addend((x.shape[0], self.hidden))
+            self.down(h, out=part)  # partial sum over this rank's K shard, straight into peer-visible memory
+            return self.peer(y)
         self.down(h, out=y)         # [M, hidden]: partial sum over this rank's K shard
         if self.group is not None:
             self.torch.distributed.all_reduce(y, group=self.group)

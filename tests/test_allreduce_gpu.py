@@ -1,0 +1,90 @@
+"""The one-shot all-reduce kernel on ONE GPU: all "ranks" are buffers of this GPU and the peers' flags are written by
+the host beforehand, so the kernel under test never waits for another launch.  (The real thing, two processes on two
+GPUs, is in test_tp_gpu.py.)"""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(world, n, seed=0):
+    import torch
+    from nnfusion_b200.linear import default_context
+
+    ctx = default_context(0)
+    rng = np.random.Generator(np.random.PCG64(seed))
+    parts = [rng.standard_normal(n).astype(np.float16) for _ in range(world)]
+    bufs = [torch.from_numpy(p).cuda() for p in parts]
+    fb = int(ctx.lib.nnf_b200_allreduce_flag_bytes(n))
+    flags = [torch.zeros(fb // 4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    vp = ctypes.c_void_p
+    return ctx, parts, bufs, flags, (vp * world)(*[b.data_ptr() for b in bufs]), (vp * world)(*[f.data_ptr() for f in flags])
+
+
+@pytest.mark.parametrize("world,n,rank", [(2, 8192, 0), (4, 8192, 3), (8, 16 * 8192, 5), (3, 8, 1), (2, 2056, 1)])
+def test_sum_in_rank_order(world, n, rank):
+    import torch
+    ctx, parts, bufs, flags, pb, pf = _setup(world, n, seed=world)
+    epoch = 7
+    flags[rank].fill_(epoch)              # every peer "has announced" call 7 to this rank
+    out = torch.empty(n, dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, rank, world, pb, pf, n, out.data_ptr(), epoch))
+    torch.cuda.synchronize()
+    ctx.device_status()
+    acc = np.zeros(n, np.float32)
+    for p in parts:                       # rank order, fp32, one rounding: bit-exact
+        acc += p.astype(np.float32)
+    np.testing.assert_array_equal(out.cpu().numpy(), acc.astype(np.float16))
+    # the kernel announced itself to every peer, and to nobody else
+    for r in range(world):
+        f = flags[r].cpu().numpy().reshape(-1, 8)
+        if r != rank:
+            assert (f[:, rank] == epoch).all() and (np.delete(f, rank, axis=1) == 0).all()
+
+
+def test_later_epoch_counts_as_arrived_and_wraps():
+    import torch
+    ctx, parts, bufs, flags, pb, pf = _setup(2, 4096)
+    out = torch.empty(4096, dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    for flag, epoch in ((12, 11), (3, 0xFFFFFFFE)):   # a peer one call ahead; a peer ahead across the wrap
+        flags[0].fill_(flag if flag < 2**31 else flag - 2**32)
+        ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, out.data_ptr(), epoch))
+        torch.cuda.synchronize()
+        ctx.device_status()
+
+
+def test_wait_runs_out_and_context_stays_usable():
+    # a flag that nobody sets: the bounded wait gives up, the status word says so, nothing is written
+    import torch
+    from nnfusion_b200 import _lib as L
+    from nnfusion_b200.linear import NNFB200Error
+    ctx, parts, bufs, flags, pb, pf = _setup(2, 4096)
+    out = torch.full((4096,), 5.0, dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, out.data_ptr(), 1))
+    torch.cuda.synchronize()
+    with pytest.raises(NNFB200Error) as e:
+        ctx.device_status()
+    assert e.value.status == L.ETIMEDOUT
+    assert (out == 5.0).all()
+    ctx.device_status()                   # cleared; the context still works
+    flags[0].fill_(2)
+    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, out.data_ptr(), 2))
+    torch.cuda.synchronize()
+    ctx.device_status()
+
+
+def test_invalid_arguments():
+    from nnfusion_b200 import _lib as L
+    ctx, parts, bufs, flags, pb, pf = _setup(2, 4096)
+    lib, h = ctx.lib, ctx.handle
+    o = bufs[0].data_ptr()
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 9, pb, pf, 4096, o, 1) == L.EINVAL
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 2, 2, pb, pf, 4096, o, 1) == L.EINVAL
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4096, o, 0) == L.EINVAL
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4100, o, 1) == L.ENOTSUP
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4096, o + 2, 1) == L.EALIGN

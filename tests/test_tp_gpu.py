@@ -1,4 +1,5 @@
-"""Tensor-parallel MLP on 2 GPUs (NCCL): the sharded CUDA path agrees with the unsharded CPU oracle."""
+"""Tensor-parallel MLP on 2 GPUs: the sharded CUDA path, closed by NCCL's all-reduce or by the one-shot kernel over
+peer memory, agrees with the unsharded CPU oracle."""
 import os
 import socket
 import subprocess
@@ -27,18 +28,26 @@ x, gate, up, down = _mlp_inputs(M=M, hidden=1024, inter=2048)
 dev = f"cuda:{rank}"
 mlp = ShardedMLP(DeviceWeight.from_host(shard_rows_of_w(gate, rank, world), dev),
                  DeviceWeight.from_host(shard_rows_of_w(up, rank, world), dev),
-                 DeviceWeight.from_host(shard_k_of_w(down, rank, world), dev), group=dist.group.WORLD)
-y = mlp(torch.from_numpy(x).to(dev))
+                 DeviceWeight.from_host(shard_k_of_w(down, rank, world), dev), group=dist.group.WORLD,
+                 reduce=os.environ.get("NNF_REDUCE", "nccl"))
+tx = torch.from_numpy(x).to(dev)
+for _ in range(int(os.environ.get("NNF_CALLS", "1"))):   # repeated calls walk through both peer buffers
+    y = mlp(tx).clone()
 torch.cuda.synchronize()
+mlp.down.ctx.device_status()
+ys = [torch.empty_like(y) for _ in range(world)]
+dist.all_gather(ys, y)
+same = all(torch.equal(ys[0], t) for t in ys)
 if rank == 0:
     np.save(os.environ["NNF_OUT"], y.float().cpu().numpy())
+    open(os.environ["NNF_OUT"] + ".same", "w").write(str(int(same)))
 dist.barrier()
 dist.destroy_process_group()
 '''
 
 
-@pytest.mark.parametrize("M", [1, 64])
-def test_two_gpu_sharded_mlp_matches_oracle(tmp_path, M):
+@pytest.mark.parametrize("M,reduce,calls", [(1, "nccl", 1), (64, "nccl", 1), (1, "peer", 5), (16, "peer", 4)])
+def test_two_gpu_sharded_mlp_matches_oracle(tmp_path, M, reduce, calls):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -50,7 +59,8 @@ def test_two_gpu_sharded_mlp_matches_oracle(tmp_path, M):
     out = str(tmp_path / "y.npy")
     script = tmp_path / "worker.py"
     script.write_text(_WORKER)
-    env = dict(os.environ, NNF_ROOT=ROOT, NNF_OUT=out, NNF_M=str(M), NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NNF_ROOT=ROOT, NNF_OUT=out, NNF_M=str(M), NCCL_NVLS_ENABLE="0", NNF_REDUCE=reduce,
+               NNF_CALLS=str(calls))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
                        env=env, cwd=ROOT, capture_output=True, text=True, timeout=300)
@@ -60,3 +70,5 @@ def test_two_gpu_sharded_mlp_matches_oracle(tmp_path, M):
     ref = _oracle_mlp(x, gate, up, down)
     # each rank rounds its partial sum to fp16 before the all-reduce: tolerance of the fp16 path
     assert orc.max_rel_err(y, ref) < 5e-3
+    # every rank holds the same bits (the peer kernel adds in rank order; NCCL's ring gives the same guarantee)
+    assert open(out + ".same").read() == "1"
