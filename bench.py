@@ -111,7 +111,7 @@ def timed_graph_steps(torch, step_fns, steps, warmup, dist=None):
     launching stream between barrier + synchronize on both sides.  Returns milliseconds (max over ranks)."""
     n = len(step_fns)
     stream = torch.cuda.Stream()
-    chunk = min(steps, max(n, (1200 // n) * n))
+    chunk = min(steps, max(n, (1200 // n) * n))  # a multiple of n unless it is all of the steps
     graphs = {}
 
     def graph_of(count):
@@ -397,27 +397,42 @@ def run_prefill_gemm(args, torch, sampler_index):
 
 
 def run_mlp70b(args, torch, sampler_index, rank, world, dist):
-    """LLaMA-70B-shaped SwiGLU MLP, M = 1 decode, sharded over `world` GPUs."""
+    """LLaMA-70B-shaped SwiGLU MLP, M = 1 decode, sharded over `world` GPUs.  The shard boundary is closed by the
+    one-shot all-reduce kernel over peer memory; the same step with NCCL's all-reduce is timed beside it."""
     from nnfusion_b200.linear import default_context
-    from nnfusion_b200.tp import ShardedMLP, mlp_shapes
+    from nnfusion_b200.tp import PeerAllReduce, ShardedMLP, mlp_shapes
     hidden, inter, M = 8192, 28672, 1
     (n_gu, k_gu), (n_d, k_d) = mlp_shapes(hidden, inter, world)
     ctx = default_context(torch.cuda.current_device())
     # per-rank bytes per step must exceed L2 or the weights must rotate
     per_rank = 2 * (linear_bytes(M, n_gu, k_gu) - M * k_gu * 2 - M * n_gu * 2) + linear_bytes(M, n_d, k_d)
-    ncopies = max(1, int(L2_BYTES * 2.2 // per_rank) + 1)
+    ncopies = max(2, int(L2_BYTES * 2.2 // per_rank) + 1)
+    ncopies += ncopies & 1  # an even number of steps per captured graph keeps the all-reduce's two halves in step
     group = dist.group.WORLD if world > 1 else None
-    mlps = [ShardedMLP(rand_device_weight(torch, n_gu, k_gu), rand_device_weight(torch, n_gu, k_gu),
-                       rand_device_weight(torch, n_d, k_d), group=group) for _ in range(ncopies)]
+    peer = PeerAllReduce(16 * hidden, group) if world > 1 else None
+    weights = [(rand_device_weight(torch, n_gu, k_gu), rand_device_weight(torch, n_gu, k_gu),
+                rand_device_weight(torch, n_d, k_d)) for _ in range(ncopies)]
+    mlps = [ShardedMLP(*w, group=group, reduce="peer" if world > 1 else "nccl", peer=peer) for w in weights]
     x = torch.randn(M, hidden, device="cuda").to(torch.float16)
     ctx.launch_count(reset=True)
+    # every captured graph must hold an even number of steps (see PeerAllReduce): K is timed exactly when it is
+    # even, K + 1 otherwise, and the line says which
+    steps = args.steps + (args.steps & 1)
     with ClockSampler(sampler_index) as cs:
-        ms = timed_plain_steps(torch, lambda i: mlps[i % ncopies](x), args.steps, args.warmup, dist if world > 1 else None)
+        ms = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in mlps], steps, args.warmup, dist if world > 1 else None)
     ctx.device_status()
     full = 2 * (linear_bytes(M, inter, hidden) - M * hidden * 2 - M * inter * 2) + M * hidden * 2 + 2 * M * inter * 2 + \
         linear_bytes(M, hidden, inter) - M * inter * 2
-    value = full * args.steps / (ms * 1e-3) / 1e9
+    value = full * steps / (ms * 1e-3) / 1e9
     peaks = measured_peaks()
+    also = {}
+    if world > 1:
+        nccl = [ShardedMLP(*w, group=group, reduce="nccl") for w in weights]
+        nsteps = min(steps, 400)
+        ms_n = timed_plain_steps(torch, lambda i: nccl[i % ncopies](x), nsteps, 5, dist)
+        also["same_step_with_nccl_allreduce"] = {"us": round(ms_n * 1e3 / nsteps, 2), "launch": "plain launches"}
+        ms_p = timed_plain_steps(torch, lambda i: mlps[i % ncopies](x), nsteps, 6, dist)
+        also["peer_allreduce_plain_launches"] = {"us": round(ms_p * 1e3 / nsteps, 2)}
     xh = torch.randn(M, hidden).to(torch.float16).pin_memory()
     yh = torch.empty(M, hidden, dtype=torch.float16).pin_memory()
 
@@ -427,22 +442,25 @@ def run_mlp70b(args, torch, sampler_index, rank, world, dist):
         yh.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    e2e_steps = min(args.steps, 500)
-    ms_e2e = timed_plain_steps(torch, e2e_step, e2e_steps, 3, dist if world > 1 else None)
+    e2e_steps = min(steps, 500) // 2 * 2
+    ms_e2e = timed_plain_steps(torch, e2e_step, e2e_steps, 4, dist if world > 1 else None)
+    ctx.device_status()
     return {
-        "metric": "int4_g128_decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
-        "ms_per_step": ms / args.steps, "dtype": "f16", "scaling": "strong",
+        "metric": "int4_g128_decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "steps": steps,
+        "ms_per_step": ms / steps, "dtype": "f16", "scaling": "strong",
         "config": {"workload": "mlp70b_decode: X f16 [1,8192], gate/up u4-g128 [28672,8192] column-sharded, down [8192,28672] "
-                               "row-sharded, NCCL all-reduce of f16 [1,8192]",
+                               "row-sharded, one-shot all-reduce of f16 [1,8192] over peer memory",
                    "algorithmic_bytes_per_step": full, "parallelism": f"tp{world}",
-                   "l2": f"{ncopies} weight copies per rank in rotation ({ncopies * per_rank / 1e6:.0f} MB per rank) larger than L2"},
+                   "l2": f"{ncopies} weight copies per rank in rotation ({ncopies * per_rank / 1e6:.0f} MB per rank) larger than L2",
+                   "launch": "CUDA graph replay of the C-ABI calls"},
         "roofline": {"bound": "hbm", "achieved": round(value / world, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(value / world / peaks["hbm_gbs"], 4), "traffic": None,
                      "peak_source": f"of {peaks['source']}, per GPU", "kernel": "dq_gemv_kernel (gate/up fused SiLU*mul, down)"},
         "e2e": {"value": round(full * e2e_steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": M * hidden * 2, "d2h_bytes_per_step": M * hidden * 2},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": (3 if world > 1 else 2) * steps,
         "clocks": cs.summary(),
+        **({"also": also} if also else {}),
     }
 
 
@@ -519,7 +537,8 @@ def main():
         else:
             out = run_mlp70b(args, torch, local_rank, rank, world, dist)
         if rank == 0:
-            out.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+            out.setdefault("steps", args.steps)
+            out.update({"n_gpus": world, "warmup": args.warmup, "higher_is_better": True,
                         "vs_baseline": None, "data": "synthetic", "impl": "ours"})
             if world == 1:
                 # the reference's CPU path on this box's host cores, bounded sample

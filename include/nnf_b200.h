@@ -262,16 +262,19 @@ NNF_B200_API int nnf_b200_decode_attention(nnf_b200_ctx* ctx, void* stream, cons
  *
  * bufs[r] / flags[r] (host arrays of `world` entries, world <= 8): rank r's addend buffer and flag words as mapped
  * into THIS process (peer pointers for r != rank; memory every rank has mapped, e.g. from cuMemMap or CUDA IPC).
- * Every rank calls with the same count and epoch.  Rules for the caller: flags start zeroed and are never written
- * by anyone else; epoch starts at 1 and grows by one per call; the addend buffers alternate between two sets from
- * call to call (a rank may be one call ahead of a peer that is still reading); the addend of this call must be
- * complete in stream order before the call.  count: fp16 elements, a multiple of 8, bufs 16-byte aligned.
+ * A buffer has two halves, half_stride_bytes apart; call number e reads half (e & 1) of every rank, so a rank may
+ * be one call ahead of a peer that is still reading.  epoch: the call number, starting at 1 and growing by one per
+ * call, the same on every rank -- or 0 to let the kernel count calls itself in words kept after the flags (then a
+ * captured sequence with an even number of calls can be replayed).  Other rules for the caller: the flag words
+ * (nnf_b200_allreduce_flag_bytes of them) start zeroed and are never written by anyone else; the addend of this
+ * call must be complete in its half, in stream order, before the call.  count: fp16 elements, a multiple of 8;
+ * bufs 16-byte aligned.
  * A rank whose peers never call gives up after about 0.1 s, writes nothing, and nnf_b200_device_status then
  * reports NNF_B200_ETIMEDOUT. */
 NNF_B200_API size_t nnf_b200_allreduce_flag_bytes(size_t count);
 NNF_B200_API int nnf_b200_allreduce_oneshot(nnf_b200_ctx* ctx, void* stream, int rank, int world,
-                                            const void* const* bufs, void* const* flags, size_t count, void* out,
-                                            uint32_t epoch);
+                                            const void* const* bufs, void* const* flags, size_t count,
+                                            size_t half_stride_bytes, void* out, uint32_t epoch);
 
 /* Reads (and clears) the device-side status word: 0, or NNF_B200_ETIMEDOUT when a
  * bounded wait inside a kernel gave up since the last query.  Synchronises the

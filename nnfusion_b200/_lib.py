@@ -92,6 +92,6 @@ def load() -> ctypes.CDLL:
     L.nnf_b200_allreduce_flag_bytes.argtypes = [sz]
     L.nnf_b200_allreduce_flag_bytes.restype = sz
     L.nnf_b200_allreduce_oneshot.argtypes = [vp, vp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(vp),
-                                             ctypes.POINTER(vp), sz, vp, ctypes.c_uint32]
+                                             ctypes.POINTER(vp), sz, sz, vp, ctypes.c_uint32]
     _lib = L
     return L

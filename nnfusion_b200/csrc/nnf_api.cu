@@ -212,12 +212,14 @@ size_t nnf_b200_allreduce_flag_bytes(size_t count)
 }
 
 int nnf_b200_allreduce_oneshot(nnf_b200_ctx* ctx, void* stream, int rank, int world, const void* const* bufs,
-                               void* const* flags, size_t count, void* out, uint32_t epoch)
+                               void* const* flags, size_t count, size_t half_stride_bytes, void* out, uint32_t epoch)
 {
     if (!ctx)
         return NNF_B200_EINVAL;
-    if (world < 1 || world > 8 || rank < 0 || rank >= world || !bufs || !flags || !out || count == 0 || epoch == 0)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "1 <= world <= 8, 0 <= rank < world, non-null arrays, epoch >= 1");
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || !bufs || !flags || !out || count == 0)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "1 <= world <= 8, 0 <= rank < world, non-null arrays, count > 0");
+    if (half_stride_bytes < count * 2 || half_stride_bytes % 16 != 0)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "half_stride_bytes must hold the tensor and be a multiple of 16");
     if (count % 8 != 0 || count > (size_t)1 << 24)
         return nnf::set_error(ctx, NNF_B200_ENOTSUP, "count must be a multiple of 8 fp16 elements, at most 2^24");
     for (int r = 0; r < world; r++)
@@ -229,7 +231,8 @@ int nnf_b200_allreduce_oneshot(nnf_b200_ctx* ctx, void* stream, int rank, int wo
     }
     if (!aligned16(out))
         return nnf::set_error(ctx, NNF_B200_EALIGN, "out must be 16-byte aligned");
-    return nnf::allreduce_launch(ctx, static_cast<cudaStream_t>(stream), rank, world, bufs, flags, count, out, epoch);
+    return nnf::allreduce_launch(ctx, static_cast<cudaStream_t>(stream), rank, world, bufs, flags, count,
+                                 half_stride_bytes, out, epoch);
 }
 
 size_t nnf_b200_decode_attention_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_attn_desc* desc)

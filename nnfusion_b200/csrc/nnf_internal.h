@@ -71,7 +71,7 @@ int gemm_configure(nnf_b200_ctx* ctx);
 
 size_t allreduce_flag_bytes(size_t count);
 int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world, const void* const* bufs,
-                     void* const* flags, size_t count, void* out, uint32_t epoch);
+                     void* const* flags, size_t count, size_t half_stride, void* out, uint32_t epoch);
 
 int attn_check(const nnf_b200_attn_desc& d, std::string* why);
 size_t attn_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_attn_desc& d);

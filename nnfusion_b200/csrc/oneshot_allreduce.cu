@@ -4,15 +4,17 @@
 // Stands in for the NCCL call behind the reference's only collective, cuda::SuperScalerAllReduce
 // (src/nnfusion/core/kernels/cuda_gpu/kernels/allreduce.cpp:18-98; the call itself in
 // src/tools/nnfusion/templates/super_scaler/super_scaler.cu:244-277), where a ring over a few kilobytes is all
-// latency.  Every rank keeps its addend in a buffer that all ranks have mapped (plain peer pointers; no multicast,
-// no TMA): a CTA tells every peer "my buffer holds call number `epoch`" with one flag store per peer, waits until every
+// latency.  Every rank keeps its addend in a buffer that all ranks have mapped (plain peer pointers,
+// plain loads and stores): a CTA tells every peer "my buffer holds call number `epoch`" with one flag store per peer, waits until every
 // peer has said the same to it, then reads its slice of all buffers with 16-byte peer loads, adds them in rank
 // order in fp32 (so every rank gets the same bits) and writes the sum to local memory.
 //
 // Flags are never reset: they only grow (one 32-bit word per CTA and sender on the receiving rank), a wait is
-// "flag >= epoch".  The caller alternates between two buffers from call to call: a rank may run one call ahead of a
-// peer that is still reading, never two (its next wait needs that peer's next flag).  Every wait is bounded; a wait
-// that gives up raises the context's device status word and the CTA writes nothing.
+// "flag >= epoch".  Calls alternate between the two halves of every rank's buffer (half = epoch & 1): a rank may run
+// one call ahead of a peer that is still reading, never two (its next wait needs that peer's next flag).  The call
+// number comes from the host, or (epoch argument 0) from a counter per CTA kept next to the flags, which makes a
+// captured sequence of calls replayable.  Every wait is bounded; a wait that gives up raises the context's device
+// status word and the CTA writes nothing.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <string>
@@ -27,8 +29,10 @@ constexpr uint32_t kArSpin = 1u << 21; // polls of about 50 ns each: gives up af
 
 struct ArParams
 {
-    const uint4* bufs[kMaxRanks]; // this call's buffer of every rank (own included), as mapped on this rank
-    uint32_t* flags[kMaxRanks];   // flag words of every rank: [CTA][sender]
+    const char* bufs[kMaxRanks]; // buffer (both halves) of every rank, own included, as mapped on this rank
+    uint32_t* flags[kMaxRanks];  // flag words of every rank: [CTA][sender]
+    uint32_t* counters;          // this rank's call counters, one per CTA
+    size_t half_stride;          // bytes between the two halves of a buffer
     uint4* out;
     int* status;
     int rank, world;
@@ -50,19 +54,32 @@ __device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p)
 __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(const ArParams p)
 {
     __shared__ int ok_s;
+    __shared__ uint32_t epoch_s;
     const int tid = threadIdx.x;
     if (tid == 0)
+    {
         ok_s = 1;
+        uint32_t e = p.epoch;
+        if (e == 0)
+        {
+            e = p.counters[blockIdx.x] + 1; // only this CTA of this rank ever touches the word; launches are ordered
+            if (e == 0)
+                e = 2;                      // skip 0 ("take the counter") at the wrap, keeping the parity
+            p.counters[blockIdx.x] = e;
+        }
+        epoch_s = e;
+    }
     __syncthreads();
+    const uint32_t epoch = epoch_s;
     // thread r talks to rank r: announce, then wait for its announcement
     if (tid < p.world && tid != p.rank)
     {
-        store_release_sys(p.flags[tid] + blockIdx.x * kMaxRanks + p.rank, p.epoch);
+        store_release_sys(p.flags[tid] + blockIdx.x * kMaxRanks + p.rank, epoch);
         const uint32_t* mine = p.flags[p.rank] + blockIdx.x * kMaxRanks + tid;
         bool seen = false;
         for (uint32_t i = 0; i < kArSpin && !seen; i++)
         {
-            seen = (int32_t)(load_acquire_sys(mine) - p.epoch) >= 0;
+            seen = (int32_t)(load_acquire_sys(mine) - epoch) >= 0;
             if (!seen)
                 __nanosleep(40);
         }
@@ -86,7 +103,8 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(const ArP
 #pragma unroll
     for (int r = 0; r < kMaxRanks; r++)
         if (r < p.world)
-            part[r] = __ldcv(p.bufs[r] + v); // volatile-class load: never served from a stale line
+            part[r] = __ldcv(reinterpret_cast<const uint4*>(p.bufs[r] + (epoch & 1u) * p.half_stride) + v); // never
+                                                                          // served from a stale line
 #pragma unroll
     for (int r = 0; r < kMaxRanks; r++)
         if (r < p.world)
@@ -114,16 +132,16 @@ size_t allreduce_flag_bytes(size_t count)
 {
     const size_t vecs = (count + 7) / 8;
     const size_t ctas = (vecs + kArThreads - 1) / kArThreads;
-    return ctas * kMaxRanks * sizeof(uint32_t);
+    return ctas * (kMaxRanks + 1) * sizeof(uint32_t); // flags [CTA][sender], then one call counter per CTA
 }
 
 int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world, const void* const* bufs,
-                     void* const* flags, size_t count, void* out, uint32_t epoch)
+                     void* const* flags, size_t count, size_t half_stride, void* out, uint32_t epoch)
 {
     ArParams p{};
     for (int r = 0; r < world; r++)
     {
-        p.bufs[r] = static_cast<const uint4*>(bufs[r]);
+        p.bufs[r] = static_cast<const char*>(bufs[r]);
         p.flags[r] = static_cast<uint32_t*>(flags[r]);
     }
     p.out = static_cast<uint4*>(out);
@@ -131,7 +149,9 @@ int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world
     p.rank = rank, p.world = world;
     p.vecs = (uint32_t)(count / 8);
     p.epoch = epoch;
+    p.half_stride = half_stride;
     const unsigned ctas = (p.vecs + kArThreads - 1) / kArThreads;
+    p.counters = p.flags[rank] + (size_t)ctas * kMaxRanks;
     (void)cudaGetLastError();
     oneshot_allreduce_kernel<<<ctas, kArThreads, 0, stream>>>(p);
     cudaError_t e = cudaGetLastError();

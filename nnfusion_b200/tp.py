@@ -82,7 +82,7 @@ class PeerAllReduce:
         self.epoch = 0
         vp = ctypes.c_void_p
         self._flags = (vp * self.world)(*[p + self.flag_off for p in self.ptrs])
-        self._bufs = [(vp * self.world)(*[p + half * self.data_bytes for p in self.ptrs]) for half in (0, 1)]
+        self._bufs = (vp * self.world)(*self.ptrs)
 
     def addend(self, shape):
         """The buffer this rank fills for the next call, viewed as fp16 ``shape``."""
@@ -95,11 +95,11 @@ class PeerAllReduce:
         return self.mem[half * self.data_bytes: half * self.data_bytes + 2 * n].view(self.torch.float16).view(shape)
 
     def __call__(self, out):
+        """Call numbers are counted on the device, so a CUDA graph holding an even number of calls replays."""
         self.epoch += 1
-        half = self.epoch & 1
         stream = self.torch.cuda.current_stream().cuda_stream
-        rc = self.ctx.lib.nnf_b200_allreduce_oneshot(self.ctx.handle, stream, self.rank, self.world, self._bufs[half],
-                                                     self._flags, out.numel(), out.data_ptr(), self.epoch)
+        rc = self.ctx.lib.nnf_b200_allreduce_oneshot(self.ctx.handle, stream, self.rank, self.world, self._bufs,
+                                                     self._flags, out.numel(), self.data_bytes, out.data_ptr(), 0)
         self.ctx.check(rc)
         return out
 
@@ -114,7 +114,7 @@ class ShardedMLP:
     """
 
     def __init__(self, gate, up, down, group=None, gain=None, eps: float = 1e-6, reduce: str = "nccl",
-                 peer_max_rows: int = 16):
+                 peer_max_rows: int = 16, peer: "Optional[PeerAllReduce]" = None):
         import torch
 
         from .linear import DequantDot
@@ -128,7 +128,9 @@ class ShardedMLP:
         self._y = {}
         if reduce not in ("nccl", "peer"):
             raise ValueError("reduce must be 'nccl' or 'peer'")
-        self.peer = PeerAllReduce(peer_max_rows * down.N, group) if (reduce == "peer" and group is not None) else None
+        # (several layers may share one PeerAllReduce: calls are ordered on the stream)
+        self.peer = peer if peer is not None else (
+            PeerAllReduce(peer_max_rows * down.N, group) if (reduce == "peer" and group is not None) else None)
         self.peer_max_rows = peer_max_rows
 
     def buffers(self, M: int, dtype, device):

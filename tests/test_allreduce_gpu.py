@@ -15,8 +15,9 @@ def _setup(world, n, seed=0):
 
     ctx = default_context(0)
     rng = np.random.Generator(np.random.PCG64(seed))
+    # two halves per rank; `parts` is what half 1 holds (odd call numbers), half 0 holds its negation
     parts = [rng.standard_normal(n).astype(np.float16) for _ in range(world)]
-    bufs = [torch.from_numpy(p).cuda() for p in parts]
+    bufs = [torch.from_numpy(np.concatenate([-p, p])).cuda() for p in parts]
     fb = int(ctx.lib.nnf_b200_allreduce_flag_bytes(n))
     flags = [torch.zeros(fb // 4, dtype=torch.int32, device="cuda") for _ in range(world)]
     vp = ctypes.c_void_p
@@ -28,10 +29,10 @@ def test_sum_in_rank_order(world, n, rank):
     import torch
     ctx, parts, bufs, flags, pb, pf = _setup(world, n, seed=world)
     epoch = 7
-    flags[rank].fill_(epoch)              # every peer "has announced" call 7 to this rank
+    flags[rank][: (n // 8 + 255) // 256 * 8].fill_(epoch)   # every peer "has announced" call 7 to this rank
     out = torch.empty(n, dtype=torch.float16, device="cuda")
     s = torch.cuda.current_stream().cuda_stream
-    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, rank, world, pb, pf, n, out.data_ptr(), epoch))
+    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, rank, world, pb, pf, n, 2 * n, out.data_ptr(), epoch))
     torch.cuda.synchronize()
     ctx.device_status()
     acc = np.zeros(n, np.float32)
@@ -40,9 +41,29 @@ def test_sum_in_rank_order(world, n, rank):
     np.testing.assert_array_equal(out.cpu().numpy(), acc.astype(np.float16))
     # the kernel announced itself to every peer, and to nobody else
     for r in range(world):
-        f = flags[r].cpu().numpy().reshape(-1, 8)
+        ctas = (n // 8 + 255) // 256
+        f = flags[r].cpu().numpy()[: ctas * 8].reshape(-1, 8)
         if r != rank:
             assert (f[:, rank] == epoch).all() and (np.delete(f, rank, axis=1) == 0).all()
+
+
+def test_device_counted_calls_alternate_halves():
+    import torch
+    ctx, parts, bufs, flags, pb, pf = _setup(3, 4096, seed=9)
+    flags[1][: 2 * 8].fill_(1000)          # the peers are "far ahead": no call of this test has to wait
+    out = torch.empty(4096, dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    acc = np.zeros(4096, np.float32)
+    for p in parts:
+        acc += p.astype(np.float32)
+    for call in (1, 2, 3, 4):
+        ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 1, 3, pb, pf, 4096, 8192, out.data_ptr(), 0))
+        torch.cuda.synchronize()
+        ctx.device_status()
+        want = acc if call & 1 else -acc    # half (call & 1)
+        np.testing.assert_array_equal(out.cpu().numpy(), want.astype(np.float16))
+    counters = flags[1].cpu().numpy()[2 * 8: 2 * 8 + 2]
+    assert (counters == 4).all()
 
 
 def test_later_epoch_counts_as_arrived_and_wraps():
@@ -52,7 +73,7 @@ def test_later_epoch_counts_as_arrived_and_wraps():
     s = torch.cuda.current_stream().cuda_stream
     for flag, epoch in ((12, 11), (3, 0xFFFFFFFE)):   # a peer one call ahead; a peer ahead across the wrap
         flags[0].fill_(flag if flag < 2**31 else flag - 2**32)
-        ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, out.data_ptr(), epoch))
+        ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, 8192, out.data_ptr(), epoch))
         torch.cuda.synchronize()
         ctx.device_status()
 
@@ -65,7 +86,7 @@ def test_wait_runs_out_and_context_stays_usable():
     ctx, parts, bufs, flags, pb, pf = _setup(2, 4096)
     out = torch.full((4096,), 5.0, dtype=torch.float16, device="cuda")
     s = torch.cuda.current_stream().cuda_stream
-    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, out.data_ptr(), 1))
+    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, 8192, out.data_ptr(), 1))
     torch.cuda.synchronize()
     with pytest.raises(NNFB200Error) as e:
         ctx.device_status()
@@ -73,7 +94,7 @@ def test_wait_runs_out_and_context_stays_usable():
     assert (out == 5.0).all()
     ctx.device_status()                   # cleared; the context still works
     flags[0].fill_(2)
-    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, out.data_ptr(), 2))
+    ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, 0, 2, pb, pf, 4096, 8192, out.data_ptr(), 2))
     torch.cuda.synchronize()
     ctx.device_status()
 
@@ -83,8 +104,8 @@ def test_invalid_arguments():
     ctx, parts, bufs, flags, pb, pf = _setup(2, 4096)
     lib, h = ctx.lib, ctx.handle
     o = bufs[0].data_ptr()
-    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 9, pb, pf, 4096, o, 1) == L.EINVAL
-    assert lib.nnf_b200_allreduce_oneshot(h, None, 2, 2, pb, pf, 4096, o, 1) == L.EINVAL
-    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4096, o, 0) == L.EINVAL
-    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4100, o, 1) == L.ENOTSUP
-    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4096, o + 2, 1) == L.EALIGN
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 9, pb, pf, 4096, 8192, o, 1) == L.EINVAL
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 2, 2, pb, pf, 4096, 8192, o, 1) == L.EINVAL
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4096, 100, o, 1) == L.EINVAL
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4100, 16384, o, 1) == L.ENOTSUP
+    assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4096, 8192, o + 2, 1) == L.EALIGN
