@@ -129,8 +129,12 @@ class DequantDot:
     def __init__(self, weight: DeviceWeight, weight2: Optional[DeviceWeight] = None,
                  gain: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
                  eps: float = 1e-6, y_dtype: Optional[torch.dtype] = None, kernel: int = L.KERNEL_AUTO,
-                 split_k: int = 0, flags: int = 0, ctx: Optional[Context] = None, add: bool = False):
+                 split_k: int = 0, flags: int = 0, ctx: Optional[Context] = None, add: bool = False,
+                 kernel_db=None, db_device: str = "B200"):
         self.w, self.w2, self.gain, self.bias = weight, weight2, gain, bias
+        # measured launch choices (nnfusion_b200.kernel_db.KernelCacheManager); entries found there override the
+        # built-in rule, like the reference's FetchBasedSelector overrides priorities
+        self.kernel_db, self.db_device = kernel_db, db_device
         self.add = add  # y = x.W^T + addend, the addend ([M,N], y's dtype) being given at call time
         if add and (bias is not None or weight2 is not None):
             raise ValueError("the add epilogue excludes bias and the SiLU*mul epilogue")
@@ -163,6 +167,13 @@ class DequantDot:
         d.kernel = self.kernel
         d.split_k = self.split_k
         d.flags = self.flags
+        if self.kernel_db is not None and self.kernel == L.KERNEL_AUTO and self.split_k == 0:
+            from . import kernel_db as kdb
+            ident = kdb.identifier(M, d.N, d.K, d.w_bits, d.group_size, d.x_dtype, d.scale_dtype, d.y_dtype,
+                                   self.w2 is not None)
+            hit = self.kernel_db.fetch_with_tags(ident, kdb.DEVICE_TYPE, {"fast"}, self.db_device)
+            if hit is not None:
+                d.kernel, d.split_k = int(hit.function["kernel"]), int(hit.function["split_k"])
         return d
 
     def workspace(self, d: L.LinearDesc) -> Optional[torch.Tensor]:

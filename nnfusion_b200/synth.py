@@ -12,7 +12,7 @@ from typing import Optional
 
 import numpy as np
 
-from .quant import pack_u4
+from .quant import pack_u4, unpack_u4
 
 
 @dataclass
@@ -35,6 +35,16 @@ class QuantLinear:
     def zpq(self) -> np.ndarray:
         """Zero-point bytes as the kernels read them."""
         return pack_u4(self.zp) if self.bits == 4 else self.zp
+
+    @staticmethod
+    def from_packed(N: int, K: int, bits: int, group: int, wq: np.ndarray, scale: np.ndarray,
+                    zpq: np.ndarray) -> "QuantLinear":
+        """From the bytes the kernels read (the on-disk form) back to one value per element / group."""
+        G = K // group
+        if bits == 4:
+            return QuantLinear(N, K, bits, group, unpack_u4(np.asarray(wq), K), np.asarray(scale),
+                               unpack_u4(np.asarray(zpq), G))
+        return QuantLinear(N, K, bits, group, np.asarray(wq), np.asarray(scale), np.asarray(zpq))
 
 
 def make_weights(rng: np.random.Generator, N: int, K: int, bits: int, group: int,
