@@ -215,6 +215,26 @@ def cpu_reference_gemv(seconds_budget: float, rows: int, K: int = 4096, M: int =
     return sum(times) / len(times), len(times), cores, kind
 
 
+def cpu_reference_gemm_only(rows: int, K: int = 4096, M: int = 1, calls: int = 20):
+    """Seconds per call of the SGEMM alone on already dequantised fp32 weights: what the reference's CPU graph runs
+    per call when its constant folding has materialised the weights.  None without the compiled reference."""
+    import numpy as np
+    from oracle import oracle as orc
+    if not orc.have_ref():
+        return None
+    rng = np.random.Generator(np.random.PCG64(0))
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    graph = orc.RefLinearGraph(rows, K)
+    graph(x, rng.integers(0, 16, size=(rows, K), dtype=np.uint8),
+          rng.uniform(0.002, 0.02, size=(rows, K // 128)).astype(np.float32),
+          rng.integers(0, 16, size=(rows, K // 128), dtype=np.uint8), 128)   # leaves the dequantised weights behind
+    graph.gemm_only(x)
+    t0 = time.perf_counter()
+    for _ in range(calls):
+        graph.gemm_only(x)
+    return (time.perf_counter() - t0) / calls
+
+
 # ----------------------------------------------------------------------------------------------- workloads (ours)
 def run_decode_gemv(args, torch, sampler_index):
     from nnfusion_b200.linear import DequantDot, default_context
@@ -556,6 +576,10 @@ def main():
                     sample = "1376 of 11008 weight rows per call (dequant graph + MLAS SGEMM), ~10 s of calls"
                 out["cpu_baseline"] = {"value": v, "unit": unit, "cores": cores, "kind": kind, "sample": sample,
                                        "calls": n, "ms_per_call": sec * 1e3}
+                if workload == "decode_gemv":
+                    g = cpu_reference_gemm_only(1376, 4096, 1)
+                    if g is not None:
+                        out["cpu_baseline"]["gemm_only_on_dequantised_fp32_ms_per_call"] = g * 1e3
                 if not args.no_extras:
                     out["also"] = extra_measurements(torch)
             order = ["metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",

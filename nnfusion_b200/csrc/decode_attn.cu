@@ -62,6 +62,10 @@ __global__ void __launch_bounds__(kThreads, 4) decode_attention_kernel(const Att
     __shared__ float stat_s[2][4]; // per-warp maximum / sum
     __shared__ int last_s;
 
+    // The next launch on the stream may start as SMs become free; this one waits for the launch before it (which
+    // produced q, k, v; the cache rows it reads were written by earlier steps, but nothing is assumed about those).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int half = lane >> 4, dg = lane & 15; // which of the warp's two rows, which 8 dimensions
     const int head = blockIdx.y, split = blockIdx.x;
@@ -316,8 +320,14 @@ int attn_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_attn_desc
         p.ws_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + cnt);
     }
     (void)cudaGetLastError();
-    decode_attention_kernel<<<dim3(p.splits, d.heads), kThreads, 0, stream>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.splits, d.heads);
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    overlap_attribute(attr, &cfg.numAttrs);
+    cfg.attrs = attr;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_attention_kernel, p);
     if (e != cudaSuccess)
         return set_error(ctx, NNF_B200_ECUDA, std::string("decode_attention launch: ") + cudaGetErrorString(e));
     ctx->launches++;

@@ -30,6 +30,7 @@
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 
 #include "nnf_internal.h"
 #include "sm100_ptx.cuh"
@@ -226,6 +227,8 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     constexpr int MPAD = 8 * MB;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // The next launch on the stream may start as soon as SMs become free (it waits for this grid's results itself).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int nwarps = (blockDim.x >> 5) - 1; // arithmetic warps; the last warp of the CTA only asks for data
     const int nthreads = nwarps * 32;
     const int tid = threadIdx.x;
@@ -375,6 +378,11 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             soff[l][h] = ((g + 8 * h) * p.G + grp_of[l]) * sbytes;
             zoff[l][h] = p.scale_tile_bytes + (g + 8 * h) * p.zp_row_bytes + (WBITS == 4 ? grp_of[l] >> 1 : grp_of[l]);
         }
+
+    // Everything above reads only constants (weights, scales, zero-points).  The activations, the output and the
+    // workspace may belong to the launch before this one on the stream: when this kernel was launched as its
+    // programmatic dependent, it has been running beside that launch's tail until here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---------------------------------------------------------------- activations -> B fragments in registers
     uint32_t xf[2][MB][XS][NF];
@@ -923,9 +931,17 @@ cudaError_t launch(const GemvParams& p, int warps, int /*grid*/, size_t smem, cu
     if (e != cudaSuccess)
         return e;
     (void)cudaGetLastError(); // do not inherit a stale error left behind by an unrelated earlier call
-    dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT, FAST>
-        <<<dim3(p.ctas_per_split, p.splits), (warps + 1) * 32, smem, stream>>>(p);
-    return cudaGetLastError();
+    // Programmatic dependent launch: the CTAs may start while the launch before this one on the stream is still
+    // finishing; they stream their weights at once and wait (griddepcontrol.wait) before touching anything else.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.ctas_per_split, p.splits);
+    cfg.blockDim = dim3((warps + 1) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    nnf::overlap_attribute(attr, &cfg.numAttrs);
+    cfg.attrs = attr;
+    return cudaLaunchKernelEx(&cfg, dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT, FAST>, p);
 }
 
 #define NNF_GEMV_FOR_EACH_VARIANT(X)                                                                              \

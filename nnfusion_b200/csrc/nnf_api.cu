@@ -3,6 +3,8 @@
 #include <cstring>
 #include <new>
 
+#include <cstdlib>
+
 #include "nnf_internal.h"
 #include "sm100_ptx.cuh"
 
@@ -44,6 +46,17 @@ bool encode_tensor_map_2d(void* encode_fn, CUtensorMap* map, CUtensorMapDataType
                                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
+}
+
+void overlap_attribute(cudaLaunchAttribute* attr, unsigned* count)
+{
+    static const bool on = [] {
+        const char* v = getenv("NNF_B200_NO_OVERLAP");
+        return !(v && v[0] == '1');
+    }();
+    attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr->val.programmaticStreamSerializationAllowed = 1;
+    *count = on ? 1 : 0;
 }
 
 const CUtensorMap* weight_tensor_map(nnf_b200_ctx* ctx, const void* base, int rows, int row_bytes, int box_bytes,

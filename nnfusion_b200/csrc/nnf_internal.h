@@ -51,6 +51,11 @@ struct GemvPlan
 
 int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
 
+// Launch attribute that lets a kernel start while the launch before it on the stream is finishing (programmatic
+// dependent launch); every kernel launched with it executes griddepcontrol.wait before it touches anything that
+// launch may have written.  count is 0 when NNF_B200_NO_OVERLAP=1 is set in the environment.
+void overlap_attribute(cudaLaunchAttribute* attr, unsigned* count);
+
 // Cached 2-D byte tensor map [rows][row_bytes] with a box of box_rows x box_bytes (128-byte swizzle when
 // box_bytes == 128, none otherwise); nullptr if the driver refuses it.
 const CUtensorMap* weight_tensor_map(nnf_b200_ctx* ctx, const void* base, int rows, int row_bytes, int box_bytes,

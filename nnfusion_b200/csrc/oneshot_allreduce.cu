@@ -55,6 +55,8 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(const ArP
 {
     __shared__ int ok_s;
     __shared__ uint32_t epoch_s;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory"); // the addend comes from the launch before this one
     const int tid = threadIdx.x;
     if (tid == 0)
     {
@@ -153,8 +155,14 @@ int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world
     const unsigned ctas = (p.vecs + kArThreads - 1) / kArThreads;
     p.counters = p.flags[rank] + (size_t)ctas * kMaxRanks;
     (void)cudaGetLastError();
-    oneshot_allreduce_kernel<<<ctas, kArThreads, 0, stream>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kArThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    overlap_attribute(attr, &cfg.numAttrs);
+    cfg.attrs = attr;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, oneshot_allreduce_kernel, p);
     if (e != cudaSuccess)
         return set_error(ctx, NNF_B200_ECUDA, std::string("oneshot_allreduce launch: ") + cudaGetErrorString(e));
     ctx->launches++;
