@@ -120,7 +120,7 @@ def load_linear(directory: str, name: str, device: str = "cuda:0", stream=None):
     out = []
     with torch.cuda.stream(stream) if stream is not None else _null():
         for arr in (w.wq, w.scale, w.zpq):
-            staged = torch.from_numpy(np.ascontiguousarray(arr)).pin_memory()
+            staged = torch.from_numpy(np.array(arr)).pin_memory()   # (a writable copy of the read-only mapping)
             out.append(staged.to(device, non_blocking=True))
     torch.cuda.current_stream().synchronize() if stream is None else stream.synchronize()
     return DeviceWeight(w.N, w.K, w.bits, w.group, *out)
