@@ -69,6 +69,9 @@ struct GemvParams
     int tq;          // accumulator column pairs kept: 1, 2 or 4, at least ceil(min(M, 8) / 2); 4 when M > 8
     int row_bytes;   // bytes of one packed weight row
     int bulk_params; // scales / zero-points of a tile arrive by bulk copy in shared memory
+    int lsu_weights; // weights arrive by per-thread cp.async (each thread fetches exactly the bytes it will read)
+                     // instead of bulk copies: the bulk-copy engine moves 16 bytes per clock and SM, which caps a
+                     // launch at 4.6 TB/s over 148 SMs
     int scale_tile_bytes, zp_tile_bytes, pset_bytes; // per tile and weight set
     float eps;
     int slot_floats;
@@ -148,6 +151,29 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr)
     uint32_t v;
     asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// Wait until at most n of this thread's most recent groups are still in flight (n < 8).
+__device__ __forceinline__ void cp_async_wait(int n)
+{
+    switch (n)
+    {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    }
 }
 __device__ __forceinline__ void named_barrier(int id, int threads)
 {
@@ -256,7 +282,9 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     // Shared-memory bytes between two rows of a tile.  When a CTA takes whole rows, a tile is one contiguous piece of
     // memory and arrives with a single copy, rows back to back (the fragment loads then pay a two-way bank conflict,
     // which is cheap next to sixteen separate copies).
-    const bool whole_rows = p.splits == 1 && p.row_bytes == nwarps * 128;
+    const bool lsu = p.lsu_weights != 0;
+    const bool use_full = !lsu || p.bulk_params; // does anything arrive through the slots' "full" barriers?
+    const bool whole_rows = !lsu && p.splits == 1 && p.row_bytes == nwarps * 128;
     const int row_stride = whole_rows ? nwarps * 128 : nwarps * 128 + 64;
     const uint32_t full_s = smem_u32(bars), empty_s = full_s + 8 * kMaxDepth;
 
@@ -274,7 +302,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     const int seg_bytes = min(my_slices * 128, p.row_bytes - slice0 * 128);
     auto tile_rows = [&](int step) { return min(16, p.N - (cta_in_split + step * p.ctas_per_split) * 16); };
     auto expect = [&](int step) {
-        uint32_t bytes = (uint32_t)(SETS * tile_rows(step) * seg_bytes);
+        uint32_t bytes = lsu ? 0u : (uint32_t)(SETS * tile_rows(step) * seg_bytes);
         if (p.bulk_params)
             bytes += (uint32_t)(SETS * (p.scale_tile_bytes + p.zp_tile_bytes));
         mbar_arrive_expect_tx(full_s + 8 * (step % p.depth), bytes);
@@ -284,7 +312,11 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         const uint32_t bar = full_s + 8 * slot;
         const int tile = cta_in_split + step * p.ctas_per_split;
         const int rows = tile_rows(step);
-        if (whole_rows)
+        if (lsu)
+        {
+            // the arithmetic warps fetch their own weights
+        }
+        else if (whole_rows)
         {
             if (lane < SETS)
                 bulk_load(ring_s + (uint32_t)((slot * SETS + lane) * 16 * row_stride),
@@ -327,13 +359,15 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             mbar_init(full_s + 8 * lane, 1);
             mbar_init(empty_s + 8 * lane, (uint32_t)nwarps);
             fence_barrier_init();
-            if (lane < nsteps)
+            if (lane < nsteps && use_full)
                 expect(lane);
         }
         NNF_TRACE_PRODUCER(1);
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"r"(nthreads + 32) : "memory"); // barriers are ready
         NNF_TRACE_PRODUCER(2);
+        if (!use_full)
+            return; // nothing travels through the slots' barriers
         for (int i = 0; i < p.depth && i < nsteps; i++)
             copy(i);
         NNF_TRACE_PRODUCER(3);
@@ -366,6 +400,42 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         unit_of[l] = u;
         grp_of[l] = (u * F::UE) / p.group;
     }
+    // Shared-memory addresses that never change for this lane: its 16 bytes of rows g / g + 8 of slot 0 (unit 1
+    // sits 64 bytes further).
+    const uint32_t wrow[2] = {ring_s + (uint32_t)(warp * 128 + g * row_stride + t * 16),
+                              ring_s + (uint32_t)(warp * 128 + (g + 8) * row_stride + t * 16)};
+    const uint32_t wset_bytes = (uint32_t)(16 * row_stride);
+    // With per-thread fetching a thread asks for exactly the four 16-byte pieces per weight set that it will read,
+    // so no other thread is involved and no barrier guards them: cp.async groups, one per tile, the ring's depth
+    // in flight.  Rows past N read row N - 1 (never stored); a unit past the end of the row is skipped (its
+    // activations are zero and the unpacking makes finite numbers of any bits).
+    auto fetch_tile = [&](int step) {
+        const int slot = step % p.depth;
+        const int tile = cta_in_split + step * p.ctas_per_split;
+#pragma unroll
+        for (int s = 0; s < SETS; s++)
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+            {
+                const int row = min(tile * 16 + g + 8 * h, p.N - 1);
+                const uint8_t* src = (s == 0 ? p.wq[0] : p.wq[1]) + (size_t)row * p.row_bytes + slice * 128 + t * 16;
+                const uint32_t dst = wrow[h] + (uint32_t)(slot * SETS + s) * wset_bytes;
+                if (unit_ok[0])
+                    cp_async16(dst, src);
+                if (unit_ok[1])
+                    cp_async16(dst + 64, src + 64);
+            }
+    };
+    if (lsu)
+    {
+        // The first tile leaves before anything else happens (weights are constants: this needs no
+        // griddepcontrol.wait).  The rest of the ring follows once the activation loads are out, which would
+        // otherwise queue behind 160 KB of weights.  One group per slot, empty ones included, keeps the count uniform.
+        if (nsteps > 0 && has_slice)
+            fetch_tile(0);
+        cp_async_commit();
+    }
+
     // Byte offsets of this lane's scales / zero-points inside a slot's parameter block: rows g and g + 8 of the
     // tile, groups of the two units of the slice.
     const int sbytes = p.scale_f32 ? 4 : 2;
@@ -392,6 +462,32 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     for (int mb = 0; mb < MB; mb++)
         ss_local[mb] = 0.f;
     const bool plain = !XSPLIT && !p.x_f32 && !p.rmsnorm; // fp16 activations used as they are
+    // fp16 activations: all loads first, so that they are on their way before the bulk of the weight requests
+    uint4 xraw[2][MB][F::LE / 8];
+    if (plain)
+    {
+#pragma unroll
+        for (int l = 0; l < 2; l++)
+#pragma unroll
+            for (int mb = 0; mb < MB; mb++)
+            {
+                const int m = g + 8 * mb;
+                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __half*>(p.x) + (size_t)m * p.K +
+                                                                 unit_of[l] * F::UE + t * F::LE);
+#pragma unroll
+                for (int j = 0; j < F::LE / 8; j++)
+                    xraw[l][mb][j] = (unit_ok[l] && m < p.M) ? __ldg(src + j) : make_uint4(0u, 0u, 0u, 0u);
+            }
+    }
+    if (lsu)
+    {
+        for (int i = 1; i < p.depth; i++)
+        {
+            if (i < nsteps && has_slice)
+                fetch_tile(i);
+            cp_async_commit();
+        }
+    }
 #pragma unroll
     for (int l = 0; l < 2; l++)
     {
@@ -405,12 +501,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             {
                 // Element order inside a fragment mirrors the order the weight unpacking produces:
                 // uint4 word i yields pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7); uint8 word i yields (b0,b1) (b2,b3).
-                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __half*>(p.x) +
-                                                                 (size_t)m * p.K + k0);
 #pragma unroll
                 for (int j = 0; j < F::LE / 8; j++)
                 {
-                    const uint4 v = live ? __ldg(src + j) : make_uint4(0u, 0u, 0u, 0u);
+                    const uint4 v = xraw[l][mb][j];
                     if (WBITS == 4)
                     {
                         xf[l][mb][0][4 * j + 0] = __byte_perm(v.x, v.z, 0x5410);
@@ -553,10 +647,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     auto row_of = [&](int step, int h) { return min((cta_in_split + step * p.ctas_per_split) * 16 + g + 8 * h, p.N - 1); };
     float tot[SETS][MB][4];
     const uint32_t k6400 = held_constant(0x64006400u), k5400 = held_constant(0x54005400u);
-    // Shared-memory addresses that never change for this lane: its 16 bytes of rows g / g + 8 in slot 0 (unit 1
-    // sits 64 bytes further), and its scales / zero-points in slot 0's parameter block.
-    const uint32_t wrow[2] = {ring_s + (uint32_t)(warp * 128 + g * row_stride + t * 16),
-                              ring_s + (uint32_t)(warp * 128 + (g + 8) * row_stride + t * 16)};
+    // This lane's scales / zero-points in slot 0's parameter block.
     uint32_t sa[2][2], za[2][2];
 #pragma unroll
     for (int l = 0; l < 2; l++)
@@ -564,7 +655,6 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         for (int h = 0; h < 2; h++)
             sa[l][h] = pring_s + (uint32_t)soff[l][h], za[l][h] = pring_s + (uint32_t)zoff[l][h];
     const int zsh[2] = {(WBITS == 4) ? 4 * (grp_of[0] & 1) : 0, (WBITS == 4) ? 4 * (grp_of[1] & 1) : 0};
-    const uint32_t wset_bytes = (uint32_t)(16 * row_stride);
     const bool one_col = p.M == 1; // only accumulator column 0 carries a batch row
 
     auto compute = [&](int step, int slot) {
@@ -868,8 +958,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         for (int j = 0; j < count; j++)
         {
             const int st = first + j;
-            if (!mbar_wait(full_s + 8 * slot, parity))
+            if (use_full && !mbar_wait(full_s + 8 * slot, parity))
                 timed_out = true;
+            if (lsu)
+                cp_async_wait(p.depth - 1); // this thread's pieces of tile st have landed
             if (st < 5)
                 NNF_TRACE_POINT(4 + 2 * st);
             float4* my = reinterpret_cast<float4*>(red + warp * warp_stride + j * SETS * per_tile);
@@ -896,6 +988,13 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             }
             if (st < 5)
                 NNF_TRACE_POINT(5 + 2 * st);
+            if (lsu)
+            {
+                // what this thread read from the slot is in its registers: ask for the tile that lands there next
+                if (st + p.depth < nsteps && has_slice)
+                    fetch_tile(st + p.depth);
+                cp_async_commit();
+            }
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(empty_s + 8 * slot);
@@ -1060,6 +1159,13 @@ void fill_params(GemvParams& p, const nnf_b200_linear_desc& d, const nnf::GemvPl
     auto ok16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
     p.bulk_params = plan.pset_bytes > 0 && ok16(w->scale) && ok16(w->zp) &&
                     (!plan.dual || (ok16(w2->scale) && ok16(w2->zp)));
+    // How the weights travel: bulk copies from the producer warp, or cp.async from the arithmetic threads
+    // themselves.  NNF_B200_WEIGHT_PATH=bulk|lsu overrides the rule.
+    static const int forced = [] {
+        const char* v = getenv("NNF_B200_WEIGHT_PATH");
+        return !v ? 0 : (v[0] == 'b' ? 1 : (v[0] == 'l' ? 2 : 0));
+    }();
+    p.lsu_weights = forced ? forced == 2 : 0;
     if (plan.splits > 1)
     {
         const size_t cnt = ((size_t)plan.row_tiles * sizeof(unsigned) + 255) / 256 * 256;
