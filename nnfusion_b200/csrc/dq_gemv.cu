@@ -1165,7 +1165,7 @@ void fill_params(GemvParams& p, const nnf_b200_linear_desc& d, const nnf::GemvPl
         const char* v = getenv("NNF_B200_WEIGHT_PATH");
         return !v ? 0 : (v[0] == 'b' ? 1 : (v[0] == 'l' ? 2 : 0));
     }();
-    p.lsu_weights = forced ? forced == 2 : 0;
+    p.lsu_weights = forced ? forced == 2 : plan.lsu_weights;
     if (plan.splits > 1)
     {
         const size_t cnt = ((size_t)plan.row_tiles * sizeof(unsigned) + 255) / 256 * 256;
@@ -1242,6 +1242,10 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
             {
                 fits = true;
                 pl.ctas_per_split = per_split;
+                // Bulk copies move 16 bytes per clock and SM (4.6 TB/s over 148 SMs), cp.async from the arithmetic
+                // threads more, at the price of instructions: measured, the latter wins once the ring has to be
+                // refilled (large matrices) and loses when the whole share fits the ring, or with 16 batch rows.
+                pl.lsu_weights = pl.mb == 1 && steps > pl.depth;
             }
         }
         if (fits || d.split_k > 0)
