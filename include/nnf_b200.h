@@ -4,10 +4,15 @@
  *
  * The library is what the generated `cuda_codegen` runtime links instead of
  * (a) the element-wise Convert / Subtract / Multiply kernels that materialise
- * dequantised weights and (b) the cuBLAS call behind `Dot`.  All entry points
- * are stream-ordered, take plain device pointers, and never allocate device
- * memory: like every kernel of the generated runtime they receive tensors that
- * live in the runtime's own memory pool.
+ * dequantised weights and (b) the cuBLAS call behind `Dot`; for a whole decoder
+ * layer at decode time also instead of (c) the rotary / BatchMatMul / Softmax
+ * chain of one attention step and (d) the NCCL all-reduce at the shard boundary
+ * of a tensor-parallel layer.  All entry points are stream-ordered, take plain
+ * device pointers, and never allocate device memory: like every kernel of the
+ * generated runtime they receive tensors that live in the runtime's own memory
+ * pool.  Kernels are launched as programmatic dependents of whatever precedes
+ * them on the stream (they wait for it before touching anything it may have
+ * written); NNF_B200_NO_OVERLAP=1 in the environment switches that off.
  *
  * Each declaration names the reference interface it stands in for (paths are
  * relative to the reference project root).
