@@ -9,9 +9,11 @@ One JSON line on stdout (rank 0).  Workloads (``--workload``; ``auto`` picks by 
                   the fused linear on the next of 12 weight copies (282 MB in rotation, larger than L2), so every step
                   reads its weights from HBM.  value = algorithmic bytes / time in GB/s.
   mlp70b_decode   (N GPUs, default for N > 1)  LLaMA-70B-shaped SwiGLU MLP at M = 1, uint4 group-128: gate/up split
-                  by column, down by row, one NCCL all-reduce of the fp16 [1,8192] output; a step is the whole MLP
-                  (366 MB of weights, larger than L2).  value = algorithmic bytes of the whole job / time, GB/s.
+                  by column, down by row, the fp16 [1,8192] output summed by the one-shot all-reduce kernel over peer
+                  memory; a step is the whole MLP (366 MB of weights, larger than L2).  value = algorithmic bytes of
+                  the whole job / time, GB/s.
   prefill_gemm    (1 GPU)  uint4 group-128 GEMM, X fp16 [4096,4096], W [11008,4096]; value in TFLOP/s.
+  layer7b_decode  (1 GPU)  one LLaMA-7B-shaped decoder layer at decode time, 2048 cached rows: five launches per step.
 
 ``--impl reference`` times the reference's own CPU path for the same workload (vendored MLAS SGEMM behind the
 Convert / Subtract / Multiply kernels its CPU code generation emits, all host threads) on a bounded sample.
@@ -416,6 +418,59 @@ def run_prefill_gemm(args, torch, sampler_index):
     }
 
 
+def run_layer7b(args, torch, sampler_index):
+    """Configuration 4: one 7B-shaped decoder layer at decode time (2048 cached rows, the token at position 2048), five
+    launches per step; rotation over layer copies (weights + caches 139 MB each) defeats L2."""
+    from nnfusion_b200.decoder_layer import DecoderLayer
+    from nnfusion_b200.linear import default_context
+    H, I, heads, pos, copies = 4096, 11008, 32, 2048, 2
+    ctx = default_context(torch.cuda.current_device())
+    layers = []
+    for _ in range(copies):
+        W = [rand_device_weight(torch, n, k) for n, k in ((H, H), (H, H), (H, H), (H, H), (I, H), (I, H), (H, I))]
+        g1, g2 = (torch.rand(H, device="cuda") * 0.2 + 0.9 for _ in range(2))
+        layer = DecoderLayer(*W, g1, g2, heads=heads, kv_heads=heads, capacity=pos + 1)
+        layer.attn.k_cache.normal_()
+        layer.attn.v_cache.normal_()
+        layers.append(layer)
+    x = torch.randn(1, H, device="cuda").to(torch.float16)
+    y = torch.empty_like(x)
+    ctx.launch_count(reset=True)
+    with ClockSampler(sampler_index) as cs:
+        ms = timed_graph_steps(torch, [(lambda l=l: l(x, pos, out=y)) for l in layers], args.steps, args.warmup)
+    ctx.device_status()
+    kv = 2 * heads * pos * 128 * 2
+    b = layers[0].weight_bytes + kv + 2 * (3 * H + H + H + 2 * H + I + I + H)
+    value = b * args.steps / (ms * 1e-3) / 1e9
+    peaks = measured_peaks()
+    xh, yh = torch.randn(1, H).to(torch.float16).pin_memory(), torch.empty(1, H, dtype=torch.float16).pin_memory()
+
+    def e2e_step(i):
+        x.copy_(xh, non_blocking=True)
+        layers[i % copies](x, pos, out=y)
+        yh.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = min(args.steps, 500)
+    ms_e2e = timed_plain_steps(torch, e2e_step, e2e_steps, 3)
+    return {
+        "metric": "layer7b_decode_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "ms_per_step": ms / args.steps,
+        "dtype": "f16", "scaling": "weak",
+        "config": {"workload": "layer7b_decode: hidden f16 [1,4096], q/k/v/o u4-g128 [4096,4096], gate/up [11008,4096], "
+                               "down [4096,11008], caches f16 2x[32,2049,128], position 2048",
+                   "algorithmic_bytes_per_step": b, "launches_per_step": layers[0].launches,
+                   "l2": f"rotation over {copies} layers ({copies * b / 1e6:.0f} MB) larger than L2",
+                   "launch": "CUDA graph replay of the C-ABI calls"},
+        "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(value / peaks["hbm_gbs"], 4), "traffic": None,
+                     "peak_source": f"of {peaks['source']}", "kernel": "dq_gemv_kernel x4, decode_attention_kernel"},
+        "e2e": {"value": round(b * e2e_steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
+                "h2d_bytes_per_step": H * 2, "d2h_bytes_per_step": H * 2},
+        "gpu_launches": layers[0].launches * args.steps,
+        "clocks": cs.summary(),
+    }
+
+
 def run_mlp70b(args, torch, sampler_index, rank, world, dist):
     """LLaMA-70B-shaped SwiGLU MLP, M = 1 decode, sharded over `world` GPUs.  The shard boundary is closed by the
     one-shot all-reduce kernel over peer memory; the same step with NCCL's all-reduce is timed beside it."""
@@ -491,7 +546,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", default="auto", choices=["auto", "decode_gemv", "mlp70b_decode", "prefill_gemm"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "decode_gemv", "mlp70b_decode", "prefill_gemm", "layer7b_decode"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements at 1 GPU")
     args = ap.parse_args()
 
@@ -554,6 +609,8 @@ def main():
             out, *_ = run_decode_gemv(args, torch, local_rank)
         elif workload == "prefill_gemm":
             out = run_prefill_gemm(args, torch, local_rank)
+        elif workload == "layer7b_decode":
+            out = run_layer7b(args, torch, local_rank)
         else:
             out = run_mlp70b(args, torch, local_rank, rank, world, dist)
         if rank == 0:
