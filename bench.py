@@ -287,7 +287,7 @@ def run_decode_gemv(args, torch, sampler_index):
     return out, ops, x, y
 
 
-def extra_measurements(torch, budget_s=60.0):
+def extra_measurements(torch, budget_s=90.0):
     """Other regimes of the same path at 1 GPU, reported beside the headline (each a few hundred ms of GPU time)."""
     from nnfusion_b200.linear import DequantDot
     peaks = measured_peaks()
@@ -369,12 +369,31 @@ def extra_measurements(torch, budget_s=60.0):
         gbs = b * steps / (ms * 1e-3) / 1e9
         also[name] = {"us": round(ms * 1e3 / steps, 2), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
 
+    def mlp70b_one_gpu(name, steps=200):
+        """The N > 1 workload (whole 70B-shaped MLP at M = 1) on this one GPU, with the same byte count: the
+        one-GPU point of that strong-scaling series."""
+        if time.time() - t_begin > budget_s:
+            return
+        from nnfusion_b200.tp import ShardedMLP
+        hidden, inter, M = 8192, 28672, 1
+        mlps = [ShardedMLP(rand_device_weight(torch, inter, hidden), rand_device_weight(torch, inter, hidden),
+                           rand_device_weight(torch, hidden, inter)) for _ in range(2)]
+        x = torch.randn(M, hidden, device="cuda").to(torch.float16)
+        ms = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in mlps], steps, 3)
+        full = 2 * (linear_bytes(M, inter, hidden) - M * hidden * 2 - M * inter * 2) + M * hidden * 2 + \
+            2 * M * inter * 2 + linear_bytes(M, hidden, inter) - M * inter * 2
+        gbs = full * steps / (ms * 1e-3) / 1e9
+        also[name] = {"us": round(ms * 1e3 / steps, 2), "GB/s": round(gbs, 1), "algorithmic_bytes": full,
+                      "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4),
+                      "note": "same workload and value formula as the --gpus N > 1 lines (mlp70b_decode)"}
+
     gemv("decode_gemv_down_4096x11008", 1, 4096, 11008, 12)
     gemv("config1_u8_perchannel_f32_m16_4096x4096", 16, 4096, 4096, 12, bits=8, group=4096, xdt=torch.float32, sdt=torch.float32)
     gemv("mlp70b_gate_up_silu_m1_28672x8192", 1, 28672, 8192, 2, dual=True, steps=100)
     gemv("mlp70b_down_m1_8192x28672", 1, 8192, 28672, 3, steps=150)
     attention("decode_attention_32x2048x128")
     layer7b("layer7b_decode_pos2048")
+    mlp70b_one_gpu("mlp70b_decode_whole_mlp_m1_one_gpu")
     for M in (256, 1024, 4096):
         gemm(f"prefill_gemm_up_m{M}_11008x4096", M, 11008, 4096)
     gemm("prefill_gemm_down_m4096_4096x11008", 4096, 4096, 11008)
