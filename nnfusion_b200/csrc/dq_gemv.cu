@@ -73,6 +73,7 @@ struct GemvParams
                      // instead of bulk copies: the bulk-copy engine moves 16 bytes per clock and SM, which caps a
                      // launch at 4.6 TB/s over 148 SMs
     int scale_tile_bytes, zp_tile_bytes, pset_bytes; // per tile and weight set
+    int xfrag_bytes; // shared memory per warp for the activation fragments of batch rows 8..15 (0 when M <= 8)
     float eps;
     int slot_floats;
 };
@@ -222,8 +223,10 @@ struct Fmt
 // Shared-memory footprint, shared by host and device.  All sizes in bytes.
 struct SmemLayout
 {
-    size_t ring, pring, bars, red, ss, flags, total;
-    __host__ __device__ SmemLayout(int sets, int mb, int warps, int depth, int batch, int tq, int pset_bytes)
+    size_t ring, pring, bars, red, ss, flags, xsm, total;
+    // xfrag_bytes: activation fragments of batch rows 8..15 kept per warp in shared memory (0 when M <= 8)
+    __host__ __device__ SmemLayout(int sets, int mb, int warps, int depth, int batch, int tq, int pset_bytes,
+                                   int xfrag_bytes)
     {
         ring = (size_t)depth * sets * 16 * (warps * 128 + 64);
         pring = (size_t)depth * sets * pset_bytes;
@@ -231,7 +234,8 @@ struct SmemLayout
         red = sizeof(float) * (size_t)warps * batch * sets * mb * 8 * tq * 4;
         ss = sizeof(float) * ((size_t)warps * 8 * mb + 8 * mb);
         flags = sizeof(int) * kBatch;
-        total = ring + pring + bars + red + ss + flags;
+        xsm = (size_t)warps * xfrag_bytes;
+        total = ring + pring + bars + red + ss + flags + xsm;
     }
 };
 
@@ -251,6 +255,9 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     constexpr int XS = XSPLIT ? 2 : 1;
     constexpr int NF = F::NF;
     constexpr int MPAD = 8 * MB;
+    // 16 batch rows, one weight set: the B fragments of rows 8..15 are parked in shared memory (see xsm_s below).
+    // With two weight sets the ring needs that memory more than the registers need relief (measured).
+    constexpr bool XSM = (MB == 2) && !DUAL;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // The next launch on the stream may start as soon as SMs become free (it waits for this grid's results itself).
@@ -268,7 +275,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
 
     // ring: [depth][SETS][16 rows] of (nwarps * 128 + 64) bytes, warp w's 128 bytes of a row at w * 128; then per
     // slot and set the tile's scales and zero-points
-    const SmemLayout lay(SETS, MB, nwarps, p.depth, p.batch, tq, p.pset_bytes);
+    const SmemLayout lay(SETS, MB, nwarps, p.depth, p.batch, tq, p.pset_bytes, p.xfrag_bytes);
     // (pointers stay derived from the array itself, never from an integer, so that every access below is compiled
     // as a shared-memory access with a 32-bit address rather than as a generic one)
     uint8_t* ring = smem_raw;
@@ -278,6 +285,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     float* ss_w = red + lay.red / sizeof(float);                     // [nwarps][MPAD]
     float* ss_cta = ss_w + nwarps * MPAD;                            // [MPAD]
     int* last_flag = reinterpret_cast<int*>(ss_cta + MPAD);          // [kBatch]
+    // With 16 batch rows the B fragments of rows 8..15 do not fit the register file next to those of rows 0..7
+    // (96 registers per thread): they live here, [warp][unit][xs][fragment pair][lane] x 8 bytes, and every product
+    // fetches its pair with one conflict-free 8-byte load.
+    const uint32_t xsm_s = smem_u32(last_flag + kBatch) + (uint32_t)(warp * p.xfrag_bytes) + (uint32_t)lane * 8u;
     const uint32_t ring_s = smem_u32(ring), pring_s = smem_u32(pring);
     // Shared-memory bytes between two rows of a tile.  When a CTA takes whole rows, a tile is one contiguous piece of
     // memory and arrives with a single copy, rows back to back (the fragment loads then pay a two-way bank conflict,
@@ -611,6 +622,18 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                 c1[l][mb][0] = d[0], c1[l][mb][1] = d[1];
                 c2[l][mb][0] = d[2], c2[l][mb][1] = d[3];
             }
+            if (XSM && mb == 1)
+            {
+                // park the fragments of batch rows 8..15 in shared memory right away: their registers are needed
+#pragma unroll
+                for (int xsn = 0; xsn < XS; xsn++)
+#pragma unroll
+                    for (int f = 0; f < NF; f += 2)
+                        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(
+                                         xsm_s + (uint32_t)(((l * XS + xsn) * (NF / 2) + f / 2) * 256)),
+                                     "r"(xf[l][1][xsn][f]), "r"(xf[l][1][xsn][f + 1])
+                                     : "memory");
+            }
         }
     }
 
@@ -780,12 +803,17 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
 #pragma unroll
                             for (int xsn = 0; xsn < XS; xsn++)
                             {
-                                if (w4 == 0 && q == 0 && xsn == 0) // first product of this chain
-                                    mma16816_first(acc[l][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
-                                                   xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
+                                uint32_t b0, b1;
+                                if (!XSM || mb == 0)
+                                    b0 = xf[l][mb][xsn][f], b1 = xf[l][mb][xsn][f + 1];
                                 else
-                                    mma16816(acc[l][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1],
-                                             xf[l][mb][xsn][f], xf[l][mb][xsn][f + 1]);
+                                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];"
+                                                 : "=r"(b0), "=r"(b1)
+                                                 : "r"(xsm_s + (uint32_t)(((l * XS + xsn) * (NF / 2) + f / 2) * 256)));
+                                if (w4 == 0 && q == 0 && xsn == 0) // first product of this chain
+                                    mma16816_first(acc[l][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1], b0, b1);
+                                else
+                                    mma16816(acc[l][mb], a[0][q], a[1][q], a[0][q + 1], a[1][q + 1], b0, b1);
                             }
                     }
                 }
@@ -1079,7 +1107,8 @@ cudaError_t dispatch(int wbits, const nnf::GemvPlan& plan, const GemvParams& p, 
 // Ring depth and batch length for a CTA of `warps` warps that walks over at most `steps` row tiles, within `cap`
 // bytes of shared memory.  Bytes in flight come first (about 96 KB per SM cover the HBM latency at full rate), then
 // the batch length, which only sets how often the warps meet.
-bool choose_ring(int sets, int mb, int warps, int tq, int pset_bytes, int steps, int cap, int* depth, int* batch)
+bool choose_ring(int sets, int mb, int warps, int tq, int pset_bytes, int xfrag_bytes, int steps, int cap, int* depth,
+                 int* batch)
 {
     const int want_d = std::min(kMaxDepth, std::max(1, steps)), want_b = std::min(kBatch, std::max(1, steps));
     const size_t slot_bytes = (size_t)sets * 16 * (warps * 128 + 64) + (size_t)sets * pset_bytes;
@@ -1093,7 +1122,7 @@ bool choose_ring(int sets, int mb, int warps, int tq, int pset_bytes, int steps,
         last_b = b;
         for (int d = want_d; d >= 1; d--)
         {
-            if ((int)SmemLayout(sets, mb, warps, d, b, tq, pset_bytes).total + 1024 > cap)
+            if ((int)SmemLayout(sets, mb, warps, d, b, tq, pset_bytes, xfrag_bytes).total + 1024 > cap)
                 continue;
             if (d > best_d)
                 best_d = d, best_b = b;
@@ -1154,6 +1183,7 @@ void fill_params(GemvParams& p, const nnf_b200_linear_desc& d, const nnf::GemvPl
     p.scale_tile_bytes = plan.scale_tile_bytes;
     p.zp_tile_bytes = plan.zp_tile_bytes;
     p.pset_bytes = plan.pset_bytes;
+    p.xfrag_bytes = plan.xfrag_bytes;
     p.slot_floats = (int)plan.slot_floats;
     // Bulk copies of the quantisation parameters need whole tiles inside the tensors and 16-byte aligned sources.
     auto ok16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
@@ -1211,6 +1241,8 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
     pl.zp_tile_bytes = 16 * ((d.w_bits == 4) ? (G + 1) / 2 : G);
     // whole tiles of parameters only: a ragged last tile makes the kernel read them with plain loads
     pl.pset_bytes = (d.N % 16 == 0) ? pl.scale_tile_bytes + pl.zp_tile_bytes : 0;
+    // activation fragments of batch rows 8..15: 2 units x (1 or 2 halves of fp32 x) x NF/2 pairs x 32 lanes x 8 bytes
+    pl.xfrag_bytes = (pl.mb == 2 && !pl.dual) ? 2 * (pl.xsplit ? 2 : 1) * ((d.w_bits == 4 ? 16 : 8) / 2) * 256 : 0;
     const int sms = ctx ? ctx->sm_count : 148;
     const int smem_cap = ctx ? ctx->smem_optin : 227 * 1024;
     const int sets = pl.dual ? 2 : 1;
@@ -1237,8 +1269,8 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
             int per_split = std::max(1, (sms * resident) / pl.splits);
             per_split = std::min(per_split, pl.row_tiles);
             const int steps = (pl.row_tiles + per_split - 1) / per_split;
-            if (choose_ring(sets, pl.mb, pl.warps, pl.tq, pl.pset_bytes, steps, smem_cap / resident, &pl.depth,
-                            &pl.batch))
+            if (choose_ring(sets, pl.mb, pl.warps, pl.tq, pl.pset_bytes, pl.xfrag_bytes, steps, smem_cap / resident,
+                            &pl.depth, &pl.batch))
             {
                 fits = true;
                 pl.ctas_per_split = per_split;
@@ -1256,7 +1288,7 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
         *why = "shared memory: the launch shape does not fit";
         return NNF_B200_ENOTSUP;
     }
-    pl.smem_bytes = SmemLayout(sets, pl.mb, pl.warps, pl.depth, pl.batch, pl.tq, pl.pset_bytes).total;
+    pl.smem_bytes = SmemLayout(sets, pl.mb, pl.warps, pl.depth, pl.batch, pl.tq, pl.pset_bytes, pl.xfrag_bytes).total;
     pl.slot_floats = (size_t)sets * pl.mb * 128 + 8 * pl.mb;
     pl.workspace_bytes = 0;
     if (pl.splits > 1)

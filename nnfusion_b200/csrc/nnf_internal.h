@@ -48,6 +48,7 @@ struct GemvPlan
     int zp_tile_bytes = 0;      // zero-points of one 16-row tile
     int pset_bytes = 0;         // shared memory per ring slot and weight set for both (0: plain loads)
     int lsu_weights = 0;        // weights by per-thread cp.async instead of bulk copies
+    int xfrag_bytes = 0;        // shared memory per warp for the activation fragments of batch rows 8..15
 };
 
 int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
