@@ -281,6 +281,35 @@ NNF_B200_API int nnf_b200_allreduce_oneshot(nnf_b200_ctx* ctx, void* stream, int
                                             const void* const* bufs, void* const* flags, size_t count,
                                             size_t half_stride_bytes, void* out, uint32_t epoch);
 
+/* ---- small-M linear whose result is summed over the ranks of a tensor-parallel group in the same launch ----
+ *
+ * y = sum over ranks r of x_r . dequant(W_r)^T (+ bias or addend, applied once, on the sum): the row-parallel
+ * linear of a sharded layer and the all-reduce that follows it, as one kernel.  In the reference these are a Dot
+ * kernel and cuda::SuperScalerAllReduce (src/nnfusion/core/kernels/cuda_gpu/kernels/allreduce.cpp:18-98).
+ * The CTA that finishes a 16-row tile of the output writes its fp32 sums into this rank's peer-visible buffer,
+ * announces the tile to every peer, waits (bounded) for their announcements of the same tile, reads their sums
+ * with plain peer loads and adds in rank order, so every rank stores the same bits and the exchange of early
+ * tiles overlaps the arithmetic of later ones.
+ *
+ * peers->bufs[r] / flags[r]: rank r's buffer (two halves of M*N floats, half_stride_bytes apart) and flag words
+ * (nnf_b200_linear_allreduce_flag_bytes(desc) bytes, zeroed once, never written by anyone else) as mapped into
+ * this process.  peers->epoch: call number, from 1, +1 per call, the same on every rank -- or 0 to count on the
+ * device (then a captured sequence with an even number of calls can be replayed).  Every rank calls with the same
+ * descriptor.  Restrictions: M <= 16, fp16 output, no RMSNorm prologue, no SiLU*mul epilogue. */
+typedef struct nnf_b200_peers
+{
+    int32_t rank, world;
+    void* const* bufs;
+    void* const* flags;
+    size_t half_stride_bytes;
+    uint32_t epoch;
+} nnf_b200_peers;
+
+NNF_B200_API size_t nnf_b200_linear_allreduce_flag_bytes(const nnf_b200_linear_desc* desc);
+NNF_B200_API int nnf_b200_linear_allreduce(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc* desc,
+                                           const void* x, const nnf_b200_qweight* w, const void* bias, void* y,
+                                           void* workspace, size_t workspace_bytes, const nnf_b200_peers* peers);
+
 /* Reads (and clears) the device-side status word: 0, or NNF_B200_ETIMEDOUT when a
  * bounded wait inside a kernel gave up since the last query.  Synchronises the
  * stream; meant for tests and debugging, not for the hot path. */

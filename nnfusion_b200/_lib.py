@@ -26,6 +26,7 @@ EXPORTS = (
     "nnf_b200_launch_count", "nnf_b200_pack_u4", "nnf_b200_device_status", "nnf_b200_linear_plan",
     "nnf_b200_linear_static_scratch", "nnf_b200_decode_attention_workspace_bytes", "nnf_b200_decode_attention",
     "nnf_b200_allreduce_flag_bytes", "nnf_b200_allreduce_oneshot",
+    "nnf_b200_linear_allreduce_flag_bytes", "nnf_b200_linear_allreduce",
 )
 
 
@@ -47,6 +48,12 @@ class AttnDesc(ctypes.Structure):
         ("rotary_base", ctypes.c_float), ("softmax_scale", ctypes.c_float),
         ("splits", ctypes.c_int32), ("dtype", ctypes.c_int32), ("reserved", ctypes.c_int32 * 4),
     ]
+
+
+class Peers(ctypes.Structure):
+    _fields_ = [("rank", ctypes.c_int32), ("world", ctypes.c_int32), ("bufs", ctypes.POINTER(ctypes.c_void_p)),
+                ("flags", ctypes.POINTER(ctypes.c_void_p)), ("half_stride_bytes", ctypes.c_size_t),
+                ("epoch", ctypes.c_uint32)]
 
 
 class QWeight(ctypes.Structure):
@@ -89,6 +96,10 @@ def load() -> ctypes.CDLL:
     L.nnf_b200_decode_attention_workspace_bytes.argtypes = [vp, ctypes.POINTER(AttnDesc)]
     L.nnf_b200_decode_attention_workspace_bytes.restype = sz
     L.nnf_b200_decode_attention.argtypes = [vp, vp, ctypes.POINTER(AttnDesc), vp, vp, vp, vp, vp, vp, vp, sz]
+    L.nnf_b200_linear_allreduce_flag_bytes.argtypes = [ctypes.POINTER(LinearDesc)]
+    L.nnf_b200_linear_allreduce_flag_bytes.restype = sz
+    L.nnf_b200_linear_allreduce.argtypes = [vp, vp, ctypes.POINTER(LinearDesc), vp, ctypes.POINTER(QWeight), vp, vp,
+                                            vp, sz, ctypes.POINTER(Peers)]
     L.nnf_b200_allreduce_flag_bytes.argtypes = [sz]
     L.nnf_b200_allreduce_flag_bytes.restype = sz
     L.nnf_b200_allreduce_oneshot.argtypes = [vp, vp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(vp),

@@ -74,6 +74,12 @@ struct GemvParams
                      // launch at 4.6 TB/s over 148 SMs
     int scale_tile_bytes, zp_tile_bytes, pset_bytes; // per tile and weight set
     int xfrag_bytes; // shared memory per warp for the activation fragments of batch rows 8..15 (0 when M <= 8)
+    // Sum over the ranks of a tensor-parallel group inside this launch (ar_world > 1): see the end of flush().
+    const char* ar_bufs[8]; // every rank's fp32 partial-output buffer (two halves), own included, as mapped here
+    uint32_t* ar_flags[8];  // every rank's flag words [row tile][sender], then one call counter per row tile
+    size_t ar_half_stride;  // bytes between the two halves of a buffer
+    uint32_t ar_epoch;      // call number from the host, or 0: counted in the words after the flags
+    int ar_rank, ar_world;
     float eps;
     int slot_floats;
 };
@@ -233,7 +239,7 @@ struct SmemLayout
         bars = 8 * 2 * kMaxDepth;
         red = sizeof(float) * (size_t)warps * batch * sets * mb * 8 * tq * 4;
         ss = sizeof(float) * ((size_t)warps * 8 * mb + 8 * mb);
-        flags = sizeof(int) * kBatch;
+        flags = sizeof(int) * (2 * kBatch + 4); // last-arriver flags, call numbers, "all peers answered"
         xsm = (size_t)warps * xfrag_bytes;
         total = ring + pring + bars + red + ss + flags + xsm;
     }
@@ -288,7 +294,9 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     // With 16 batch rows the B fragments of rows 8..15 do not fit the register file next to those of rows 0..7
     // (96 registers per thread): they live here, [warp][unit][xs][fragment pair][lane] x 8 bytes, and every product
     // fetches its pair with one conflict-free 8-byte load.
-    const uint32_t xsm_s = smem_u32(last_flag + kBatch) + (uint32_t)(warp * p.xfrag_bytes) + (uint32_t)lane * 8u;
+    uint32_t* ep_s = reinterpret_cast<uint32_t*>(last_flag + kBatch); // [kBatch] call number per tile of the batch
+    int* ar_ok = reinterpret_cast<int*>(ep_s + kBatch);               // have all peers answered?
+    const uint32_t xsm_s = smem_u32(ar_ok + 4) + (uint32_t)(warp * p.xfrag_bytes) + (uint32_t)lane * 8u;
     const uint32_t ring_s = smem_u32(ring), pring_s = smem_u32(pring);
     // Shared-memory bytes between two rows of a tile.  When a CTA takes whole rows, a tile is one contiguous piece of
     // memory and arrives with a single copy, rows back to back (the fragment loads then pay a two-way bank conflict,
@@ -892,11 +900,107 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         return v;
     };
 
+    // ---- summing over the ranks of a tensor-parallel group, fused into the launch (ar_world > 1)
+    // The CTA that holds the final sum of a row tile on this rank (for splits == 1 the tile's own CTA, otherwise the
+    // split that arrived last) writes it as fp32 into this rank's peer-visible buffer, tells every peer "tile t,
+    // call e" with one release store, waits (bounded) for the peers' words for the same tile, reads their sums
+    // with plain peer loads and adds everything in rank order: every rank stores the same bits.  Calls alternate
+    // between the two halves of the buffers (half = e & 1): a rank can be one call ahead of a peer that is still
+    // reading a tile, never two, because the same tile's flag of the call in between is needed first.  Nothing here
+    // waits on a CTA of this GPU, and the peers' CTAs announce before they wait, so no cycle of waits can form.
+    const bool ar = p.ar_world > 1;
+    auto ar_exchange = [&](int first, int count, bool by_last_flag) {
+        auto owns = [&](int j) { return !by_last_flag || last_flag[j] != 0; };
+        uint32_t* counters = p.ar_flags[p.ar_rank] + (size_t)p.row_tiles * 8;
+        // 0. the call number of every tile of the batch that this CTA finishes
+        if (tid < count && owns(tid))
+        {
+            const int rt = cta_in_split + (first + tid) * p.ctas_per_split;
+            uint32_t e = p.ar_epoch;
+            if (e == 0)
+            {
+                e = __ldcg(counters + rt) + 1; // only the CTA that finishes the tile touches the word
+                if (e == 0)
+                    e = 2;                     // 0 means "count for me": skip it, keeping the parity
+            }
+            ep_s[tid] = e;
+        }
+        if (tid == 0)
+            *ar_ok = 1;
+        named_barrier(1, nthreads);
+    };
+    auto ar_finish = [&](int first, int count, bool by_last_flag) {
+        auto owns = [&](int j) { return !by_last_flag || last_flag[j] != 0; };
+        uint32_t* counters = p.ar_flags[p.ar_rank] + (size_t)p.row_tiles * 8;
+        __threadfence_system(); // this rank's sums (written by the caller) before its announcements
+        named_barrier(1, nthreads);
+        // 1. announce to every peer, 2. wait for every peer: thread (tile j, peer r)
+        if (tid < count * p.ar_world)
+        {
+            const int j = tid / p.ar_world, r = tid - j * p.ar_world;
+            if (r != p.ar_rank && owns(j))
+            {
+                const int rt = cta_in_split + (first + j) * p.ctas_per_split;
+                const uint32_t e = ep_s[j];
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ar_flags[r] + (size_t)rt * 8 + p.ar_rank), "r"(e)
+                             : "memory");
+                const uint32_t* mine = p.ar_flags[p.ar_rank] + (size_t)rt * 8 + r;
+                bool seen = false;
+                for (uint32_t i = 0; i < (1u << 21) && !seen; i++)
+                {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+                    seen = (int32_t)(v - e) >= 0;
+                    if (!seen)
+                        __nanosleep(40);
+                }
+                if (!seen)
+                {
+                    *ar_ok = 0;
+                    atomicExch(p.status, 1);
+                }
+            }
+        }
+        if (p.ar_epoch == 0 && tid < count && owns(tid))
+            __stcg(counters + cta_in_split + (first + tid) * p.ctas_per_split, ep_s[tid]);
+        named_barrier(1, nthreads);
+        if (!*ar_ok)
+            return;
+        // 3. everybody's sums in rank order
+        for (int idx = tid; idx < count * per_tile; idx += nthreads)
+        {
+            const int j = idx >> pt_shift, e = idx & (per_tile - 1);
+            if (!owns(j))
+                continue;
+            int row, m, o;
+            decode(e, row, m, o);
+            const int n = (cta_in_split + (first + j) * p.ctas_per_split) * 16 + row;
+            if (m < p.M && n < p.N)
+            {
+                const size_t off = (size_t)(ep_s[j] & 1u) * p.ar_half_stride + ((size_t)m * p.N + n) * sizeof(float);
+                float v = 0.f;
+                for (int r = 0; r < p.ar_world; r++)
+                    v += __ldcv(reinterpret_cast<const float*>(p.ar_bufs[r] + off));
+                store_y(m, n, finish(v, 0.f, 0.f, m, n));
+            }
+        }
+    };
+    // Where a finished sum goes: to y, or (summing over ranks) into this rank's peer-visible buffer.
+    auto emit = [&](int j, int m, int n, float a0, float a1, float ssum) {
+        if (!ar)
+            store_y(m, n, finish(a0, a1, ssum, m, n));
+        else
+            *reinterpret_cast<float*>(const_cast<char*>(p.ar_bufs[p.ar_rank]) + (size_t)(ep_s[j] & 1u) * p.ar_half_stride +
+                                      ((size_t)m * p.N + n) * sizeof(float)) = a0;
+    };
+
     // Add up the warps' partial sums of tiles [first, first + count) and write the results out.
     auto flush = [&](int first, int count) {
         named_barrier(1, nthreads);
         if (p.splits == 1)
         {
+            if (ar)
+                ar_exchange(first, count, false);
             for (int idx = tid; idx < count * per_tile; idx += nthreads)
             {
                 const int j = idx >> pt_shift, e = idx & (per_tile - 1);
@@ -904,9 +1008,10 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                 decode(e, row, m, o);
                 const int n = (cta_in_split + (first + j) * p.ctas_per_split) * 16 + row;
                 if (m < p.M && n < p.N)
-                    store_y(m, n, finish(sum_warps(j, 0, e), DUAL ? sum_warps(j, 1, e) : 0.f,
-                                         p.rmsnorm ? ss_cta[m] : 0.f, m, n));
+                    emit(j, m, n, sum_warps(j, 0, e), DUAL ? sum_warps(j, 1, e) : 0.f, p.rmsnorm ? ss_cta[m] : 0.f);
             }
+            if (ar)
+                ar_finish(first, count, false);
         }
         else
         {
@@ -945,6 +1050,8 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             }
             named_barrier(1, nthreads);
             __threadfence();
+            if (ar)
+                ar_exchange(first, count, true);
             // 3. fixed-order sum over the splits
             for (int idx = tid; idx < count * per_tile; idx += nthreads)
             {
@@ -967,9 +1074,11 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                         if (p.rmsnorm)
                             ssum += __ldcg(slot + SETS * MB * 128 + m);
                     }
-                    store_y(m, n, finish(a0, a1, ssum, m, n));
+                    emit(j, m, n, a0, a1, ssum);
                 }
             }
+            if (ar)
+                ar_finish(first, count, true);
         }
         named_barrier(1, nthreads);
     };
@@ -1141,8 +1250,19 @@ bool choose_ring(int sets, int mb, int warps, int tq, int pset_bytes, int xfrag_
 // Everything the kernel needs to know that does not depend on where the operands live.
 void fill_params(GemvParams& p, const nnf_b200_linear_desc& d, const nnf::GemvPlan& plan, const void* x,
                  const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias, void* y,
-                 int* status, void* workspace)
+                 int* status, void* workspace, const nnf_b200_peers* peers = nullptr)
 {
+    if (peers && peers->world > 1)
+    {
+        for (int r = 0; r < peers->world; r++)
+        {
+            p.ar_bufs[r] = static_cast<const char*>(peers->bufs[r]);
+            p.ar_flags[r] = static_cast<uint32_t*>(peers->flags[r]);
+        }
+        p.ar_half_stride = peers->half_stride_bytes;
+        p.ar_epoch = peers->epoch;
+        p.ar_rank = peers->rank, p.ar_world = peers->world;
+    }
     const int ue = (d.w_bits == 4) ? 128 : 64;
     p.wq[0] = static_cast<const uint8_t*>(w->wq);
     p.scale[0] = w->scale;
@@ -1302,11 +1422,11 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
 
 int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan_in,
                 const void* x, const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
-                const void* bias, void* y, void* workspace)
+                const void* bias, void* y, void* workspace, const nnf_b200_peers* peers)
 {
     const GemvPlan& plan = plan_in;
     GemvParams p{};
-    fill_params(p, d, plan, x, w, w2, gain, bias, y, ctx->dev_status, workspace);
+    fill_params(p, d, plan, x, w, w2, gain, bias, y, ctx->dev_status, workspace, peers);
     const int grid = plan.splits * plan.ctas_per_split;
     cudaError_t e = dispatch(d.w_bits, plan, p, grid, stream);
     if (e != cudaSuccess)

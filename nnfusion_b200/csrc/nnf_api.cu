@@ -317,9 +317,55 @@ int nnf_b200_workspace_reset(nnf_b200_ctx* ctx, void* stream, void* workspace, s
     return NNF_B200_OK;
 }
 
+size_t nnf_b200_linear_allreduce_flag_bytes(const nnf_b200_linear_desc* desc)
+{
+    if (!desc || desc->N < 1)
+        return 0;
+    return (size_t)((desc->N + 15) / 16) * 9 * sizeof(uint32_t); // [row tile][8 senders], then [row tile] counters
+}
+
+static int linear_impl(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc* desc, const void* x,
+                       const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias,
+                       void* y, void* workspace, size_t workspace_bytes, const nnf_b200_peers* peers);
+
 int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc* desc, const void* x,
                     const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias,
                     void* y, void* workspace, size_t workspace_bytes)
+{
+    return linear_impl(ctx, stream, desc, x, w, w2, gain, bias, y, workspace, workspace_bytes, nullptr);
+}
+
+int nnf_b200_linear_allreduce(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc* desc, const void* x,
+                              const nnf_b200_qweight* w, const void* bias, void* y, void* workspace,
+                              size_t workspace_bytes, const nnf_b200_peers* peers)
+{
+    if (!ctx)
+        return NNF_B200_EINVAL;
+    if (!peers || !desc)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "null descriptor or peer description");
+    if (peers->world < 1 || peers->world > 8 || peers->rank < 0 || peers->rank >= peers->world || !peers->bufs ||
+        !peers->flags)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "1 <= world <= 8, 0 <= rank < world, non-null pointer arrays");
+    if (desc->M > 16 || desc->kernel == NNF_B200_KERNEL_GEMM || desc->prologue != NNF_B200_PROLOGUE_NONE ||
+        desc->epilogue == NNF_B200_EPILOGUE_SILU_MUL || desc->y_dtype != NNF_B200_F16)
+        return nnf::set_error(ctx, NNF_B200_ENOTSUP,
+                              "the fused sum over ranks serves the small-M kernel (M <= 16), fp16 output, no RMSNorm "
+                              "prologue and no SiLU*mul epilogue");
+    if (peers->half_stride_bytes < (size_t)desc->M * desc->N * sizeof(float) || peers->half_stride_bytes % 16 != 0)
+        return nnf::set_error(ctx, NNF_B200_EINVAL, "half_stride_bytes must hold M*N floats and be a multiple of 16");
+    for (int r = 0; r < peers->world; r++)
+    {
+        if (!peers->bufs[r] || !peers->flags[r])
+            return nnf::set_error(ctx, NNF_B200_EINVAL, "null peer buffer or flag pointer");
+        if (!aligned16(peers->bufs[r]) || (reinterpret_cast<uintptr_t>(peers->flags[r]) & 3u))
+            return nnf::set_error(ctx, NNF_B200_EALIGN, "peer buffers 16-byte aligned, flags 4-byte aligned");
+    }
+    return linear_impl(ctx, stream, desc, x, w, nullptr, nullptr, bias, y, workspace, workspace_bytes, peers);
+}
+
+static int linear_impl(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc* desc, const void* x,
+                       const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias,
+                       void* y, void* workspace, size_t workspace_bytes, const nnf_b200_peers* peers)
 {
     int rc = validate(ctx, desc);
     if (rc != NNF_B200_OK)
@@ -357,8 +403,10 @@ int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_desc*
         if (plan.workspace_bytes > 0 && (!workspace || workspace_bytes < plan.workspace_bytes))
             return nnf::set_error(ctx, NNF_B200_EWORKSPACE,
                                   "workspace of " + std::to_string(plan.workspace_bytes) + " bytes required");
-        return nnf::gemv_launch(ctx, s, d, plan, x, w, w2, gain, bias, y, workspace);
+        return nnf::gemv_launch(ctx, s, d, plan, x, w, w2, gain, bias, y, workspace, peers);
     }
+    if (peers)
+        return nnf::set_error(ctx, NNF_B200_ENOTSUP, "the fused sum over ranks needs the small-M kernel");
     std::string why;
     rc = nnf::gemm_supported(ctx, d, &why);
     if (rc != NNF_B200_OK)

@@ -66,7 +66,7 @@ const CUtensorMap* weight_tensor_map(nnf_b200_ctx* ctx, const void* base, int ro
 int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan, std::string* why);
 int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan,
                 const void* x, const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
-                const void* bias, void* y, void* workspace);
+                const void* bias, void* y, void* workspace, const nnf_b200_peers* peers = nullptr);
 int gemv_configure(nnf_b200_ctx* ctx);
 
 size_t gemm_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d);

@@ -104,13 +104,70 @@ class PeerAllReduce:
         return out
 
 
+class PeerLinear:
+    """Row-parallel linear whose partial results are summed over the ranks inside the same launch
+    (``nnf_b200_linear_allreduce``): y = sum_r x_r . dequant(W_r)^T.  ``weight`` is this rank's K shard."""
+
+    def __init__(self, weight, group, max_rows: int = 16, ctx=None):
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib as L
+        from .linear import DequantDot, default_context
+
+        self.torch, self.ctypes, self.L = torch, ctypes, L
+        dev = weight.wq.device
+        self.ctx = ctx or default_context(dev.index or 0)
+        self.node = DequantDot(weight, ctx=self.ctx)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("the fused sum serves up to 8 ranks of one node")
+        self.max_rows = max_rows
+        self.half = (max_rows * weight.N * 4 + 255) // 256 * 256
+        d = self.node.desc(1, torch.float16)
+        flag_bytes = int(self.ctx.lib.nnf_b200_linear_allreduce_flag_bytes(ctypes.byref(d)))
+        self.flag_off = 2 * self.half
+        total = (self.flag_off + flag_bytes + 255) // 256 * 256
+        self.mem = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self.mem.zero_()
+        torch.cuda.synchronize()
+        self.handle = symm_mem.rendezvous(self.mem, group)
+        dist.barrier(group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        vp = ctypes.c_void_p
+        self._bufs = (vp * self.world)(*ptrs)
+        self._flags = (vp * self.world)(*[p + self.flag_off for p in ptrs])
+        self._peers = L.Peers(self.rank, self.world, self._bufs, self._flags, self.half, 0)  # calls counted on device
+
+    def __call__(self, x, out=None):
+        torch, ctypes = self.torch, self.ctypes
+        M = x.shape[0]
+        if M > self.max_rows or x.dtype != torch.float16:
+            raise ValueError("the fused sum serves fp16 activations of at most max_rows rows")
+        if out is None:
+            out = torch.empty((M, self.node.w.N), dtype=torch.float16, device=x.device)
+        d = self.node.desc(M, x.dtype)
+        ws = self.node.workspace(d)
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = self.ctx.lib.nnf_b200_linear_allreduce(
+            self.ctx.handle, stream, ctypes.byref(d), x.data_ptr(), ctypes.byref(self.node._abi_w), None,
+            out.data_ptr(), ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+            ctypes.byref(self._peers))
+        self.ctx.check(rc)
+        return out
+
+
 class ShardedMLP:
     """This rank's part of y = down(SiLU(gate(x)) * up(x)), followed by the all-reduce.
 
     ``gate``/``up``/``down`` are device weights already sharded for this rank (``DeviceWeight``); ``group`` is the
     ``torch.distributed`` process group, or None for a single GPU.  ``gain`` enables the fused RMSNorm prologue of
     the gate/up linear (small-M kernel only).  ``reduce``: "nccl" (``torch.distributed.all_reduce``) or "peer" (the
-    one-shot kernel over peer memory, fp16 outputs of at most ``peer_max_rows`` rows).
+    one-shot kernel over peer memory, fp16 outputs of at most ``peer_max_rows`` rows) or "fused" (the down linear
+    sums over the ranks inside its own launch, same limits).
     """
 
     def __init__(self, gate, up, down, group=None, gain=None, eps: float = 1e-6, reduce: str = "nccl",
@@ -126,8 +183,9 @@ class ShardedMLP:
         self.hidden = down.N
         self._h = {}
         self._y = {}
-        if reduce not in ("nccl", "peer"):
-            raise ValueError("reduce must be 'nccl' or 'peer'")
+        if reduce not in ("nccl", "peer", "fused"):
+            raise ValueError("reduce must be 'nccl', 'peer' or 'fused'")
+        self.fused = PeerLinear(down, group, peer_max_rows) if (reduce == "fused" and group is not None) else None
         # (several layers may share one PeerAllReduce: calls are ordered on the stream)
         self.peer = peer if peer is not None else (
             PeerAllReduce(peer_max_rows * down.N, group) if (reduce == "peer" and group is not None) else None)
@@ -143,6 +201,8 @@ class ShardedMLP:
     def __call__(self, x):
         h, y = self.buffers(x.shape[0], x.dtype, x.device)
         self.gate_up(x, out=h)      # [M, inter / world]: SiLU(gate) * up, local
+        if self.fused is not None and x.shape[0] <= self.peer_max_rows and x.dtype == self.torch.float16:
+            return self.fused(h, out=y)  # partial sums exchanged and added inside the launch
         if self.peer is not None and x.shape[0] <= self.peer_max_rows and x.dtype == self.torch.float16:
             part = self.peer.addend((x.shape[0], self.hidden))
             self.down(h, out=part)  # partial sum over this rank's K shard, straight into peer-visible memory
@@ -154,4 +214,4 @@ class ShardedMLP:
 
     @property
     def launches_per_step(self) -> int:
-        return 2
+        return 3 if self.peer is not None else 2

@@ -109,3 +109,83 @@ def test_invalid_arguments():
     assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4096, 100, o, 1) == L.EINVAL
     assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4100, 16384, o, 1) == L.ENOTSUP
     assert lib.nnf_b200_allreduce_oneshot(h, None, 0, 2, pb, pf, 4096, 8192, o + 2, 1) == L.EALIGN
+
+
+@pytest.mark.parametrize("M,N,K,world,rank", [(1, 272, 1024, 2, 0), (16, 96, 512, 3, 1), (3, 512, 4608, 4, 2)])
+def test_linear_with_fused_sum_over_ranks(M, N, K, world, rank):
+    """nnf_b200_linear_allreduce on one GPU: the peers' buffers hold known partial sums and their flags were set by
+    the host, so nothing waits; K = 4608 exercises split-K (the last-arriving split does the exchange)."""
+    import torch
+    from nnfusion_b200 import _lib as L
+    from nnfusion_b200 import synth
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+    from tests.util import oracle_linear
+
+    rng = np.random.Generator(np.random.PCG64(1000 + M))
+    x = synth.make_x(rng, M, K, np.float16)
+    w = synth.make_weights(rng, N, K, 4, 128)
+    node = DequantDot(DeviceWeight.from_host(w, "cuda:0"))
+    ctx = node.ctx
+    half = (M * N * 4 + 255) // 256 * 256
+    d = node.desc(M, torch.float16)
+    fb = int(ctx.lib.nnf_b200_linear_allreduce_flag_bytes(ctypes.byref(d)))
+    others = [rng.standard_normal((M, N)).astype(np.float32) for _ in range(world)]
+    bufs, flags = [], []
+    for r in range(world):
+        b = torch.zeros(2 * half // 4, dtype=torch.float32, device="cuda")
+        if r != rank:
+            b[: M * N] = torch.from_numpy(-others[r].reshape(-1)).cuda()                 # half 0: even calls
+            b[half // 4: half // 4 + M * N] = torch.from_numpy(others[r].reshape(-1)).cuda()  # half 1: odd calls
+        bufs.append(b)
+        f = torch.zeros(fb // 4, dtype=torch.int32, device="cuda")
+        flags.append(f)
+    tiles = (N + 15) // 16
+    flags[rank][: tiles * 8].fill_(1000)      # the peers are far ahead: no wait in this test
+    vp = ctypes.c_void_p
+    pb = (vp * world)(*[b.data_ptr() for b in bufs])
+    pf = (vp * world)(*[f.data_ptr() for f in flags])
+    peers = L.Peers(rank, world, pb, pf, half, 0)
+    tx = torch.from_numpy(x).cuda()
+    y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    ws = node.workspace(d)
+    own = oracle_linear(x, w, out_dtype=np.float32).astype(np.float32)
+    s = torch.cuda.current_stream().cuda_stream
+    for call in (1, 2, 3):
+        ctx.check(ctx.lib.nnf_b200_linear_allreduce(
+            ctx.handle, s, ctypes.byref(d), tx.data_ptr(), ctypes.byref(node._abi_w), None, y.data_ptr(),
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, ctypes.byref(peers)))
+        torch.cuda.synchronize()
+        ctx.device_status()
+        sign = 1.0 if call & 1 else -1.0
+        ref = own + sign * sum(others[r] for r in range(world) if r != rank)
+        err = np.abs(y.cpu().numpy().astype(np.float32) - ref).max() / np.abs(ref).max()
+        assert err <= 5e-3, (call, err)
+    # the device counted three calls for every tile, and told every peer so
+    assert (flags[rank].cpu().numpy()[tiles * 8: tiles * 9] == 3).all()
+    for r in range(world):
+        if r != rank:
+            assert (flags[r].cpu().numpy()[: tiles * 8].reshape(tiles, 8)[:, rank] == 3).all()
+
+
+def test_fused_sum_rejects_what_it_does_not_serve():
+    import torch
+    from nnfusion_b200 import _lib as L
+    from nnfusion_b200 import synth
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+
+    x, w = synth.u4g128(7, 32, 64, 256)
+    node = DequantDot(DeviceWeight.from_host(w, "cuda:0"))
+    ctx = node.ctx
+    d = node.desc(32, torch.float16)      # 32 rows: not the small-M kernel
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    vp = ctypes.c_void_p
+    pb, pf = (vp * 2)(buf.data_ptr(), buf.data_ptr()), (vp * 2)(buf.data_ptr(), buf.data_ptr())
+    peers = L.Peers(0, 2, pb, pf, 32 * 64 * 4, 1)
+    rc = ctx.lib.nnf_b200_linear_allreduce(ctx.handle, None, ctypes.byref(d), buf.data_ptr(),
+                                           ctypes.byref(node._abi_w), None, buf.data_ptr(), None, 0, ctypes.byref(peers))
+    assert rc == L.ENOTSUP
+    d = node.desc(4, torch.float16)
+    peers = L.Peers(2, 2, pb, pf, 4 * 64 * 4, 1)
+    rc = ctx.lib.nnf_b200_linear_allreduce(ctx.handle, None, ctypes.byref(d), buf.data_ptr(),
+                                           ctypes.byref(node._abi_w), None, buf.data_ptr(), None, 0, ctypes.byref(peers))
+    assert rc == L.EINVAL

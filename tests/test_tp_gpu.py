@@ -46,7 +46,8 @@ dist.destroy_process_group()
 '''
 
 
-@pytest.mark.parametrize("M,reduce,calls", [(1, "nccl", 1), (64, "nccl", 1), (1, "peer", 5), (16, "peer", 4)])
+@pytest.mark.parametrize("M,reduce,calls", [(1, "nccl", 1), (64, "nccl", 1), (1, "peer", 5), (16, "peer", 4),
+                                            (1, "fused", 5), (16, "fused", 4)])
 def test_two_gpu_sharded_mlp_matches_oracle(tmp_path, M, reduce, calls):
     import torch
     if torch.cuda.device_count() < 2:
