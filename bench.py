@@ -492,7 +492,8 @@ def run_layer7b(args, torch, sampler_index):
 
 def run_mlp70b(args, torch, sampler_index, rank, world, dist):
     """LLaMA-70B-shaped SwiGLU MLP, M = 1 decode, sharded over `world` GPUs.  The shard boundary is closed by the
-    one-shot all-reduce kernel over peer memory; the same step with NCCL's all-reduce is timed beside it."""
+    one-shot all-reduce kernel over peer memory (launched as a programmatic dependent of the down linear); the same
+    step with the sum fused into the down linear's own launch, and with NCCL's all-reduce, is timed beside it."""
     from nnfusion_b200.linear import default_context
     from nnfusion_b200.tp import PeerAllReduce, ShardedMLP, mlp_shapes
     hidden, inter, M = 8192, 28672, 1
@@ -525,8 +526,9 @@ def run_mlp70b(args, torch, sampler_index, rank, world, dist):
         nsteps = min(steps, 400)
         ms_n = timed_plain_steps(torch, lambda i: nccl[i % ncopies](x), nsteps, 5, dist)
         also["same_step_with_nccl_allreduce"] = {"us": round(ms_n * 1e3 / nsteps, 2), "launch": "plain launches"}
-        ms_p = timed_plain_steps(torch, lambda i: mlps[i % ncopies](x), nsteps, 6, dist)
-        also["peer_allreduce_plain_launches"] = {"us": round(ms_p * 1e3 / nsteps, 2)}
+        fused = [ShardedMLP(*w, group=group, reduce="fused") for w in weights]
+        ms_t = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in fused], steps, 4, dist)
+        also["sum_fused_into_the_down_linear"] = {"us": round(ms_t * 1e3 / steps, 2), "launch": "CUDA graph replay"}
     xh = torch.randn(M, hidden).to(torch.float16).pin_memory()
     yh = torch.empty(M, hidden, dtype=torch.float16).pin_memory()
 

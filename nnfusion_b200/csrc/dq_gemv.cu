@@ -932,7 +932,8 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     auto ar_finish = [&](int first, int count, bool by_last_flag) {
         auto owns = [&](int j) { return !by_last_flag || last_flag[j] != 0; };
         uint32_t* counters = p.ar_flags[p.ar_rank] + (size_t)p.row_tiles * 8;
-        __threadfence_system(); // this rank's sums (written by the caller) before its announcements
+        // this rank's sums (written by all threads above) are ordered before the announcements below by the barrier
+        // and the release stores, which are cumulative over what the barrier made visible to the storing thread
         named_barrier(1, nthreads);
         // 1. announce to every peer, 2. wait for every peer: thread (tile j, peer r)
         if (tid < count * p.ar_world)
