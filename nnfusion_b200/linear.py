@@ -208,6 +208,35 @@ class DequantDot:
         self.run_raw(d, x.data_ptr(), out.data_ptr(), ws, addend.data_ptr() if addend is not None else None)
         return out
 
+    def host_entry(self, x_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
+        """The call with host buffers, like the generated runtime's ``kernel_entry_host`` (``-fhost_entry``:
+        ``src/nnfusion/engine/pass/codegen/cuda_codegen_pass.cpp:117-168``): copy x to the device, run the node, copy y
+        back, return when y is on the host.  Both tensors must be pinned.  The three operations are captured once
+        per (x, y) pair as a CUDA graph, so a call costs one graph launch and one stream synchronisation."""
+        if not (x_host.is_pinned() and y_host.is_pinned()):
+            raise ValueError("host_entry needs pinned host tensors")
+        key = (x_host.data_ptr(), y_host.data_ptr(), tuple(x_host.shape), x_host.dtype)
+        graphs = self.__dict__.setdefault("_host_graphs", {})
+        if key not in graphs:
+            dev = self.w.wq.device
+            x_dev = torch.empty(x_host.shape, dtype=x_host.dtype, device=dev)
+            y_dev = torch.empty(y_host.shape, dtype=y_host.dtype, device=dev)
+            self(x_dev, out=y_dev)                  # workspace allocation and first-call set-up outside the capture
+            torch.cuda.synchronize()
+            stream = torch.cuda.Stream(device=dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                with torch.cuda.graph(g, stream=stream):
+                    x_dev.copy_(x_host, non_blocking=True)
+                    self(x_dev, out=y_dev)
+                    y_host.copy_(y_dev, non_blocking=True)
+            graphs[key] = (g, stream, x_dev, y_dev)
+        g, stream, _, _ = graphs[key]
+        with torch.cuda.stream(stream):
+            g.replay()
+        stream.synchronize()
+        return y_host
+
     def run_raw(self, d: L.LinearDesc, x_ptr: int, y_ptr: int, ws: Optional[torch.Tensor],
                 addend_ptr: Optional[int] = None) -> None:
         """The C-ABI call itself, on the current stream, with raw device addresses."""

@@ -72,3 +72,22 @@ def test_launch_choice_from_the_database(tmp_path):
     assert orc.max_rel_err(y, oracle_linear(x, w)) <= TOL_F16
     # other shapes fall back to the built-in rule
     assert DequantDot(dw, kernel_db=db).desc(5, torch.float16).kernel == L.KERNEL_AUTO
+
+
+def test_host_entry_copies_in_and_out():
+    # the host-buffer entry point (kernel_entry_host of the generated runtime): pinned x in, pinned y out
+    import torch
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+
+    x, w = synth.u4g128(51, 2, 272, 1024)
+    op = DequantDot(DeviceWeight.from_host(w, "cuda:0"))
+    xh = torch.from_numpy(x).pin_memory()
+    yh = torch.empty((2, 272), dtype=torch.float16).pin_memory()
+    op.host_entry(xh, yh)
+    ref = oracle_linear(x, w)
+    assert orc.max_rel_err(yh.numpy(), ref) <= TOL_F16
+    xh.mul_(2)                                   # new contents, same buffers: the captured graph is reused
+    op.host_entry(xh, yh)
+    assert orc.max_rel_err(yh.numpy(), oracle_linear(xh.numpy(), w)) <= TOL_F16
+    with pytest.raises(ValueError):
+        op.host_entry(torch.from_numpy(x), yh)   # not pinned
