@@ -132,10 +132,18 @@ def timed_graph_steps(torch, step_fns, steps, warmup, dist=None):
         full, rem = divmod(steps, chunk)
         g_full = graph_of(chunk) if full else None
         g_rem = graph_of(rem) if rem else None
-        # graph warm-up: brings the clocks up and pages everything in
-        t0 = time.time()
-        while time.time() - t0 < 0.5:
-            (g_full or g_rem).replay()
+        # graph warm-up: brings the clocks up and pages everything in.  With several ranks every rank must replay
+        # the same number of times (the steps contain exchanges between the ranks: a rank that stopped earlier would
+        # leave the others waiting for it), so the count is fixed there instead of timed.
+        if dist is None:
+            t0 = time.time()
+            while time.time() - t0 < 0.5:
+                (g_full or g_rem).replay()
+                torch.cuda.synchronize()
+        else:
+            dist.barrier()  # capture takes a different time on every rank: start the replays together
+            for _ in range(max(3, 4000 // max(1, chunk))):
+                (g_full or g_rem).replay()
             torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()

@@ -274,7 +274,7 @@ NNF_B200_API int nnf_b200_decode_attention(nnf_b200_ctx* ctx, void* stream, cons
  * (nnf_b200_allreduce_flag_bytes of them) start zeroed and are never written by anyone else; the addend of this
  * call must be complete in its half, in stream order, before the call.  count: fp16 elements, a multiple of 8;
  * bufs 16-byte aligned.
- * A rank whose peers never call gives up after about 0.1 s, writes nothing, and nnf_b200_device_status then
+ * A rank whose peers never call gives up after about 0.4 s, writes nothing, and nnf_b200_device_status then
  * reports NNF_B200_ETIMEDOUT. */
 NNF_B200_API size_t nnf_b200_allreduce_flag_bytes(size_t count);
 NNF_B200_API int nnf_b200_allreduce_oneshot(nnf_b200_ctx* ctx, void* stream, int rank, int world,

@@ -947,7 +947,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                              : "memory");
                 const uint32_t* mine = p.ar_flags[p.ar_rank] + (size_t)rt * 8 + r;
                 bool seen = false;
-                for (uint32_t i = 0; i < (1u << 21) && !seen; i++)
+                for (uint32_t i = 0; i < (1u << 19) && !seen; i++) // roughly 0.4 s
                 {
                     uint32_t v;
                     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");

@@ -25,7 +25,7 @@ namespace
 {
 constexpr int kMaxRanks = 8;
 constexpr int kArThreads = 256;
-constexpr uint32_t kArSpin = 1u << 21; // polls of about 50 ns each: gives up after roughly 0.1 s
+constexpr uint32_t kArSpin = 1u << 19; // polls of just under a microsecond each: gives up after roughly 0.4 s
 
 struct ArParams
 {
