@@ -126,6 +126,9 @@ def timed_graph_steps(torch, step_fns, steps, warmup, dist=None):
         return graphs[count]
 
     with torch.cuda.stream(stream):
+        if dist is not None:
+            torch.cuda.synchronize()
+            dist.barrier()  # set-up takes a different time on every rank; the steps' exchanges have bounded waits
         for i in range(max(warmup, 3)):
             step_fns[i % n]()
         torch.cuda.synchronize()
@@ -168,6 +171,9 @@ def timed_graph_steps(torch, step_fns, steps, warmup, dist=None):
 
 def timed_plain_steps(torch, step_fn, steps, warmup, dist=None):
     """Same contract without graph capture (used where a step contains a collective or host copies)."""
+    if dist is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
     for i in range(max(warmup, 3)):
         step_fn(i)
     torch.cuda.synchronize()
