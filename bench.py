@@ -108,9 +108,30 @@ def linear_bytes(M, N, K, bits=4, group=128, act_bytes=2, scale_bytes=2):
     return N * K * bits // 8 + N * G * scale_bytes + N * ((G + 1) // 2 if bits == 4 else G) + M * K * act_bytes + M * N * act_bytes
 
 
-def timed_graph_steps(torch, step_fns, steps, warmup, dist=None):
+class ExchangeUnhealthy(RuntimeError):
+    """A bounded wait of a peer-memory exchange gave up on some rank during the warm-up (raised on every rank)."""
+
+
+def ranks_healthy(torch, dist, ctx):
+    """True when no rank's context has recorded a device-side wait that gave up (synchronises; every rank gets the
+    same answer, so all of them take the same branch afterwards)."""
+    ok = 1
+    try:
+        ctx.device_status()
+    except Exception as e:  # the status call raises with the kernel's record of where it gave up
+        sys.stderr.write(f"[bench] device status: {e}\n")
+        ok = 0
+    t = torch.tensor([ok], device="cuda", dtype=torch.int32)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item())
+
+
+def timed_graph_steps(torch, step_fns, steps, warmup, dist=None, health=None):
     """Runs `steps` steps (step i calls step_fns[i % len]) replayed from CUDA graphs, timed with CUDA events on the
-    launching stream between barrier + synchronize on both sides.  Returns milliseconds (max over ranks)."""
+    launching stream between barrier + synchronize on both sides.  Returns milliseconds (max over ranks).
+    `health` (several ranks only) is asked after the plain warm-up steps and after a first short graph replay; when
+    it answers False the function raises ExchangeUnhealthy instead of replaying thousands of steps whose waits
+    would each run to their limit."""
     n = len(step_fns)
     stream = torch.cuda.Stream()
     chunk = min(steps, max(n, (1200 // n) * n))  # a multiple of n unless it is all of the steps
@@ -129,9 +150,19 @@ def timed_graph_steps(torch, step_fns, steps, warmup, dist=None):
         if dist is not None:
             torch.cuda.synchronize()
             dist.barrier()  # set-up takes a different time on every rank; the steps' exchanges have bounded waits
-        for i in range(max(warmup, 3)):
+        for i in range(max(warmup, 3) // 2 * 2 if health is not None else max(warmup, 3)):
             step_fns[i % n]()
         torch.cuda.synchronize()
+        if health is not None:
+            if not health():
+                raise ExchangeUnhealthy("during the plain warm-up steps")
+            probe = graph_of(2)  # an even number of steps: the exchanges' two buffer halves stay in step
+            dist.barrier()
+            for _ in range(3):
+                probe.replay()
+            torch.cuda.synchronize()
+            if not health():
+                raise ExchangeUnhealthy("during the first graph replays")
         full, rem = divmod(steps, chunk)
         g_full = graph_of(chunk) if full else None
         g_rem = graph_of(rem) if rem else None
@@ -527,22 +558,41 @@ def run_mlp70b(args, torch, sampler_index, rank, world, dist):
     # every captured graph must hold an even number of steps (see PeerAllReduce): K is timed exactly when it is
     # even, K + 1 otherwise, and the line says which
     steps = args.steps + (args.steps & 1)
+    # With several ranks the warm-up asks every rank whether one of the exchange's bounded waits gave up; if so the
+    # headline is taken with NCCL's all-reduce instead (and says so) rather than from steps that each ran to the limit.
+    health = (lambda: ranks_healthy(torch, dist, ctx)) if world > 1 else None
+    exchange = "one-shot all-reduce of f16 [1,8192] over peer memory" if world > 1 else "one GPU: no exchange"
+    launch = "CUDA graph replay of the C-ABI calls"
     with ClockSampler(sampler_index) as cs:
-        ms = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in mlps], steps, args.warmup, dist if world > 1 else None)
-    ctx.device_status()
+        try:
+            ms = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in mlps], steps, args.warmup,
+                                   dist if world > 1 else None, health)
+            ctx.device_status()
+        except ExchangeUnhealthy as e:
+            sys.stderr.write(f"[bench] peer-memory exchange gave up {e}; timing the step with NCCL's all-reduce\n")
+            ms = None
     full = 2 * (linear_bytes(M, inter, hidden) - M * hidden * 2 - M * inter * 2) + M * hidden * 2 + 2 * M * inter * 2 + \
         linear_bytes(M, hidden, inter) - M * inter * 2
-    value = full * steps / (ms * 1e-3) / 1e9
     peaks = measured_peaks()
-    also = {}
+    also, nccl = {}, None
     if world > 1:
         nccl = [ShardedMLP(*w, group=group, reduce="nccl") for w in weights]
-        nsteps = min(steps, 400)
-        ms_n = timed_plain_steps(torch, lambda i: nccl[i % ncopies](x), nsteps, 5, dist)
-        also["same_step_with_nccl_allreduce"] = {"us": round(ms_n * 1e3 / nsteps, 2), "launch": "plain launches"}
-        fused = [ShardedMLP(*w, group=group, reduce="fused") for w in weights]
-        ms_t = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in fused], steps, 4, dist)
-        also["sum_fused_into_the_down_linear"] = {"us": round(ms_t * 1e3 / steps, 2), "launch": "CUDA graph replay"}
+        nsteps = min(steps, 400) if ms is not None else steps
+        with ClockSampler(sampler_index) as cs_n:
+            ms_n = timed_plain_steps(torch, lambda i: nccl[i % ncopies](x), nsteps, max(5, args.warmup), dist)
+        if ms is not None:
+            also["same_step_with_nccl_allreduce"] = {"us": round(ms_n * 1e3 / nsteps, 2), "launch": "plain launches"}
+            fused = [ShardedMLP(*w, group=group, reduce="fused") for w in weights]
+            try:
+                ms_t = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in fused], steps, 4, dist, health)
+                also["sum_fused_into_the_down_linear"] = {"us": round(ms_t * 1e3 / steps, 2), "launch": "CUDA graph replay"}
+            except ExchangeUnhealthy as e:
+                also["sum_fused_into_the_down_linear"] = {"us": None, "note": f"a bounded wait gave up {e}"}
+        else:
+            ms, cs, mlps = ms_n, cs_n, nccl
+            exchange, launch = ("NCCL all-reduce of f16 [1,8192] (a bounded wait of the peer-memory exchange gave up "
+                                "during the warm-up on this box)"), "plain launches of the C-ABI calls"
+    value = full * steps / (ms * 1e-3) / 1e9
     xh = torch.randn(M, hidden).to(torch.float16).pin_memory()
     yh = torch.empty(M, hidden, dtype=torch.float16).pin_memory()
 
@@ -559,16 +609,16 @@ def run_mlp70b(args, torch, sampler_index, rank, world, dist):
         "metric": "int4_g128_decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "steps": steps,
         "ms_per_step": ms / steps, "dtype": "f16", "scaling": "strong",
         "config": {"workload": "mlp70b_decode: X f16 [1,8192], gate/up u4-g128 [28672,8192] column-sharded, down [8192,28672] "
-                               "row-sharded, one-shot all-reduce of f16 [1,8192] over peer memory",
+                               "row-sharded, " + exchange,
                    "algorithmic_bytes_per_step": full, "parallelism": f"tp{world}",
                    "l2": f"{ncopies} weight copies per rank in rotation ({ncopies * per_rank / 1e6:.0f} MB per rank) larger than L2",
-                   "launch": "CUDA graph replay of the C-ABI calls"},
+                   "launch": launch},
         "roofline": {"bound": "hbm", "achieved": round(value / world, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(value / world / peaks["hbm_gbs"], 4), "traffic": None,
                      "peak_source": f"of {peaks['source']}, per GPU", "kernel": "dq_gemv_kernel (gate/up fused SiLU*mul, down)"},
         "e2e": {"value": round(full * e2e_steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": M * hidden * 2, "d2h_bytes_per_step": M * hidden * 2},
-        "gpu_launches": (3 if world > 1 else 2) * steps,
+        "gpu_launches": (3 if (world > 1 and mlps is not nccl) else 2) * steps,  # NCCL's kernel is not counted
         "clocks": cs.summary(),
         **({"also": also} if also else {}),
     }
