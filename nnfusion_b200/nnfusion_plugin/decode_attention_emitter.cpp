@@ -64,7 +64,10 @@ namespace nnfusion
                 {
                     LanguageUnit_p _lu(new LanguageUnit(get_function_name() + "_dep"));
                     _lu->require(header::cuda);
+                    _lu->require(header::stdexcept);
+                    _lu->require(header::sstream);
                     _lu->require(header::nnf_b200); // codegen_units.cpp
+                    _lu->require(declaration::nnf_b200_ctx);
                     _lu->require(macro::NNF_B200_SAFE_CALL);
                     return _lu;
                 }
