@@ -646,6 +646,10 @@ def main():
         # The reference's CPU path, rank 0 only; other ranks leave without work.
         if rank != 0:
             return 0
+        # torch.distributed.run sets OMP_NUM_THREADS=1 for its workers when the variable is unset; this arm is the
+        # only rank doing work and is meant to use every host core, so undo that default before OpenMP is loaded
+        if "TORCHELASTIC_RUN_ID" in os.environ and os.environ.get("OMP_NUM_THREADS") == "1":
+            os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
         steps = args.steps if args.steps is not None else 20
         warmup = args.warmup if args.warmup is not None else 3
         if workload == "prefill_gemm":
@@ -663,7 +667,8 @@ def main():
                   f"Dot = reference MLAS SGEMM" if kind == "reference" else f"{rows} of {full_rows} rows, C restatement")
         print(json.dumps({
             "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": n,
-            "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "strong" if workload == "mlp70b_decode" else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": workload + " (CPU reference path)"},
             "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
