@@ -642,14 +642,17 @@ def main():
     if workload == "auto":
         workload = "decode_gemv" if max(world, args.gpus) == 1 else "mlp70b_decode"
 
+    # torch.distributed.run sets OMP_NUM_THREADS=1 for its workers when the variable is unset.  The CPU baseline (the
+    # reference arm's one working rank; rank 0 of a one-GPU run) is meant to use every host core, so that default is
+    # undone before anything loads OpenMP.
+    if (rank == 0 and (args.impl == "reference" or world == 1) and "TORCHELASTIC_RUN_ID" in os.environ
+            and os.environ.get("OMP_NUM_THREADS") == "1"):
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+
     if args.impl == "reference":
         # The reference's CPU path, rank 0 only; other ranks leave without work.
         if rank != 0:
             return 0
-        # torch.distributed.run sets OMP_NUM_THREADS=1 for its workers when the variable is unset; this arm is the
-        # only rank doing work and is meant to use every host core, so undo that default before OpenMP is loaded
-        if "TORCHELASTIC_RUN_ID" in os.environ and os.environ.get("OMP_NUM_THREADS") == "1":
-            os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
         steps = args.steps if args.steps is not None else 20
         warmup = args.warmup if args.warmup is not None else 3
         if workload == "prefill_gemm":
