@@ -150,7 +150,7 @@ def timed_graph_steps(torch, step_fns, steps, warmup, dist=None, health=None):
         if dist is not None:
             torch.cuda.synchronize()
             dist.barrier()  # set-up takes a different time on every rank; the steps' exchanges have bounded waits
-        for i in range(max(warmup, 3) // 2 * 2 if health is not None else max(warmup, 3)):
+        for i in range((max(warmup, 3) + 1) // 2 * 2 if health is not None else max(warmup, 3)):
             step_fns[i % n]()
         torch.cuda.synchronize()
         if health is not None:
