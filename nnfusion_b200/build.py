@@ -10,7 +10,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libnnf_b200.so")
-SOURCES = ["nnf_api.cu", "dq_gemv.cu", "dq_gemm_tcgen05.cu", "decode_attn.cu", "oneshot_allreduce.cu"]
+SOURCES = ["nnf_api.cu", "dq_gemv.cu", "dq_gemv_direct.cu", "dq_gemm_tcgen05.cu", "decode_attn.cu", "oneshot_allreduce.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"

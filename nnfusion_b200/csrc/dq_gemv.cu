@@ -187,37 +187,6 @@ __device__ __forceinline__ void named_barrier(int id, int threads)
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// Compile with -DNNF_TRACE to record, per CTA, the time at which thread 0 and thread 256 pass the marked points.
-#ifndef NNF_TRACE_BASE
-#define NNF_TRACE_BASE 0 // first of the five row tiles whose times are recorded
-#endif
-#ifdef NNF_TRACE
-__device__ unsigned long long g_nnf_trace[3 * 2048 * 16];
-#define NNF_CTA_ID (blockIdx.y * gridDim.x + blockIdx.x)
-#define NNF_TRACE_WRITE(row, i)                                                                                    \
-    do                                                                                                             \
-    {                                                                                                              \
-        unsigned long long t_;                                                                                     \
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                     \
-        g_nnf_trace[((row) + NNF_CTA_ID) * 16 + (i)] = t_;                                                         \
-    } while (0)
-#define NNF_TRACE_POINT(i)                                                                                         \
-    do                                                                                                             \
-    {                                                                                                              \
-        if ((threadIdx.x == 0 || threadIdx.x == 256) && NNF_CTA_ID < 2048)                                         \
-            NNF_TRACE_WRITE(threadIdx.x ? 2048 : 0, i);                                                            \
-    } while (0)
-#define NNF_TRACE_PRODUCER(i)                                                                                      \
-    do                                                                                                             \
-    {                                                                                                              \
-        if ((threadIdx.x & 31) == 0 && NNF_CTA_ID < 2048)                                                          \
-            NNF_TRACE_WRITE(4096, i);                                                                              \
-    } while (0)
-#else
-#define NNF_TRACE_POINT(i)
-#define NNF_TRACE_PRODUCER(i)
-#endif
-
 template <int WBITS>
 struct Fmt
 {
@@ -277,7 +246,6 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
     const int tq_shift = tq >> 1;                        // tq is 1, 2 or 4
     const int pt_shift = 5 + tq_shift + (MB == 2 ? 1 : 0);
     const int per_tile = 1 << pt_shift; // MB * 8 * tq * 4 floats: one warp's partial sums of one tile and weight set
-    NNF_TRACE_POINT(0);
 
     // ring: [depth][SETS][16 rows] of (nwarps * 128 + 64) bytes, warp w's 128 bytes of a row at w * 128; then per
     // slot and set the tile's scales and zero-points
@@ -371,7 +339,6 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
         // A warp of its own: asking for data never waits for anybody's activation loads, and the arithmetic warps
         // never wait for the requests to be issued.  The first ring-full leaves at once; slots are then refilled
         // as the arithmetic warps hand them back.
-        NNF_TRACE_PRODUCER(0);
         if (lane < p.depth)
         {
             // lane i owns ring slot i: barrier operations take tens of nanoseconds each, so they run side by side
@@ -381,15 +348,12 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             if (lane < nsteps && use_full)
                 expect(lane);
         }
-        NNF_TRACE_PRODUCER(1);
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"r"(nthreads + 32) : "memory"); // barriers are ready
-        NNF_TRACE_PRODUCER(2);
         if (!use_full)
             return; // nothing travels through the slots' barriers
         for (int i = 0; i < p.depth && i < nsteps; i++)
             copy(i);
-        NNF_TRACE_PRODUCER(3);
         bool gave_up = false;
         for (int st = p.depth; st < nsteps; st++)
         {
@@ -659,9 +623,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                 ss_w[warp * MPAD + g + 8 * mb] = v;
         }
     }
-    NNF_TRACE_POINT(2);
     asm volatile("bar.sync 2, %0;" ::"r"(nthreads + 32) : "memory"); // ring barriers initialised, ss_w visible
-    NNF_TRACE_POINT(3);
     if (p.rmsnorm)
     {
         if (tid < MPAD)
@@ -1100,8 +1062,6 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                 timed_out = true;
             if (lsu)
                 cp_async_wait(p.depth - 1); // this thread's pieces of tile st have landed
-            if (st < 5)
-                NNF_TRACE_POINT(4 + 2 * st);
             float4* my = reinterpret_cast<float4*>(red + warp * warp_stride + j * SETS * per_tile);
             if (has_slice)
                 compute(st, slot);
@@ -1124,8 +1084,6 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
                         my[(s * MB + mb) * 8 * tq + g * tq + t] =
                             make_float4(tot[s][mb][0], tot[s][mb][1], tot[s][mb][2], tot[s][mb][3]);
             }
-            if (st < 5)
-                NNF_TRACE_POINT(5 + 2 * st);
             if (lsu)
             {
                 // what this thread read from the slot is in its registers: ask for the tile that lands there next
@@ -1139,9 +1097,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             if (++slot == p.depth)
                 slot = 0, parity ^= 1;
         }
-        NNF_TRACE_POINT(14);
         flush(first, count);
-        NNF_TRACE_POINT(15);
     }
     if (timed_out)
         atomicExch(p.status, 1);
@@ -1151,13 +1107,19 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
 template <int WBITS, int MB, bool XSPLIT, bool DUAL, bool EXACT, bool FAST>
 cudaError_t ensure_smem(size_t smem)
 {
-    static size_t configured = 48 * 1024;
-    if (smem <= configured)
+    static size_t configured[nnf::kMaxDevices] = {}; // the attribute belongs to the device that is current
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return e;
+    if (dev < 0 || dev >= nnf::kMaxDevices)
+        return cudaErrorInvalidDevice;
+    if (smem <= std::max(configured[dev], (size_t)48 * 1024))
         return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT, FAST>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    e = cudaFuncSetAttribute(dq_gemv_kernel<WBITS, MB, XSPLIT, DUAL, EXACT, FAST>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
-        configured = smem;
+        configured[dev] = smem;
     return e;
 }
 
@@ -1311,12 +1273,8 @@ void fill_params(GemvParams& p, const nnf_b200_linear_desc& d, const nnf::GemvPl
     p.bulk_params = plan.pset_bytes > 0 && ok16(w->scale) && ok16(w->zp) &&
                     (!plan.dual || (ok16(w2->scale) && ok16(w2->zp)));
     // How the weights travel: bulk copies from the producer warp, or cp.async from the arithmetic threads
-    // themselves.  NNF_B200_WEIGHT_PATH=bulk|lsu overrides the rule.
-    static const int forced = [] {
-        const char* v = getenv("NNF_B200_WEIGHT_PATH");
-        return !v ? 0 : (v[0] == 'b' ? 1 : (v[0] == 'l' ? 2 : 0));
-    }();
-    p.lsu_weights = forced ? forced == 2 : plan.lsu_weights;
+    // themselves.
+    p.lsu_weights = plan.lsu_weights;
     if (plan.splits > 1)
     {
         const size_t cnt = ((size_t)plan.row_tiles * sizeof(unsigned) + 255) / 256 * 256;
@@ -1333,7 +1291,8 @@ int gemv_configure(nnf_b200_ctx*)
     return NNF_B200_OK;
 }
 
-int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan, std::string* why)
+int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan, std::string* why,
+              bool allow_direct)
 {
     const int ue = (d.w_bits == 4) ? 128 : 64;
     const int group = d.group_size > 0 ? d.group_size : d.K;
@@ -1364,6 +1323,16 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
     pl.pset_bytes = (d.N % 16 == 0) ? pl.scale_tile_bytes + pl.zp_tile_bytes : 0;
     // activation fragments of batch rows 8..15: 2 units x (1 or 2 halves of fp32 x) x NF/2 pairs x 32 lanes x 8 bytes
     pl.xfrag_bytes = (pl.mb == 2 && !pl.dual) ? 2 * (pl.xsplit ? 2 : 1) * ((d.w_bits == 4 ? 16 : 8) / 2) * 256 : 0;
+    if (d.split_k > 0 && (pl.slices + d.split_k - 1) / d.split_k > kMaxWarps)
+    {
+        *why = "split_k too small: more than " + std::to_string(kMaxWarps) + " slices of 128 bytes per split";
+        return NNF_B200_EINVAL;
+    }
+    if (allow_direct && gemv_direct_plan(ctx, d, &pl))
+    {
+        *plan = pl;
+        return NNF_B200_OK;
+    }
     const int sms = ctx ? ctx->sm_count : 148;
     const int smem_cap = ctx ? ctx->smem_optin : 227 * 1024;
     const int sets = pl.dual ? 2 : 1;
@@ -1374,14 +1343,7 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
     {
         pl.splits = (pl.slices + max_warps - 1) / max_warps;
         if (d.split_k > 0)
-        {
-            if ((pl.slices + d.split_k - 1) / d.split_k > kMaxWarps)
-            {
-                *why = "split_k too small: more than " + std::to_string(kMaxWarps) + " slices of 128 bytes per split";
-                return NNF_B200_EINVAL;
-            }
             pl.splits = std::min(d.split_k, pl.slices);
-        }
         pl.warps = (pl.slices + pl.splits - 1) / pl.splits;
         // CTAs per SM by registers (the kernel is compiled for at most 120 per thread: 544 threads per SM, one
         // warp of each CTA being its producer), then the ring that lets that many CTAs share the shared memory.
@@ -1421,15 +1383,26 @@ int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* 
     return NNF_B200_OK;
 }
 
-int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan_in,
+// Launches whichever small-M kernel the plan names.
+static cudaError_t gemv_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& plan, const void* x,
+                                 const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
+                                 const void* bias, void* y, int* status, void* workspace,
+                                 const nnf_b200_peers* peers, cudaStream_t stream)
+{
+    if (plan.direct)
+        return peers ? cudaErrorInvalidValue
+                     : gemv_direct_dispatch(d, plan, x, w, w2, gain, bias, y, status, workspace, stream);
+    GemvParams p{};
+    fill_params(p, d, plan, x, w, w2, gain, bias, y, status, workspace, peers);
+    return dispatch(d.w_bits, plan, p, plan.splits * plan.ctas_per_split, stream);
+}
+
+int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan,
                 const void* x, const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
                 const void* bias, void* y, void* workspace, const nnf_b200_peers* peers)
 {
-    const GemvPlan& plan = plan_in;
-    GemvParams p{};
-    fill_params(p, d, plan, x, w, w2, gain, bias, y, ctx->dev_status, workspace, peers);
     const int grid = plan.splits * plan.ctas_per_split;
-    cudaError_t e = dispatch(d.w_bits, plan, p, grid, stream);
+    cudaError_t e = gemv_dispatch(d, plan, x, w, w2, gain, bias, y, ctx->dev_status, workspace, peers, stream);
     if (e != cudaSuccess)
         return set_error(ctx, NNF_B200_ECUDA,
                          std::string("dq_gemv launch: ") + cudaGetErrorString(e) + " (grid " + std::to_string(grid) +
@@ -1474,13 +1447,6 @@ void put_message(char* buf, size_t len, const char* msg)
         snprintf(buf, len, "%s", msg);
 }
 } // namespace
-
-#ifdef NNF_TRACE
-extern "C" __attribute__((visibility("default"))) int nnf_debug_trace_read(unsigned long long* out, int n)
-{
-    return (int)cudaMemcpyFromSymbol(out, g_nnf_trace, (size_t)n * sizeof(unsigned long long));
-}
-#endif
 
 extern "C" __attribute__((visibility("default"))) int
 nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, const void* x,
@@ -1564,8 +1530,6 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
         return NNF_B200_EWORKSPACE;
     }
 
-    GemvParams p{};
-    fill_params(p, d, plan, x, w, w2, gain, bias, y, st.status, st.scratch);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (plan.splits > 1)
     {
@@ -1577,7 +1541,7 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
             return NNF_B200_ECUDA;
         }
     }
-    cudaError_t e = dispatch(d.w_bits, plan, p, plan.splits * plan.ctas_per_split, s);
+    cudaError_t e = gemv_dispatch(d, plan, x, w, w2, gain, bias, y, st.status, st.scratch, nullptr, s);
     if (e != cudaSuccess)
     {
         put_message(errbuf, errbuf_len, cudaGetErrorString(e));

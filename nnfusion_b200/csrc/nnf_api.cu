@@ -210,11 +210,15 @@ size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_l
         return 0;
     if (pick_kernel(*desc) == NNF_B200_KERNEL_GEMV)
     {
-        nnf::GemvPlan plan;
+        // The larger of what the two small-M kernels ask for: which of them runs is settled per call (the sum over
+        // ranks inside the launch is served by the ring kernel only).
+        nnf::GemvPlan plan, ring;
         std::string why;
         if (nnf::gemv_plan(ctx, *desc, &plan, &why) != NNF_B200_OK)
             return 0;
-        return plan.workspace_bytes;
+        if (nnf::gemv_plan(ctx, *desc, &ring, &why, false) != NNF_B200_OK)
+            return plan.workspace_bytes;
+        return plan.workspace_bytes > ring.workspace_bytes ? plan.workspace_bytes : ring.workspace_bytes;
     }
     return nnf::gemm_workspace_bytes(ctx, *desc);
 }
@@ -397,7 +401,7 @@ static int linear_impl(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_de
     {
         nnf::GemvPlan plan;
         std::string why;
-        rc = nnf::gemv_plan(ctx, d, &plan, &why);
+        rc = nnf::gemv_plan(ctx, d, &plan, &why, peers == nullptr);
         if (rc != NNF_B200_OK)
             return nnf::set_error(ctx, rc, why);
         if (plan.workspace_bytes > 0 && (!workspace || workspace_bytes < plan.workspace_bytes))

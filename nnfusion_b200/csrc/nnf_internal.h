@@ -26,6 +26,8 @@ struct nnf_b200_ctx
 
 namespace nnf
 {
+constexpr int kMaxDevices = 64; // per-device bookkeeping (shared-memory opt-ins) is kept in arrays of this size
+
 // Launch plan of the small-M kernel, shared by workspace sizing and launch.
 struct GemvPlan
 {
@@ -49,6 +51,8 @@ struct GemvPlan
     int pset_bytes = 0;         // shared memory per ring slot and weight set for both (0: plain loads)
     int lsu_weights = 0;        // weights by per-thread cp.async instead of bulk copies
     int xfrag_bytes = 0;        // shared memory per warp for the activation fragments of batch rows 8..15
+    int direct = 0;             // served by the register-pipeline kernel (dq_gemv_direct.cu) instead of the ring kernel
+    int prefetch_tiles = 0;     // register-pipeline kernel: L2 prefetch window in row tiles
 };
 
 int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
@@ -63,7 +67,13 @@ void overlap_attribute(cudaLaunchAttribute* attr, unsigned* count);
 const CUtensorMap* weight_tensor_map(nnf_b200_ctx* ctx, const void* base, int rows, int row_bytes, int box_bytes,
                                      int box_rows);
 
-int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan, std::string* why);
+// allow_direct = false keeps the plan on the ring kernel (the only one that sums over ranks inside the launch).
+int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan, std::string* why,
+              bool allow_direct = true);
+bool gemv_direct_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan);
+cudaError_t gemv_direct_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& plan, const void* x,
+                                 const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
+                                 const void* bias, void* y, int* status, void* workspace, cudaStream_t stream);
 int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan,
                 const void* x, const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
                 const void* bias, void* y, void* workspace, const nnf_b200_peers* peers = nullptr);
