@@ -12,7 +12,7 @@
  * generated runtime they receive tensors that live in the runtime's own memory
  * pool.  Kernels are launched as programmatic dependents of whatever precedes
  * them on the stream (they wait for it before touching anything it may have
- * written); NNF_B200_NO_OVERLAP=1 in the environment switches that off.
+ * written).
  *
  * Each declaration names the reference interface it stands in for (paths are
  * relative to the reference project root).
@@ -208,8 +208,10 @@ NNF_B200_API int nnf_b200_linear(nnf_b200_ctx* ctx, void* stream, const nnf_b200
  * calls no allocator.  Shapes whose split-K scratch exceeds the array are refused with
  * NNF_B200_EWORKSPACE (the text in errbuf names both sizes).
  * The first call made while a given device is current fetches the array's device
- * address, raises the kernel's shared-memory limit and looks up the tensor-map encoder:
- * make that call outside of any stream capture.  Every call uses the same array and
+ * address and reads the device's attributes, and the first call of each kernel variant
+ * on a device raises that kernel's shared-memory limit: make those calls outside of
+ * any stream capture.  Host threads may call concurrently (the set-up is guarded); the
+ * calls themselves still share the one array.  Every call uses the same array and
  * finds in it what the previous call left; the counters that must start at zero are
  * cleared on `stream` by each call.  Two calls that overlap on the GPU (for instance
  * on two streams of one process) race on the array: serialise them.  Each process
@@ -219,6 +221,13 @@ NNF_B200_API int nnf_b200_linear_static_scratch(void* stream, const nnf_b200_lin
                                                 const nnf_b200_qweight* w, const nnf_b200_qweight* w2,
                                                 const void* gain, const void* bias, void* y, char* errbuf,
                                                 size_t errbuf_len);
+
+/* Companion of nnf_b200_linear_static_scratch (like it, without a counterpart in the
+ * reference): reads and clears the status word that kernels launched through that entry
+ * point raise when a bounded device-side wait gives up, for the device that is current.
+ * Returns NNF_B200_OK, NNF_B200_ETIMEDOUT, or NNF_B200_ECUDA.  Synchronises `stream`,
+ * allocates nothing; meant for tests and for a check outside the hot loop. */
+NNF_B200_API int nnf_b200_static_scratch_status(void* stream);
 
 /* ---- single-token (decode) attention over a key/value cache ---------------------------------------------
  *
@@ -272,7 +281,9 @@ NNF_B200_API int nnf_b200_decode_attention(nnf_b200_ctx* ctx, void* stream, cons
  * call, the same on every rank -- or 0 to let the kernel count calls itself in words kept after the flags (then a
  * captured sequence with an even number of calls can be replayed).  Other rules for the caller: the flag words
  * (nnf_b200_allreduce_flag_bytes of them) start zeroed and are never written by anyone else; the addend of this
- * call must be complete in its half, in stream order, before the call.  count: fp16 elements, a multiple of 8;
+ * call must be complete in its half, in stream order, before the call.  A flag area sized for `count` elements
+ * serves every call of up to that many elements (its layout does not depend on the size of a call), as long as
+ * all ranks make the same sequence of calls on it.  count: fp16 elements, a multiple of 8;
  * bufs 16-byte aligned.
  * A rank whose peers never call gives up after about 0.4 s, writes nothing, and nnf_b200_device_status then
  * reports NNF_B200_ETIMEDOUT. */

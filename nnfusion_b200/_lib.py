@@ -24,7 +24,7 @@ EXPORTS = (
     "nnf_b200_init", "nnf_b200_free", "nnf_b200_strerror", "nnf_b200_last_error", "nnf_b200_sm_count",
     "nnf_b200_linear_workspace_bytes", "nnf_b200_workspace_reset", "nnf_b200_linear",
     "nnf_b200_launch_count", "nnf_b200_pack_u4", "nnf_b200_device_status", "nnf_b200_linear_plan",
-    "nnf_b200_linear_static_scratch", "nnf_b200_decode_attention_workspace_bytes", "nnf_b200_decode_attention",
+    "nnf_b200_linear_static_scratch", "nnf_b200_static_scratch_status", "nnf_b200_decode_attention_workspace_bytes", "nnf_b200_decode_attention",
     "nnf_b200_allreduce_flag_bytes", "nnf_b200_allreduce_oneshot",
     "nnf_b200_linear_allreduce_flag_bytes", "nnf_b200_linear_allreduce",
 )
@@ -89,6 +89,7 @@ def load() -> ctypes.CDLL:
     L.nnf_b200_device_status.argtypes = [vp, vp]
     L.nnf_b200_linear_static_scratch.argtypes = [vp, ctypes.POINTER(LinearDesc), vp, ctypes.POINTER(QWeight),
                                                  ctypes.POINTER(QWeight), vp, vp, vp, ctypes.c_char_p, sz]
+    L.nnf_b200_static_scratch_status.argtypes = [vp]
     L.nnf_b200_linear_plan.argtypes = [vp, ctypes.POINTER(LinearDesc), ctypes.POINTER(ctypes.c_int32 * 8)]
     L.nnf_b200_launch_count.argtypes = [vp, ctypes.c_int]
     L.nnf_b200_launch_count.restype = ctypes.c_uint64

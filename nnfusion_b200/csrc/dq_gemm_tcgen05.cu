@@ -475,14 +475,20 @@ cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap
                    int grid, cudaStream_t stream)
 {
     using C = Cfg<WBITS, DUAL>;
-    static bool configured = false;
-    if (!configured)
+    static bool configured[nnf::kMaxDevices] = {}; // the attribute belongs to the device that is current
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return e;
+    if (dev < 0 || dev >= nnf::kMaxDevices)
+        return cudaErrorInvalidDevice;
+    if (!configured[dev])
     {
-        cudaError_t e = cudaFuncSetAttribute(dq_gemm_kernel<WBITS, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)C::SMEM_BYTES);
+        e = cudaFuncSetAttribute(dq_gemm_kernel<WBITS, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)C::SMEM_BYTES);
         if (e != cudaSuccess)
             return e;
-        configured = true;
+        configured[dev] = true;
     }
     (void)cudaGetLastError();
     dq_gemm_kernel<WBITS, DUAL><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, tx, tw0, tw1);
@@ -563,17 +569,23 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     if (!encode_tensor_map_2d(ctx->encode_tiled, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)d.K,
                               (uint64_t)d.M, (uint64_t)d.K * 2, 64, (uint32_t)bx, CU_TENSOR_MAP_SWIZZLE_128B))
         return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the activations");
+    // copied by value at once: a later lookup may empty the context's cache
+    alignas(64) CUtensorMap tw0v, tw1v;
     const CUtensorMap* tw0 = weight_tensor_map(ctx, w->wq, d.N, row_bytes, 128, 128);
+    if (tw0)
+        tw0v = *tw0;
     const CUtensorMap* tw1 = dual ? weight_tensor_map(ctx, w2->wq, d.N, row_bytes, 128, 128) : tw0;
+    if (tw1)
+        tw1v = *tw1;
     if (!tw0 || !tw1)
         return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
 
     const int grid = p.m_tiles * n_tiles;
     cudaError_t e;
     if (d.w_bits == 4)
-        e = dual ? launch<4, true>(p, tx, *tw0, *tw1, grid, stream) : launch<4, false>(p, tx, *tw0, *tw1, grid, stream);
+        e = dual ? launch<4, true>(p, tx, tw0v, tw1v, grid, stream) : launch<4, false>(p, tx, tw0v, tw1v, grid, stream);
     else
-        e = dual ? launch<8, true>(p, tx, *tw0, *tw1, grid, stream) : launch<8, false>(p, tx, *tw0, *tw1, grid, stream);
+        e = dual ? launch<8, true>(p, tx, tw0v, tw1v, grid, stream) : launch<8, false>(p, tx, tw0v, tw1v, grid, stream);
     if (e != cudaSuccess)
         return set_error(ctx, NNF_B200_ECUDA, std::string("dq_gemm launch: ") + cudaGetErrorString(e));
     ctx->launches++;

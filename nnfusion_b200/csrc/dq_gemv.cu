@@ -31,6 +31,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 
 #include "nnf_internal.h"
 #include "sm100_ptx.cuh"
@@ -1439,7 +1440,8 @@ struct StaticDeviceState
     int sm_count = 0;
     int smem_optin = 0;
 };
-StaticDeviceState g_static_state[64];
+StaticDeviceState g_static_state[nnf::kMaxDevices];
+std::mutex g_static_mutex; // guards the once-per-device set-up
 
 void put_message(char* buf, size_t len, const char* msg)
 {
@@ -1455,57 +1457,54 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
 {
     using namespace nnf;
     put_message(errbuf, errbuf_len, "");
-    if (!desc || !x || !y || !w || !w->wq || !w->scale || !w->zp)
+    std::string why;
+    int rc = check_linear_call(desc, x, w, w2, gain, bias, y, nullptr, &why);
+    if (rc == NNF_B200_OK && (desc->kernel == NNF_B200_KERNEL_GEMM || desc->M > 16))
     {
-        put_message(errbuf, errbuf_len, "null descriptor, activations, output or weight set");
-        return NNF_B200_EINVAL;
+        rc = NNF_B200_ENOTSUP;
+        why = "this entry point serves the small-M kernel only (M <= 16)";
+    }
+    if (rc != NNF_B200_OK)
+    {
+        put_message(errbuf, errbuf_len, why.c_str());
+        return rc;
     }
     const nnf_b200_linear_desc& d = *desc;
-    const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
-    if (d.M < 1 || d.N < 1 || d.K < 1 || (d.w_bits != 4 && d.w_bits != 8) || d.group_size < 0 ||
-        (dual && (!w2 || !w2->wq || !w2->scale || !w2->zp)) || (!dual && w2) ||
-        ((d.prologue == NNF_B200_PROLOGUE_RMSNORM) != (gain != nullptr)) ||
-        ((d.epilogue == NNF_B200_EPILOGUE_BIAS || d.epilogue == NNF_B200_EPILOGUE_ADD) != (bias != nullptr)))
-    {
-        put_message(errbuf, errbuf_len, "malformed descriptor or operands that do not match it");
-        return NNF_B200_EINVAL;
-    }
-    if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(w->wq) & 15u) ||
-        (dual && (reinterpret_cast<uintptr_t>(w2->wq) & 15u)) || (gain && (reinterpret_cast<uintptr_t>(gain) & 15u)))
-    {
-        put_message(errbuf, errbuf_len, "x, wq and gain must be 16-byte aligned");
-        return NNF_B200_EALIGN;
-    }
 
-    // ---- once per device, with that device current
+    // ---- once per device, with that device current (host threads take turns)
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
     {
         put_message(errbuf, errbuf_len, "no current CUDA device");
         return NNF_B200_ECUDA;
     }
-    StaticDeviceState& st = g_static_state[dev];
-    if (!st.ready)
+    StaticDeviceState st;
     {
-        void* sp = nullptr;
-        void* tp = nullptr;
-        if (cudaGetSymbolAddress(&sp, g_static_scratch) != cudaSuccess || !sp ||
-            cudaGetSymbolAddress(&tp, g_static_status) != cudaSuccess || !tp)
+        std::lock_guard<std::mutex> guard(g_static_mutex);
+        StaticDeviceState& slot = g_static_state[dev];
+        if (!slot.ready)
         {
-            put_message(errbuf, errbuf_len, "cudaGetSymbolAddress failed for the built-in scratch array");
-            return NNF_B200_ECUDA;
+            void* sp = nullptr;
+            void* tp = nullptr;
+            if (cudaGetSymbolAddress(&sp, g_static_scratch) != cudaSuccess || !sp ||
+                cudaGetSymbolAddress(&tp, g_static_status) != cudaSuccess || !tp)
+            {
+                put_message(errbuf, errbuf_len, "cudaGetSymbolAddress failed for the built-in scratch array");
+                return NNF_B200_ECUDA;
+            }
+            int major = 0;
+            if (cudaDeviceGetAttribute(&slot.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+                cudaDeviceGetAttribute(&slot.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess ||
+                cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
+            {
+                put_message(errbuf, errbuf_len, "device attributes unavailable, or not an sm_100 device");
+                return NNF_B200_ENOTSUP;
+            }
+            slot.scratch = sp;
+            slot.status = static_cast<int*>(tp);
+            slot.ready = true;
         }
-        int major = 0;
-        if (cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&st.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
-        {
-            put_message(errbuf, errbuf_len, "device attributes unavailable, or not an sm_100 device");
-            return NNF_B200_ENOTSUP;
-        }
-        st.scratch = sp;
-        st.status = static_cast<int*>(tp);
-        st.ready = true;
+        st = slot;
     }
 
     // ---- launch shape; the only kernel served here is the small-M one, which is the one that needs scratch
@@ -1514,8 +1513,7 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
     shape_ctx.sm_count = st.sm_count;
     shape_ctx.smem_optin = st.smem_optin;
     GemvPlan plan;
-    std::string why;
-    int rc = gemv_plan(&shape_ctx, d, &plan, &why);
+    rc = gemv_plan(&shape_ctx, d, &plan, &why);
     if (rc != NNF_B200_OK)
     {
         put_message(errbuf, errbuf_len, why.c_str());
@@ -1548,4 +1546,24 @@ nnf_b200_linear_static_scratch(void* stream, const nnf_b200_linear_desc* desc, c
         return NNF_B200_ECUDA;
     }
     return NNF_B200_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int nnf_b200_static_scratch_status(void* stream)
+{
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= nnf::kMaxDevices)
+        return NNF_B200_ECUDA;
+    int* word = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(g_static_mutex);
+        if (!g_static_state[dev].ready)
+            return NNF_B200_OK; // nothing has run on this device through the allocation-free entry point yet
+        word = g_static_state[dev].status;
+    }
+    int host = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaMemsetAsync(word, 0, sizeof(int), s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess)
+        return NNF_B200_ECUDA;
+    return host != 0 ? NNF_B200_ETIMEDOUT : NNF_B200_OK;
 }

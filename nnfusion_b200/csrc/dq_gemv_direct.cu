@@ -18,8 +18,8 @@
 //   * what the register pipeline cannot hold in flight is asked for with bulk prefetches into L2
 //     (cp.async.bulk.prefetch.L2), a bounded window of tiles ahead of the loads, so that HBM streams from the first
 //     microsecond while the loads themselves only see L2 latency;
-//   * the scales and zero-points of a batch of tiles arrive in shared memory by bulk copy (two per weight set and
-//     batch), double-buffered across batches; every wait on their mbarrier is bounded;
+//   * the scales and zero-points of a batch of tiles arrive in shared memory by cp.async, every thread copying its
+//     share of 16-byte pieces, double-buffered across batches; the kernel contains no wait on another agent at all;
 //   * nibbles/bytes become exact fp16 integers with one LOP3/PRMT per pair (the 0x6400 / 0x5400 exponent trick) and
 //     feed mma.sync.m16n8k16 with W as the 16-row operand and up to 8 batch rows as the 8-column operand;
 //     accumulation is fp32; the offset and the zero-point leave the fp32 sum of each 64-byte unit afterwards,
@@ -140,12 +140,19 @@ __device__ __forceinline__ void l2_prefetch(const uint8_t* p, uint32_t bytes)
 {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
-// Untiled bulk copy global -> shared: both addresses 16-byte aligned, size a multiple of 16 bytes.
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+// 16 bytes global -> shared without passing through registers; both addresses 16-byte aligned.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src)
 {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
-                 : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+// Wait until at most one of this thread's copy groups (the most recent) is still in flight.
+__device__ __forceinline__ void cp_async_wait_but_one()
+{
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
 }
 __device__ __forceinline__ unsigned short lds_u16(uint32_t addr)
 {
@@ -181,7 +188,7 @@ struct DirectSmem
     __host__ __device__ DirectSmem(int sets, int mb, int warps, int batch, int tq, int pset_bytes, int xfrag_bytes)
     {
         params = (size_t)2 * batch * sets * pset_bytes; // two batches of (scales, zero-points) per weight set
-        bars = 16;
+        bars = 0;
         red = sizeof(float) * (size_t)warps * batch * sets * mb * 8 * tq * 4;
         ss = sizeof(float) * ((size_t)warps * 8 * mb + 8 * mb);
         flags = sizeof(int) * kBatch;
@@ -296,43 +303,45 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     // (pointers stay derived from the array itself, never from an integer, so that every access below is compiled
     // as a shared-memory access with a 32-bit address rather than as a generic one)
     uint8_t* pbuf = smem_raw; // [2 batches][SETS][scales of the batch's tiles | zero-points of the batch's tiles]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + p.off_bars);
     float* red = reinterpret_cast<float*>(smem_raw + p.off_red);        // [nwarps][batch][SETS][per_tile]
     float* ss_w = reinterpret_cast<float*>(smem_raw + p.off_ss);        // [nwarps][MPAD]
     float* ss_cta = ss_w + nwarps * MPAD;                               // [MPAD]
     int* last_flag = reinterpret_cast<int*>(smem_raw + p.off_flags);    // [kBatch]
     // [warp][unit][xs][fragment pair][lane] x 8 bytes: B fragments of batch rows 8..15
     const uint32_t xsm_s = smem_u32(last_flag + kBatch) + (uint32_t)(warp * p.xfrag_bytes) + (uint32_t)lane * 8u;
-    const uint32_t pbuf_s = smem_u32(pbuf), bar_s = smem_u32(bars);
+    const uint32_t pbuf_s = smem_u32(pbuf);
     const uint32_t pbatch_bytes = (uint32_t)(p.batch * SETS * pset_bytes); // one batch's parameters
     const uint32_t pzp_off = (uint32_t)(p.batch * p.scale_tile_bytes);     // zero-points follow the batch's scales
 
-    // Parameters of the tiles [first, first + count) of this CTA's range into buffer `which` (one thread).
+    // Parameters of the local tiles [first, first + count) into buffer `which`: every thread copies its share of
+    // 16-byte pieces with cp.async and closes one copy group (an empty one when there is nothing to copy, so that
+    // "all groups but the newest" always means "everything up to the batch before").  No barrier object, no
+    // copy-engine request: the batch's data is complete once every thread has waited for its own groups and the CTA
+    // has met at a barrier.
     auto copy_params = [&](int first, int count, int which) {
-        const uint32_t bar = bar_s + 8 * which;
-        mbar_arrive_expect_tx(bar, (uint32_t)(count * SETS * pset_bytes));
-#pragma unroll
-        for (int s = 0; s < SETS; s++)
+        if (p.bulk_params && count > 0)
         {
-            const uint32_t dst = pbuf_s + which * pbatch_bytes + s * (uint32_t)(p.batch * pset_bytes);
-            const size_t tile = (size_t)(tile0 + first);
-            bulk_load(dst, static_cast<const char*>(s == 0 ? p.scale[0] : p.scale[1]) + tile * p.scale_tile_bytes,
-                      (uint32_t)(count * p.scale_tile_bytes), bar);
-            bulk_load(dst + pzp_off, (s == 0 ? p.zp[0] : p.zp[1]) + tile * p.zp_tile_bytes,
-                      (uint32_t)(count * p.zp_tile_bytes), bar);
+            const int nsc = (count * p.scale_tile_bytes) >> 4, nzp = (count * p.zp_tile_bytes) >> 4;
+#pragma unroll
+            for (int s = 0; s < SETS; s++)
+            {
+                const uint32_t dst = pbuf_s + which * pbatch_bytes + s * (uint32_t)(p.batch * pset_bytes);
+                const size_t tile = (size_t)(tile0 + first);
+                const char* sc_src = static_cast<const char*>(s == 0 ? p.scale[0] : p.scale[1]) + tile * p.scale_tile_bytes;
+                const uint8_t* zp_src = (s == 0 ? p.zp[0] : p.zp[1]) + tile * p.zp_tile_bytes;
+                for (int i = tid; i < nsc + nzp; i += nthreads)
+                {
+                    if (i < nsc)
+                        cp_async16(dst + (uint32_t)i * 16u, sc_src + (size_t)i * 16);
+                    else
+                        cp_async16(dst + pzp_off + (uint32_t)(i - nsc) * 16u, zp_src + (size_t)(i - nsc) * 16);
+                }
+            }
         }
+        cp_async_commit();
     };
-    if (tid == 0 && p.bulk_params)
-    {
-        mbar_init(bar_s, 1);
-        mbar_init(bar_s + 8, 1);
-        fence_barrier_init();
-        if (ntiles > 0)
-            copy_params(0, min(p.batch, ntiles), 0);
-        if (ntiles > p.batch)
-            copy_params(p.batch, min(p.batch, ntiles - p.batch), 1);
-    }
-
+    copy_params(0, min(p.batch, ntiles), 0);
+    copy_params(p.batch, min(p.batch, max(ntiles - p.batch, 0)), 1);
 
     // Everything above reads only constants (weights, scales, zero-points).  The activations, the output and the workspace may belong
     // to the launch before this one on the stream: when this kernel was launched as its programmatic dependent, it
@@ -549,7 +558,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 ss_w[warp * MPAD + g + 8 * mb] = v;
         }
     }
-    __syncthreads(); // parameter barriers initialised, ss_w visible
+    cp_async_wait_but_one(); // this thread's pieces of the first batch's parameters have landed
+    __syncthreads();         // ... and everybody's; ss_w visible
     if (p.rmsnorm)
     {
         if (tid < MPAD)
@@ -749,8 +759,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     };
 
     // Add up the warps' partial sums of the local tiles [first, first + count) and write the results out.
+    // (the caller brackets it with the CTA's barriers)
     auto flush = [&](int first, int count) {
-        __syncthreads();
         if (p.splits == 1)
         {
             for (int idx = tid; idx < count * per_tile; idx += nthreads)
@@ -827,7 +837,6 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 }
             }
         }
-        __syncthreads();
     };
 
     // ---------------------------------------------------------------- main loop
@@ -838,26 +847,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     const uint32_t set_stride = (uint32_t)held(p.batch * pset_bytes);
     const bool keeps = t < tq; // does this lane hold batch rows that exist?
     int which = 0; // parameter buffer of the batch
-    uint32_t phase0 = 0u, phase1 = 0u;
     int jt = 0;      // local tile of the stage at hand
     // the tile that enters the L2 window when tile jt is done (never, without prefetching)
     const int pf_ahead = held(kDirectTiles + p.prefetch_tiles);
     const int pf_until = held(p.prefetch_tiles > 0 ? ntiles - pf_ahead : 0);
     int pf_turn = pf_ahead % p.splits; // (jt + pf_ahead) mod splits, kept by counting
-    bool timed_out = false;
     for (int first = 0; first < ntiles; first += p.batch)
     {
         const int count = min(p.batch, ntiles - first);
-        if (p.bulk_params)
-        {
-            // the batch's parameters must have landed
-            if (!mbar_wait(bar_s + 8 * which, which ? phase1 : phase0))
-                timed_out = true;
-            if (which)
-                phase1 ^= 1u;
-            else
-                phase0 ^= 1u;
-        }
         uint32_t sc_s = pbuf_s + which * pbatch_bytes, zp_s = sc_s + pzp_off;
         uint32_t red_a = red_lane_s;
         const int nst = count * SETS;
@@ -895,14 +892,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 }
             }
         }
-        flush(first, count);
+        __syncthreads();
         // everybody has read this batch's parameters: the batch after the next one may land there
-        if (tid == 0 && p.bulk_params && first + 2 * p.batch < ntiles)
-            copy_params(first + 2 * p.batch, min(p.batch, ntiles - first - 2 * p.batch), which);
+        copy_params(first + 2 * p.batch, min(p.batch, max(ntiles - first - 2 * p.batch, 0)), which);
+        flush(first, count);
+        cp_async_wait_but_one(); // the next batch's parameters (asked for a batch ago) have landed
+        __syncthreads();
         which ^= 1;
     }
-    if (timed_out)
-        atomicExch(p.status, 1);
 }
 
 // Raise a kernel's dynamic shared-memory limit once per device (the attribute belongs to the device that is

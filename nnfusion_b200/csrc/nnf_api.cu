@@ -3,8 +3,6 @@
 #include <cstring>
 #include <new>
 
-#include <cstdlib>
-
 #include "nnf_internal.h"
 #include "sm100_ptx.cuh"
 
@@ -50,13 +48,9 @@ bool encode_tensor_map_2d(void* encode_fn, CUtensorMap* map, CUtensorMapDataType
 
 void overlap_attribute(cudaLaunchAttribute* attr, unsigned* count)
 {
-    static const bool on = [] {
-        const char* v = getenv("NNF_B200_NO_OVERLAP");
-        return !(v && v[0] == '1');
-    }();
     attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr->val.programmaticStreamSerializationAllowed = 1;
-    *count = on ? 1 : 0;
+    *count = 1;
 }
 
 const CUtensorMap* weight_tensor_map(nnf_b200_ctx* ctx, const void* base, int rows, int row_bytes, int box_bytes,
@@ -85,32 +79,65 @@ bool aligned16(const void* p)
     return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
 }
 
-int validate(nnf_b200_ctx* ctx, const nnf_b200_linear_desc* d)
+} // namespace
+
+namespace nnf
 {
-    if (!ctx)
-        return NNF_B200_EINVAL;
+// Everything about a linear call that can be checked without a context: the descriptor's fields, and that the
+// operands match it.  Shared by nnf_b200_linear (and its variants) and the entry point that has no context.
+int check_linear_call(const nnf_b200_linear_desc* d, const void* x, const nnf_b200_qweight* w,
+                      const nnf_b200_qweight* w2, const void* gain, const void* bias, const void* y,
+                      const void* workspace, std::string* why)
+{
+    auto fail = [&](int status, const char* msg) {
+        *why = msg;
+        return status;
+    };
     if (!d)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "null descriptor");
+        return fail(NNF_B200_EINVAL, "null descriptor");
     if (d->M < 1 || d->N < 1 || d->K < 1)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "M, N and K must be positive");
+        return fail(NNF_B200_EINVAL, "M, N and K must be positive");
     if (d->w_bits != 4 && d->w_bits != 8)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "w_bits must be 4 or 8");
+        return fail(NNF_B200_EINVAL, "w_bits must be 4 or 8");
     if (d->group_size < 0)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "group_size must be >= 0");
+        return fail(NNF_B200_EINVAL, "group_size must be >= 0");
     for (int v : {d->x_dtype, d->y_dtype, d->scale_dtype})
         if (v != NNF_B200_F32 && v != NNF_B200_F16)
-            return nnf::set_error(ctx, NNF_B200_EINVAL, "dtype fields must be NNF_B200_F32 or NNF_B200_F16");
+            return fail(NNF_B200_EINVAL, "dtype fields must be NNF_B200_F32 or NNF_B200_F16");
     if (d->prologue != NNF_B200_PROLOGUE_NONE && d->prologue != NNF_B200_PROLOGUE_RMSNORM)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown prologue");
+        return fail(NNF_B200_EINVAL, "unknown prologue");
     if (d->epilogue < NNF_B200_EPILOGUE_NONE || d->epilogue > NNF_B200_EPILOGUE_ADD)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown epilogue");
+        return fail(NNF_B200_EINVAL, "unknown epilogue");
     if (d->kernel < NNF_B200_KERNEL_AUTO || d->kernel > NNF_B200_KERNEL_GEMM)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "unknown kernel selector");
+        return fail(NNF_B200_EINVAL, "unknown kernel selector");
     if (d->reserved[0] || d->reserved[1] || d->split_k < 0 || (d->flags & ~NNF_B200_FLAG_EXACT_ZP))
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "reserved fields must be zero, split_k >= 0, flags known");
+        return fail(NNF_B200_EINVAL, "reserved fields must be zero, split_k >= 0, flags known");
+    if (!x || !y || !w || !w->wq || !w->scale || !w->zp)
+        return fail(NNF_B200_EINVAL, "x, y and the weight set must be non-null");
+    const bool dual = d->epilogue == NNF_B200_EPILOGUE_SILU_MUL;
+    if (dual && (!w2 || !w2->wq || !w2->scale || !w2->zp))
+        return fail(NNF_B200_EINVAL, "SiLU*mul epilogue needs the second weight set");
+    if (!dual && w2)
+        return fail(NNF_B200_EINVAL, "second weight set given without the SiLU*mul epilogue");
+    if (d->prologue == NNF_B200_PROLOGUE_RMSNORM && !gain)
+        return fail(NNF_B200_EINVAL, "RMSNorm prologue needs gain");
+    if (d->prologue != NNF_B200_PROLOGUE_RMSNORM && gain)
+        return fail(NNF_B200_EINVAL, "gain given without the RMSNorm prologue");
+    const bool takes_bias = d->epilogue == NNF_B200_EPILOGUE_BIAS || d->epilogue == NNF_B200_EPILOGUE_ADD;
+    if (takes_bias && !bias)
+        return fail(NNF_B200_EINVAL, "bias / add epilogue needs the bias argument");
+    if (!takes_bias && bias)
+        return fail(NNF_B200_EINVAL, "bias given without a bias or add epilogue");
+    if (!aligned16(x) || !aligned16(w->wq) || (dual && !aligned16(w2->wq)) || (gain && !aligned16(gain)))
+        return fail(NNF_B200_EALIGN, "x, wq and gain must be 16-byte aligned");
+    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return fail(NNF_B200_EALIGN, "workspace must be 256-byte aligned");
     return NNF_B200_OK;
 }
+} // namespace nnf
 
+namespace
+{
 // Which kernel serves a descriptor: the HBM-bound small-M kernel up to 16 rows, the tensor-core kernel above.
 int pick_kernel(const nnf_b200_linear_desc& d)
 {
@@ -371,30 +398,13 @@ static int linear_impl(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_de
                        const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias,
                        void* y, void* workspace, size_t workspace_bytes, const nnf_b200_peers* peers)
 {
-    int rc = validate(ctx, desc);
+    if (!ctx)
+        return NNF_B200_EINVAL;
+    std::string bad;
+    int rc = nnf::check_linear_call(desc, x, w, w2, gain, bias, y, workspace, &bad);
     if (rc != NNF_B200_OK)
-        return rc;
+        return nnf::set_error(ctx, rc, bad);
     const nnf_b200_linear_desc& d = *desc;
-    if (!x || !y || !w || !w->wq || !w->scale || !w->zp)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "x, y and the weight set must be non-null");
-    const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
-    if (dual && (!w2 || !w2->wq || !w2->scale || !w2->zp))
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "SiLU*mul epilogue needs the second weight set");
-    if (!dual && w2)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "second weight set given without the SiLU*mul epilogue");
-    if (d.prologue == NNF_B200_PROLOGUE_RMSNORM && !gain)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "RMSNorm prologue needs gain");
-    if (d.prologue != NNF_B200_PROLOGUE_RMSNORM && gain)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "gain given without the RMSNorm prologue");
-    const bool takes_bias = d.epilogue == NNF_B200_EPILOGUE_BIAS || d.epilogue == NNF_B200_EPILOGUE_ADD;
-    if (takes_bias && !bias)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "bias / add epilogue needs the bias argument");
-    if (!takes_bias && bias)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "bias given without a bias or add epilogue");
-    if (!aligned16(x) || !aligned16(w->wq) || (dual && !aligned16(w2->wq)) || (gain && !aligned16(gain)))
-        return nnf::set_error(ctx, NNF_B200_EALIGN, "x, wq and gain must be 16-byte aligned");
-    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u))
-        return nnf::set_error(ctx, NNF_B200_EALIGN, "workspace must be 256-byte aligned");
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (pick_kernel(d) == NNF_B200_KERNEL_GEMV)

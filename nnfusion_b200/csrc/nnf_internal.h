@@ -56,10 +56,14 @@ struct GemvPlan
 };
 
 int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
+// Descriptor and operand checks of a linear call that need no context; *why receives the reason on failure.
+int check_linear_call(const nnf_b200_linear_desc* d, const void* x, const nnf_b200_qweight* w,
+                      const nnf_b200_qweight* w2, const void* gain, const void* bias, const void* y,
+                      const void* workspace, std::string* why);
 
 // Launch attribute that lets a kernel start while the launch before it on the stream is finishing (programmatic
 // dependent launch); every kernel launched with it executes griddepcontrol.wait before it touches anything that
-// launch may have written.  count is 0 when NNF_B200_NO_OVERLAP=1 is set in the environment.
+// launch may have written.
 void overlap_attribute(cudaLaunchAttribute* attr, unsigned* count);
 
 // Cached 2-D byte tensor map [rows][row_bytes] with a box of box_rows x box_bytes (128-byte swizzle when

@@ -12,9 +12,12 @@
 // Flags are never reset: they only grow (one 32-bit word per CTA and sender on the receiving rank), a wait is
 // "flag >= epoch".  Calls alternate between the two halves of every rank's buffer (half = epoch & 1): a rank may run
 // one call ahead of a peer that is still reading, never two (its next wait needs that peer's next flag).  The call
-// number comes from the host, or (epoch argument 0) from a counter per CTA kept next to the flags, which makes a
-// captured sequence of calls replayable.  Every wait is bounded; a wait that gives up raises the context's device
-// status word and the CTA writes nothing.
+// number comes from the host, or (epoch argument 0) from ONE counter per flag area, which makes a captured sequence
+// of calls replayable: every CTA of a launch reads it, the CTA that finishes last (a ticket word beside it) writes
+// the new value, and the next launch reads it only after this one has completed.  The layout of a flag area does
+// not depend on the size of the tensor of a particular call -- 16 header words (counter, ticket), then the flag
+// words [CTA][sender] -- so calls of different sizes may share one area.  Every wait is bounded; a wait that gives up
+// raises the context's device status word and the CTA writes nothing.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <string>
@@ -26,12 +29,13 @@ namespace
 constexpr int kMaxRanks = 8;
 constexpr int kArThreads = 256;
 constexpr uint32_t kArSpin = 1u << 19; // polls of just under a microsecond each: gives up after roughly 0.4 s
+constexpr int kArHeaderWords = 16;     // call counter, ticket, padding to 64 bytes; the flags follow
 
 struct ArParams
 {
     const char* bufs[kMaxRanks]; // buffer (both halves) of every rank, own included, as mapped on this rank
-    uint32_t* flags[kMaxRanks];  // flag words of every rank: [CTA][sender]
-    uint32_t* counters;          // this rank's call counters, one per CTA
+    uint32_t* flags[kMaxRanks];  // flag words of every rank: [CTA][sender] (behind the header words)
+    uint32_t* header;            // this rank's call counter [0] and ticket [1]
     size_t half_stride;          // bytes between the two halves of a buffer
     uint4* out;
     int* status;
@@ -64,10 +68,11 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(const ArP
         uint32_t e = p.epoch;
         if (e == 0)
         {
-            e = p.counters[blockIdx.x] + 1; // only this CTA of this rank ever touches the word; launches are ordered
+            // the launch before this one has completed (griddepcontrol.wait above), and nobody of this launch
+            // writes the word before every CTA has read it (see the ticket below)
+            e = __ldcg(p.header) + 1;
             if (e == 0)
-                e = 2;                      // skip 0 ("take the counter") at the wrap, keeping the parity
-            p.counters[blockIdx.x] = e;
+                e = 2; // skip 0 ("take the counter") at the wrap, keeping the parity
         }
         epoch_s = e;
     }
@@ -92,39 +97,48 @@ __global__ void __launch_bounds__(kArThreads) oneshot_allreduce_kernel(const ArP
         }
     }
     __syncthreads();
-    if (!ok_s)
-        return;
     const uint32_t v = blockIdx.x * kArThreads + tid;
-    if (v >= p.vecs)
-        return;
-    float acc[8];
+    if (ok_s && v < p.vecs)
+    {
+        float acc[8];
 #pragma unroll
-    for (int j = 0; j < 8; j++)
-        acc[j] = 0.f;
-    uint4 part[kMaxRanks];
+        for (int j = 0; j < 8; j++)
+            acc[j] = 0.f;
+        uint4 part[kMaxRanks];
 #pragma unroll
-    for (int r = 0; r < kMaxRanks; r++)
-        if (r < p.world)
-            part[r] = __ldcv(reinterpret_cast<const uint4*>(p.bufs[r] + (epoch & 1u) * p.half_stride) + v); // never
-                                                                          // served from a stale line
+        for (int r = 0; r < kMaxRanks; r++)
+            if (r < p.world) // never served from a stale line
+                part[r] = __ldcv(reinterpret_cast<const uint4*>(p.bufs[r] + (epoch & 1u) * p.half_stride) + v);
 #pragma unroll
-    for (int r = 0; r < kMaxRanks; r++)
-        if (r < p.world)
-        {
-            const __half2* h = reinterpret_cast<const __half2*>(&part[r]);
-#pragma unroll
-            for (int j = 0; j < 4; j++)
+        for (int r = 0; r < kMaxRanks; r++)
+            if (r < p.world)
             {
-                const float2 f = __half22float2(h[j]);
-                acc[2 * j] += f.x, acc[2 * j + 1] += f.y;
-            }
-        }
-    uint4 o;
-    __half2* oh = reinterpret_cast<__half2*>(&o);
+                const __half2* h = reinterpret_cast<const __half2*>(&part[r]);
 #pragma unroll
-    for (int j = 0; j < 4; j++)
-        oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
-    p.out[v] = o;
+                for (int j = 0; j < 4; j++)
+                {
+                    const float2 f = __half22float2(h[j]);
+                    acc[2 * j] += f.x, acc[2 * j + 1] += f.y;
+                }
+            }
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+        p.out[v] = o;
+    }
+    // device-counted calls: the CTA that arrives last moves the counter on (whatever happened above: a call that
+    // gave up still counts, so that the ranks stay in step once their peers are back)
+    if (p.epoch == 0 && tid == 0)
+    {
+        const uint32_t old = atomicAdd(p.header + 1, 1u);
+        if (old == gridDim.x - 1)
+        {
+            __stcg(p.header + 1, 0u);
+            __stcg(p.header, epoch);
+        }
+    }
 }
 } // namespace
 
@@ -134,7 +148,7 @@ size_t allreduce_flag_bytes(size_t count)
 {
     const size_t vecs = (count + 7) / 8;
     const size_t ctas = (vecs + kArThreads - 1) / kArThreads;
-    return ctas * (kMaxRanks + 1) * sizeof(uint32_t); // flags [CTA][sender], then one call counter per CTA
+    return (kArHeaderWords + ctas * kMaxRanks) * sizeof(uint32_t); // header, then flags [CTA][sender]
 }
 
 int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world, const void* const* bufs,
@@ -144,8 +158,9 @@ int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world
     for (int r = 0; r < world; r++)
     {
         p.bufs[r] = static_cast<const char*>(bufs[r]);
-        p.flags[r] = static_cast<uint32_t*>(flags[r]);
+        p.flags[r] = static_cast<uint32_t*>(flags[r]) + kArHeaderWords;
     }
+    p.header = static_cast<uint32_t*>(flags[rank]);
     p.out = static_cast<uint4*>(out);
     p.status = ctx->dev_status;
     p.rank = rank, p.world = world;
@@ -153,7 +168,6 @@ int allreduce_launch(nnf_b200_ctx* ctx, cudaStream_t stream, int rank, int world
     p.epoch = epoch;
     p.half_stride = half_stride;
     const unsigned ctas = (p.vecs + kArThreads - 1) / kArThreads;
-    p.counters = p.flags[rank] + (size_t)ctas * kMaxRanks;
     (void)cudaGetLastError();
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);

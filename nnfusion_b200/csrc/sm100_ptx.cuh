@@ -11,7 +11,7 @@ namespace nnf
 {
 namespace ptx
 {
-constexpr uint32_t kSpinLimit = 1u << 24; // polls of try_wait (each already waits a bounded time in hardware)
+constexpr uint32_t kSpinLimit = 1u << 22; // polls of try_wait (each already waits a bounded time in hardware): ~0.4 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
 {

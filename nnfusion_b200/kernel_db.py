@@ -54,8 +54,9 @@ def identifier(M: int, N: int, K: int, w_bits: int, group: int, x_dtype: int, sc
     zp = [N, (G + 1) // 2 if w_bits == 4 else G]
     ins = [[M, K], wq, [N, G], zp] * 1 + ([wq, [N, G], zp] if dual else [])
     shapes = ";".join(",".join(str(d) for d in s) for s in ins) + ";" + f"{M},{N}"
-    dts = [_DT_NAME[x_dtype], "uint8", _DT_NAME[scale_dtype], "uint8"] + \
-        (["uint8", _DT_NAME[scale_dtype], "uint8"] if dual else []) + [_DT_NAME[y_dtype]]
+    # element_type::c_type_string() spells uint8 tensors "uint8_t" (src/nnfusion/common/type/element_type.cpp:35)
+    dts = [_DT_NAME[x_dtype], "uint8_t", _DT_NAME[scale_dtype], "uint8_t"] + \
+        (["uint8_t", _DT_NAME[scale_dtype], "uint8_t"] if dual else []) + [_DT_NAME[y_dtype]]
     return "DequantDot" + shapes + "".join(dts)
 
 

@@ -8,6 +8,8 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
+HDR = 16  # words in front of the flag words of a flag area: call counter, ticket, padding
+
 
 def _setup(world, n, seed=0):
     import torch
@@ -29,7 +31,7 @@ def test_sum_in_rank_order(world, n, rank):
     import torch
     ctx, parts, bufs, flags, pb, pf = _setup(world, n, seed=world)
     epoch = 7
-    flags[rank][: (n // 8 + 255) // 256 * 8].fill_(epoch)   # every peer "has announced" call 7 to this rank
+    flags[rank][HDR: HDR + (n // 8 + 255) // 256 * 8].fill_(epoch)   # every peer "has announced" call 7 to this rank
     out = torch.empty(n, dtype=torch.float16, device="cuda")
     s = torch.cuda.current_stream().cuda_stream
     ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, rank, world, pb, pf, n, 2 * n, out.data_ptr(), epoch))
@@ -42,7 +44,7 @@ def test_sum_in_rank_order(world, n, rank):
     # the kernel announced itself to every peer, and to nobody else
     for r in range(world):
         ctas = (n // 8 + 255) // 256
-        f = flags[r].cpu().numpy()[: ctas * 8].reshape(-1, 8)
+        f = flags[r].cpu().numpy()[HDR: HDR + ctas * 8].reshape(-1, 8)
         if r != rank:
             assert (f[:, rank] == epoch).all() and (np.delete(f, rank, axis=1) == 0).all()
 
@@ -50,7 +52,7 @@ def test_sum_in_rank_order(world, n, rank):
 def test_device_counted_calls_alternate_halves():
     import torch
     ctx, parts, bufs, flags, pb, pf = _setup(3, 4096, seed=9)
-    flags[1][: 2 * 8].fill_(1000)          # the peers are "far ahead": no call of this test has to wait
+    flags[1][HDR: HDR + 2 * 8].fill_(1000)  # the peers are "far ahead": no call of this test has to wait
     out = torch.empty(4096, dtype=torch.float16, device="cuda")
     s = torch.cuda.current_stream().cuda_stream
     acc = np.zeros(4096, np.float32)
@@ -62,8 +64,47 @@ def test_device_counted_calls_alternate_halves():
         ctx.device_status()
         want = acc if call & 1 else -acc    # half (call & 1)
         np.testing.assert_array_equal(out.cpu().numpy(), want.astype(np.float16))
-    counters = flags[1].cpu().numpy()[2 * 8: 2 * 8 + 2]
-    assert (counters == 4).all()
+    header = flags[1].cpu().numpy()[:2]
+    assert header[0] == 4 and header[1] == 0          # four calls counted, ticket back at zero
+
+
+def test_calls_of_different_sizes_share_one_flag_area():
+    """One flag area, sized for the largest tensor, serves calls of 1, 2 and 1 rows of 8192 (4, 8, 4 CTAs): the call
+    counter and the flag words sit where they sit whatever the size of a call, every CTA of a call takes the same
+    buffer half, and CTAs that sat out a call do not fall behind."""
+    import torch
+    from nnfusion_b200.linear import default_context
+    ctx = default_context(0)
+    world, rank, row = 2, 0, 8192
+    rng = np.random.Generator(np.random.PCG64(21))
+    fb = int(ctx.lib.nnf_b200_allreduce_flag_bytes(2 * row))
+    flags = [torch.zeros(fb // 4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    flags[rank][HDR:].fill_(1000)                     # the peer is "far ahead" on every flag word
+    half = 2 * row * 2                                 # bytes of one buffer half (room for two rows)
+    bufs = [torch.zeros(2 * 2 * row, dtype=torch.float16, device="cuda") for _ in range(world)]
+    vp = ctypes.c_void_p
+    pb = (vp * world)(*[b.data_ptr() for b in bufs])
+    pf = (vp * world)(*[f.data_ptr() for f in flags])
+    s = torch.cuda.current_stream().cuda_stream
+    for call, rows in enumerate((1, 2, 1, 2, 2, 1), start=1):
+        n = rows * row
+        parts = [rng.standard_normal(n).astype(np.float16) for _ in range(world)]
+        for b, part in zip(bufs, parts):               # this call's addends go into half (call & 1); the other half
+            b.fill_(float("nan"))                      # is poison: a CTA that took the wrong half would show it
+            off = (call & 1) * 2 * row
+            b[off: off + n].copy_(torch.from_numpy(part))
+        out = torch.full((2 * row,), -7.0, dtype=torch.float16, device="cuda")
+        ctx.check(ctx.lib.nnf_b200_allreduce_oneshot(ctx.handle, s, rank, world, pb, pf, n, half, out.data_ptr(), 0))
+        torch.cuda.synchronize()
+        ctx.device_status()
+        want = (parts[0].astype(np.float32) + parts[1].astype(np.float32)).astype(np.float16)
+        got = out.cpu().numpy()
+        np.testing.assert_array_equal(got[:n], want)
+        assert (got[n:] == -7.0).all()                 # nothing written past the tensor of this call
+        assert int(flags[rank][0]) == call and int(flags[rank][1]) == 0
+        ctas = (n // 8 + 255) // 256
+        f = flags[1 - rank].cpu().numpy()[HDR:].reshape(-1, 8)
+        assert (f[:ctas, rank] == call).all()          # announced to the peer with the call number
 
 
 def test_later_epoch_counts_as_arrived_and_wraps():

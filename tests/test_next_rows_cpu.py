@@ -58,8 +58,10 @@ def test_odd_group_count_zero_points(tmp_path):
 def test_identifier_follows_the_reference_recipe():
     ident = kernel_db.identifier(1, 11008, 4096, 4, 128, L.F16, L.F16, L.F16)
     # op type, then shapes of inputs ; output joined with , and ; then the dtypes
-    assert ident == "DequantDot1,4096;11008,2048;11008,32;11008,16;1,11008halfuint8halfuint8half"
-    assert kernel_db.identifier(16, 4096, 4096, 8, 4096, L.F32, L.F32, L.F32).endswith("floatuint8floatuint8float")
+    # (element_type::c_type_string(): "half", "float", and "uint8_t" for u8 -- src/nnfusion/common/type/element_type.cpp:28-35;
+    # concatenated by KernelContext::generate_identifier, src/nnfusion/core/kernels/kernel_emitter.cpp:415-455)
+    assert ident == "DequantDot1,4096;11008,2048;11008,32;11008,16;1,11008halfuint8_thalfuint8_thalf"
+    assert kernel_db.identifier(16, 4096, 4096, 8, 4096, L.F32, L.F32, L.F32).endswith("floatuint8_tfloatuint8_tfloat")
     assert ident != kernel_db.identifier(2, 11008, 4096, 4, 128, L.F16, L.F16, L.F16)
 
 
