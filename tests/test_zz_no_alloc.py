@@ -75,3 +75,52 @@ def test_static_scratch_refuses_what_does_not_fit():
     assert str(L.STATIC_SCRATCH_BYTES) in msg and "scratch" in msg
     rc, msg = _static_call(lib, op, op.desc(17, x.dtype), x, y)      # M > 16 belongs to the other kernel
     assert rc == L.ENOTSUP
+
+
+def test_static_scratch_survives_a_change_of_shape():
+    """The built-in array keeps what the last call left.  A shape with few row tiles, then one with many (its tile
+    counters and partial-sum slots spread over what the first one used, and beyond), then the first again: every
+    result equals the regular entry point's, bit for bit, and no device-side wait has given up on the way."""
+    import torch
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+
+    lib = L.load()
+    rng = np.random.Generator(np.random.PCG64(92))
+    cases = []
+    for M, N, K in ((2, 272, 8192), (1, 4096, 11008), (3, 48, 16384)):
+        w = synth.make_weights(rng, N, K, 4, 128)
+        op = DequantDot(DeviceWeight.from_host(w))
+        tx = torch.from_numpy(synth.make_x(rng, M, K, np.float16)).cuda()
+        d = op.desc(M, tx.dtype)
+        plan = (ctypes.c_int32 * 8)()
+        assert lib.nnf_b200_linear_plan(op.ctx.handle, ctypes.byref(d), ctypes.byref(plan)) == L.OK
+        assert plan[2] > 1, "every case must use the scratch"
+        cases.append((op, tx, d, op(tx)))
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream().cuda_stream
+    for i in (0, 1, 0, 2, 1, 2, 0):
+        op, tx, d, want = cases[i]
+        got = torch.full_like(want, float("nan"))
+        rc, msg = _static_call(lib, op, d, tx, got)
+        assert rc == L.OK, msg
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(got.float().cpu().numpy(), want.float().cpu().numpy())
+    assert lib.nnf_b200_static_scratch_status(stream) == L.OK
+
+
+def test_static_scratch_checks_its_descriptor_like_the_regular_entry_point():
+    import torch
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+
+    lib = L.load()
+    rng = np.random.Generator(np.random.PCG64(93))
+    w = synth.make_weights(rng, 64, 1024, 4, 128)
+    op = DequantDot(DeviceWeight.from_host(w))
+    x = torch.zeros((1, 1024), dtype=torch.float16, device="cuda")
+    y = torch.zeros((1, 64), dtype=torch.float16, device="cuda")
+    for field, value, status in (("x_dtype", 7, L.EINVAL), ("flags", 64, L.EINVAL), ("kernel", L.KERNEL_GEMM, L.ENOTSUP),
+                                 ("epilogue", 9, L.EINVAL), ("prologue", 5, L.EINVAL)):
+        d = op.desc(1, x.dtype)
+        setattr(d, field, value)
+        rc, msg = _static_call(lib, op, d, x, y)
+        assert rc == status and msg, field
