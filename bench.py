@@ -34,9 +34,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 L2_BYTES = 126e6
-# dram__bytes_read.sum + dram__bytes_write.sum of one dq_gemv_kernel launch on the decode_gemv workload
-# (ncu capture summarised in profiles/dq_gemv_decode_11008x4096.md).
-NCU_TRAFFIC_DECODE_GEMV = 23_483_392
+# DRAM bytes (read + written) of one launch of the small-M kernel on the decode_gemv workload, from one ncu capture
+# of that launch (dram__bytes_read.sum + dram__bytes_write.sum; the output stays in L2).
+NCU_TRAFFIC_DECODE_GEMV = 23_496_448
 
 
 def measured_peaks():
@@ -91,14 +91,19 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.rows)}
 
 
-def rand_device_weight(torch, N, K, bits=4, group=128, scale_dtype=None, device="cuda"):
-    """Random quantised weights generated on the device (content does not matter for timing)."""
+def rand_device_weight(torch, N, K, bits=4, group=128, scale_dtype=None, device="cuda", seed=None):
+    """Random quantised weights generated on the device (content does not matter for timing; with `seed` every rank
+    gets the same tensors)."""
     from nnfusion_b200.linear import DeviceWeight
     scale_dtype = scale_dtype or torch.float16
     G = K // group
-    wq = torch.randint(0, 256, (N, K // 2 if bits == 4 else K), dtype=torch.uint8, device=device)
-    sc = (torch.rand((N, G), device=device) * 0.018 + 0.002).to(scale_dtype)
-    zp = torch.randint(0, 256, (N, (G + 1) // 2 if bits == 4 else G), dtype=torch.uint8, device=device)
+    gen = None
+    if seed is not None:
+        gen = torch.Generator(device=device)
+        gen.manual_seed(seed)
+    wq = torch.randint(0, 256, (N, K // 2 if bits == 4 else K), dtype=torch.uint8, device=device, generator=gen)
+    sc = (torch.rand((N, G), device=device, generator=gen) * 0.018 + 0.002).to(scale_dtype)
+    zp = torch.randint(0, 256, (N, (G + 1) // 2 if bits == 4 else G), dtype=torch.uint8, device=device, generator=gen)
     return DeviceWeight(N, K, bits, group, wq, sc, zp)
 
 
@@ -126,9 +131,13 @@ def ranks_healthy(torch, dist, ctx):
     return bool(t.item())
 
 
-def timed_graph_steps(torch, step_fns, steps, warmup, dist=None, health=None):
-    """Runs `steps` steps (step i calls step_fns[i % len]) replayed from CUDA graphs, timed with CUDA events on the
-    launching stream between barrier + synchronize on both sides.  Returns milliseconds (max over ranks).
+REPEATS = 31  # timed passes over the K captured steps; the median pass is reported
+
+
+def timed_graph_steps(torch, step_fns, steps, warmup, dist=None, health=None, repeats=REPEATS):
+    """Runs `steps` steps (step i calls step_fns[i % len]) replayed from CUDA graphs, `repeats` times over, each pass
+    timed with CUDA events on the launching stream between barrier + synchronize on both sides (several ranks: the
+    maximum over ranks of every pass).  Returns the median pass in milliseconds.
     `health` (several ranks only) is asked after the plain warm-up steps and after a first short graph replay; when
     it answers False the function raises ExchangeUnhealthy instead of replaying thousands of steps whose waits
     would each run to their limit."""
@@ -179,25 +188,27 @@ def timed_graph_steps(torch, step_fns, steps, warmup, dist=None, health=None):
             for _ in range(max(3, 4000 // max(1, chunk))):
                 (g_full or g_rem).replay()
             torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(full):
-            g_full.replay()
-        if g_rem is not None:
-            g_rem.replay()
-        e1.record(stream)
-        torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        ms = e0.elapsed_time(e1)
+        passes = []
+        for _ in range(max(1, repeats)):
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(full):
+                g_full.replay()
+            if g_rem is not None:
+                g_rem.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+            passes.append(e0.elapsed_time(e1))
     if dist is not None:
-        t = torch.tensor([ms], device="cuda")
+        t = torch.tensor(passes, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    return ms
+        passes = [float(v) for v in t.tolist()]
+    return statistics.median(passes)
 
 
 def timed_plain_steps(torch, step_fn, steps, warmup, dist=None):
@@ -228,7 +239,8 @@ def timed_plain_steps(torch, step_fn, steps, warmup, dist=None):
 
 
 # ----------------------------------------------------------------------------------------------- CPU reference path
-def cpu_reference_gemv(seconds_budget: float, rows: int, K: int = 4096, M: int = 1, steps=None, warmup: int = 1):
+def cpu_reference_gemv(seconds_budget: float, rows: int, K: int = 4096, M: int = 1, steps=None, warmup: int = 1,
+                       warm_seconds: float = 2.0):
     """Times the reference CPU graph (oracle/_ref: MLAS behind restated element-wise kernels; falls back to the C
     restatement) on a `rows`-row sample of the uint4 group-128 linear.  Returns (seconds per step, steps, cores, kind)."""
     import numpy as np
@@ -245,8 +257,12 @@ def cpu_reference_gemv(seconds_budget: float, rows: int, K: int = 4096, M: int =
     else:
         fn = lambda: orc.linear(x, q, scale, zp, 128, out_dtype=np.float32)
         cores, kind = os.cpu_count() or 1, "port"
-    for _ in range(max(1, warmup)):
+    # warm: at least `warmup` calls and `warm_seconds` of them (thread pool up, pages touched, caches and clocks
+    # settled), so that a short timed run measures the same state as a long one
+    t_warm, n_warm = time.perf_counter(), 0
+    while n_warm < max(1, warmup) or time.perf_counter() - t_warm < warm_seconds:
         fn()
+        n_warm += 1
     times = []
     t_start = time.perf_counter()
     i = 0
@@ -299,34 +315,31 @@ def run_decode_gemv(args, torch, sampler_index):
     bytes_step = linear_bytes(M, N, K)
     value = bytes_step * args.steps / (ms * 1e-3) / 1e9
 
-    # end to end through the call a user of the generated runtime makes with host buffers (kernel_entry_host):
-    # pinned host x -> device, the fused linear, device y -> pinned host, every step, synchronising per step.
+    # end to end through the call a user of the generated runtime makes with host buffers (kernel_entry_host): the
+    # node's host entry copies pinned host x to the device, runs the fused linear and copies y back to pinned host
+    # memory (one graph launch), then synchronises -- every step.
     xh = torch.randn(M, K).to(torch.float16).pin_memory()
     yh = torch.empty(M, N, dtype=torch.float16).pin_memory()
     e2e_steps = min(args.steps, 2000)
-
-    def e2e_step(i):
-        x.copy_(xh, non_blocking=True)
-        ops[i % ncopies](x, y)
-        yh.copy_(y, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-
-    ms_e2e = timed_plain_steps(torch, e2e_step, e2e_steps, args.warmup)
+    for op in ops:
+        op.host_entry(xh, yh)          # captures each node's graph outside the timed region
+    ms_e2e = timed_plain_steps(torch, lambda i: ops[i % ncopies].host_entry(xh, yh), e2e_steps, args.warmup)
     e2e_value = bytes_step * e2e_steps / (ms_e2e * 1e-3) / 1e9
     peaks = measured_peaks()
     out = {
         "metric": "int4_g128_decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
-        "ms_per_step": ms / args.steps, "dtype": "f16", "scaling": "weak",
+        "ms_per_step": ms / args.steps, "repeats": REPEATS, "dtype": "f16", "scaling": "weak",
         "config": {"workload": "decode_gemv: X f16 [1,4096], W u4-g128 [11008,4096], Y f16, f32 accumulate",
                    "algorithmic_bytes_per_step": bytes_step,
                    "l2": f"rotation over {ncopies} weight copies ({ncopies * bytes_step / 1e6:.0f} MB) larger than L2",
                    "launch": "CUDA graph replay of the C-ABI calls"},
         "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(value / peaks["hbm_gbs"], 4), "traffic": NCU_TRAFFIC_DECODE_GEMV,
-                     "peak_source": f"of {peaks['source']}", "kernel": "dq_gemv_kernel<4,1,false,false,false,true>"},
+                     "peak_source": f"of {peaks['source']}", "kernel": "dq_gemv_direct_kernel<4,1,false,false,2,1,true>"},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": M * K * 2,
                 "d2h_bytes_per_step": M * N * 2, "ms_per_step": ms_e2e / e2e_steps, "steps": e2e_steps,
-                "path": "pinned host x -> device, nnf_b200_linear, device y -> pinned host, stream sync, per step"},
+                "path": "DequantDot.host_entry: pinned host x -> device, nnf_b200_linear, device y -> pinned host "
+                        "(one graph launch), stream sync, per step"},
         "gpu_launches": args.steps, "clocks": cs.summary(),
     }
     return out, ops, x, y
@@ -350,7 +363,7 @@ def extra_measurements(torch, budget_s=90.0):
             ops.append(DequantDot(w, w2, gain=g))
         x = torch.randn(M, K, device="cuda").to(xdt)
         y = torch.empty(M, N, device="cuda", dtype=xdt)
-        ms = timed_graph_steps(torch, [(lambda op=op: op(x, y)) for op in ops], steps, 3)
+        ms = timed_graph_steps(torch, [(lambda op=op: op(x, y)) for op in ops], steps, 3, repeats=9)
         b = linear_bytes(M, N, K, bits, group, x.element_size(), 2 if sdt == torch.float16 else 4)
         if dual:
             b += b - M * K * x.element_size() - M * N * x.element_size()
@@ -389,7 +402,7 @@ def extra_measurements(torch, budget_s=90.0):
             layers.append(layer)
         x = torch.randn(1, H, device="cuda").to(torch.float16)
         y = torch.empty_like(x)
-        ms = timed_graph_steps(torch, [(lambda l=l: l(x, pos, out=y)) for l in layers], steps, 3)
+        ms = timed_graph_steps(torch, [(lambda l=l: l(x, pos, out=y)) for l in layers], steps, 3, repeats=9)
         kv = 2 * heads * pos * 128 * 2
         b = layers[0].weight_bytes + kv + 2 * (3 * H + H + H + 2 * H + I + I + H)
         gbs = b * steps / (ms * 1e-3) / 1e9
@@ -409,7 +422,7 @@ def extra_measurements(torch, budget_s=90.0):
             ops.append(op)
         q, k, v = (torch.randn(heads * 128, device="cuda").to(torch.float16) for _ in range(3))
         out = torch.empty((1, heads * 128), dtype=torch.float16, device="cuda")
-        ms = timed_graph_steps(torch, [(lambda op=op: op(q, k, v, pos, out=out)) for op in ops], steps, 3)
+        ms = timed_graph_steps(torch, [(lambda op=op: op(q, k, v, pos, out=out)) for op in ops], steps, 3, repeats=9)
         b = 2 * heads * (pos + 1) * 128 * 2 + 4 * heads * 128 * 2
         gbs = b * steps / (ms * 1e-3) / 1e9
         also[name] = {"us": round(ms * 1e3 / steps, 2), "GB/s": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4)}
@@ -424,7 +437,7 @@ def extra_measurements(torch, budget_s=90.0):
         mlps = [ShardedMLP(rand_device_weight(torch, inter, hidden), rand_device_weight(torch, inter, hidden),
                            rand_device_weight(torch, hidden, inter)) for _ in range(2)]
         x = torch.randn(M, hidden, device="cuda").to(torch.float16)
-        ms = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in mlps], steps, 3)
+        ms = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in mlps], steps, 3, repeats=9)
         full = 2 * (linear_bytes(M, inter, hidden) - M * hidden * 2 - M * inter * 2) + M * hidden * 2 + \
             2 * M * inter * 2 + linear_bytes(M, hidden, inter) - M * inter * 2
         gbs = full * steps / (ms * 1e-3) / 1e9
@@ -593,6 +606,36 @@ def run_mlp70b(args, torch, sampler_index, rank, world, dist):
             exchange, launch = ("NCCL all-reduce of f16 [1,8192] (a bounded wait of the peer-memory exchange gave up "
                                 "during the warm-up on this box)"), "plain launches of the C-ABI calls"
     value = full * steps / (ms * 1e-3) / 1e9
+    parity = strong = None
+    if world > 1:
+        using_peer = mlps is not nccl
+        parity = mlp_parity(torch, dist, group, rank, world, hidden, inter, peer if using_peer else None)
+        # other batch sizes of the configuration at this number of GPUs (the boundary closed by the one-shot kernel
+        # up to 16 rows, by NCCL above)
+        for m_rows, nsteps in ((16, 200), (256, 60), (4096, 12)):
+            xm = torch.randn(m_rows, hidden, device="cuda").to(torch.float16)
+            which = mlps if (m_rows <= 16 and using_peer) else nccl
+            ms_m = timed_plain_steps(torch, lambda i: which[i % ncopies](xm), nsteps, 4, dist)
+            flops = 2.0 * m_rows * 3 * hidden * inter
+            also[f"mlp70b_m{m_rows}"] = {"us": round(ms_m * 1e3 / nsteps, 2), "TFLOP/s": round(flops * nsteps / (ms_m * 1e-3) / 1e12, 1),
+                                         "exchange": "one-shot kernel" if which is mlps else "NCCL all-reduce",
+                                         "launch": "plain launches"}
+        # the same workload on ONE of this box's GPUs, timed in this run: what the N-GPU step is measured against
+        dist.barrier()
+        t1_ms = None
+        if rank == 0:
+            one = [ShardedMLP(rand_device_weight(torch, inter, hidden), rand_device_weight(torch, inter, hidden),
+                              rand_device_weight(torch, hidden, inter)) for _ in range(2)]
+            t1_steps = 200
+            t1_ms = timed_graph_steps(torch, [(lambda m=m: m(x)) for m in one], t1_steps, 4, repeats=9) / t1_steps
+            del one
+        dist.barrier()
+        if rank == 0:
+            tn_ms = ms / steps
+            strong = {"t1_us": round(t1_ms * 1e3, 2), "tN_us": round(tn_ms * 1e3, 2), "n": world,
+                      "efficiency": round(t1_ms / (world * tn_ms), 4),
+                      "note": "t1: the whole MLP (same weights' shapes, same byte count) on rank 0's GPU alone, "
+                              "CUDA-graph replay, in this run"}
     xh = torch.randn(M, hidden).to(torch.float16).pin_memory()
     yh = torch.empty(M, hidden, dtype=torch.float16).pin_memory()
 
@@ -607,7 +650,7 @@ def run_mlp70b(args, torch, sampler_index, rank, world, dist):
     ctx.device_status()
     return {
         "metric": "int4_g128_decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "steps": steps,
-        "ms_per_step": ms / steps, "dtype": "f16", "scaling": "strong",
+        "ms_per_step": ms / steps, "repeats": REPEATS, "dtype": "f16", "scaling": "strong",
         "config": {"workload": "mlp70b_decode: X f16 [1,8192], gate/up u4-g128 [28672,8192] column-sharded, down [8192,28672] "
                                "row-sharded, " + exchange,
                    "algorithmic_bytes_per_step": full, "parallelism": f"tp{world}",
@@ -615,13 +658,50 @@ def run_mlp70b(args, torch, sampler_index, rank, world, dist):
                    "launch": launch},
         "roofline": {"bound": "hbm", "achieved": round(value / world, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(value / world / peaks["hbm_gbs"], 4), "traffic": None,
-                     "peak_source": f"of {peaks['source']}, per GPU", "kernel": "dq_gemv_kernel (gate/up fused SiLU*mul, down)"},
+                     "traffic_note": "not captured: ncu runs on one rank of one GPU only, and a rank's kernels wait for "
+                                     "its peers; the one-GPU captures show traffic = algorithmic bytes for this kernel",
+                     "peak_source": f"of {peaks['source']}, per GPU",
+                     "kernel": "dq_gemv_direct_kernel (gate/up fused SiLU*mul, down)"},
+        **({"parity": parity} if parity else {}),
+        **({"strong_scaling": strong} if strong else {}),
         "e2e": {"value": round(full * e2e_steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": M * hidden * 2, "d2h_bytes_per_step": M * hidden * 2},
         "gpu_launches": (3 if (world > 1 and mlps is not nccl) else 2) * steps,  # NCCL's kernel is not counted
         "clocks": cs.summary(),
         **({"also": also} if also else {}),
     }
+
+
+def mlp_parity(torch, dist, group, rank, world, hidden, inter, peer):
+    """One step of the sharded MLP on seeded weights against the same MLP on one GPU (rank 0 computes it, everybody
+    compares), for M = 1 and 16, plus bit-equality of the ranks' results.  Returns what the bench line prints."""
+    from nnfusion_b200.tp import ShardedMLP
+    g, u, d = (rand_device_weight(torch, n, k, seed=s) for n, k, s in
+               ((inter, hidden, 101), (inter, hidden, 102), (hidden, inter, 103)))
+    sharded = ShardedMLP(g.shard_rows(rank, world), u.shard_rows(rank, world), d.shard_k(rank, world), group=group,
+                         reduce="peer" if peer is not None else "nccl", peer=peer)
+    whole = ShardedMLP(g, u, d) if rank == 0 else None
+    worst, identical = 0.0, True
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(7)
+    for m_rows in (1, 16):
+        x = torch.randn(m_rows, hidden, device="cuda", generator=gen).to(torch.float16)
+        # two calls: the exchange's two buffer halves stay in step with every other user of the same buffers
+        y = sharded(x).clone()
+        y2 = sharded(x)
+        ref = whole(x).clone() if rank == 0 else torch.empty_like(y)
+        dist.broadcast(ref, 0, group=group)
+        err = (y.float() - ref.float()).abs().max() / ref.float().abs().max()
+        t = torch.stack([err, (y != y2).any().float()])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        worst = max(worst, float(t[0]))
+        ys = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(ys, y, group=group)
+        identical = identical and float(t[1]) == 0.0 and all(bool((ys[0] == o).all()) for o in ys[1:])
+    torch.cuda.synchronize()
+    return {"max_rel_err_vs_one_gpu": worst, "tolerance": 5e-3, "within_tolerance": worst <= 5e-3,
+            "ranks_bit_identical": identical, "rows": [1, 16],
+            "how": "seeded weights, the sharded step against the unsharded MLP on rank 0's GPU, max|y-r|/max|r|"}
 
 
 # ----------------------------------------------------------------------------------------------- main

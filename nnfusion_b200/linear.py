@@ -109,6 +109,28 @@ class DeviceWeight:
                             torch.cat([p.scale for p in parts]).contiguous(),
                             torch.cat([p.zp for p in parts]).contiguous())
 
+    def shard_rows(self, rank: int, world: int) -> "DeviceWeight":
+        """Column-parallel shard on the device: output rows [rank * N/world, (rank+1) * N/world) with their parameters."""
+        if self.N % world:
+            raise ValueError(f"N={self.N} is not divisible by {world} ranks")
+        n = self.N // world
+        sl = slice(rank * n, (rank + 1) * n)
+        return DeviceWeight(n, self.K, self.bits, self.group, self.wq[sl].contiguous(), self.scale[sl].contiguous(),
+                            self.zp[sl].contiguous())
+
+    def shard_k(self, rank: int, world: int) -> "DeviceWeight":
+        """Row-parallel shard on the device: K columns [rank * K/world, ...); shards hold whole groups, and for 4-bit
+        weights an even number of them (the packed zero-points split on a byte boundary)."""
+        k = self.K // world
+        g = k // self.group if self.group else 0
+        if self.K % world or g * self.group != k or (self.bits == 4 and g % 2):
+            raise ValueError(f"K={self.K} cannot be split into {world} shards of whole (pairs of) groups of {self.group}")
+        per = 2 if self.bits == 4 else 1
+        return DeviceWeight(self.N, k, self.bits, self.group,
+                            self.wq[:, rank * k // per:(rank + 1) * k // per].contiguous(),
+                            self.scale[:, rank * g:(rank + 1) * g].contiguous(),
+                            self.zp[:, rank * g // per:(rank + 1) * g // per].contiguous())
+
     def abi(self) -> L.QWeight:
         return L.QWeight(self.wq.data_ptr(), self.scale.data_ptr(), self.zp.data_ptr())
 
