@@ -1,16 +1,17 @@
-// Language units the DequantDot emitter requires in the generated project.
+// Language units the DequantDot / DecodeAttention emitters require in the generated project (declared in
+// nnf_b200_langunit.hpp; LU_DEFINE: src/nnfusion/core/kernels/common_langunit.hpp:11-14).
 //   header::nnf_b200, macro::NNF_B200_SAFE_CALL  -> next to the units of
 //       src/nnfusion/core/kernels/cuda_gpu/cuda_langunit.cpp (CUDA_SAFE_CALL: :47-62)
 //   cmake::nnf_b200                               -> next to cmake::superscaler_cuda,
 //       src/nnfusion/engine/pass/codegen/codegen_langunit.cpp:44-51; cuda_codegen_pass adds it when the header
 //       unit is present (pattern: cuda_codegen_pass.cpp:62,100-104,1420-1424) and extends CUDA_ARCH (:1374).
-#include "nnfusion/common/languageunit.hpp"
+#include "nnf_b200_langunit.hpp"
 
-LU_DEFINE(nnfusion::kernels::cuda::header::nnf_b200, "#include \"nnf_b200.h\"\n");
+LU_DEFINE(nnfusion::kernels::header::nnf_b200, "#include \"nnf_b200.h\"\n");
 
-LU_DEFINE(nnfusion::kernels::cuda::declaration::nnf_b200_ctx, "nnf_b200_ctx* nnf_b200_ctx_0 = nullptr;\n");
+LU_DEFINE(nnfusion::kernels::declaration::nnf_b200_ctx, "nnf_b200_ctx* nnf_b200_ctx_0 = nullptr;\n");
 
-LU_DEFINE(nnfusion::kernels::cuda::macro::NNF_B200_SAFE_CALL,
+LU_DEFINE(nnfusion::kernels::macro::NNF_B200_SAFE_CALL,
           R"(#define NNF_B200_SAFE_CALL(func)                                                              \
     do                                                                                            \
     {                                                                                             \

@@ -3,6 +3,7 @@
 // Goes to src/nnfusion/core/kernels/cuda_gpu/kernels/decode_attention.cpp.
 #include "../cuda_emitter.hpp"
 #include "../cuda_langunit.hpp"
+#include "nnf_b200_langunit.hpp"
 #include "nnf_b200.h" // host functions only: workspace sizing at code-generation time
 #include "nnfusion/core/operators/generic_op/generic_op.hpp"
 

@@ -14,6 +14,18 @@ namespace
         return t == element::f16 ? "NNF_B200_F16" : "NNF_B200_F32";
     }
     int dtype_value(const element::Type& t) { return t == element::f16 ? NNF_B200_F16 : NNF_B200_F32; }
+    int epilogue_value(const std::string& e)
+    {
+        return e == "bias" ? NNF_B200_EPILOGUE_BIAS
+                           : e == "silu_mul" ? NNF_B200_EPILOGUE_SILU_MUL
+                                             : e == "add" ? NNF_B200_EPILOGUE_ADD : NNF_B200_EPILOGUE_NONE;
+    }
+    const char* epilogue_enum(const std::string& e)
+    {
+        return e == "bias" ? "NNF_B200_EPILOGUE_BIAS"
+                           : e == "silu_mul" ? "NNF_B200_EPILOGUE_SILU_MUL"
+                                             : e == "add" ? "NNF_B200_EPILOGUE_ADD" : "NNF_B200_EPILOGUE_NONE";
+    }
 }
 
 cuda::DequantDot::DequantDot(shared_ptr<KernelContext> ctx)
@@ -39,8 +51,7 @@ cuda::DequantDot::DequantDot(shared_ptr<KernelContext> ctx)
     d.y_dtype = dtype_value(ctx->outputs[0]->get_element_type());
     d.scale_dtype = dtype_value(ctx->inputs[2]->get_element_type());
     d.prologue = prologue == "rmsnorm" ? NNF_B200_PROLOGUE_RMSNORM : NNF_B200_PROLOGUE_NONE;
-    d.epilogue = epilogue == "bias" ? NNF_B200_EPILOGUE_BIAS
-                                    : epilogue == "silu_mul" ? NNF_B200_EPILOGUE_SILU_MUL : NNF_B200_EPILOGUE_NONE;
+    d.epilogue = epilogue_value(epilogue);
     workspace_bytes = nnf_b200_linear_workspace_bytes(nullptr, &d);
     if (workspace_bytes > 0)
         workspace = allocate_tensor(Shape{workspace_bytes + 256}, element::character);
@@ -59,6 +70,7 @@ LanguageUnit_p cuda::DequantDot::emit_function_body()
     probe.x_dtype = dtype_value(m_context->inputs[0]->get_element_type());
     probe.y_dtype = dtype_value(m_context->outputs[0]->get_element_type());
     probe.scale_dtype = dtype_value(m_context->inputs[2]->get_element_type());
+    probe.epilogue = epilogue_value(epilogue);
     if (nnf_b200_linear_plan(nullptr, &probe, plan) != NNF_B200_OK && M <= 16)
         return nullptr; // shape not served: the selector falls through to the next emitter (kernel_selection.cpp:262-267)
 
@@ -68,16 +80,14 @@ LanguageUnit_p cuda::DequantDot::emit_function_body()
     std::string gain = "nullptr", bias = "nullptr", w2 = "nullptr";
     if (prologue == "rmsnorm")
         gain = "input" + std::to_string(next++);
-    if (epilogue == "bias")
+    if (epilogue == "bias" || epilogue == "add") // the [M,N] addend travels in the bias argument
         bias = "input" + std::to_string(next++);
     lu << "static const nnf_b200_linear_desc desc = {" << M << ", " << N << ", " << K << ", " << w_bits << ", "
        << group_size << ", " << dtype_enum(m_context->inputs[0]->get_element_type()) << ", "
        << dtype_enum(m_context->outputs[0]->get_element_type()) << ", "
        << dtype_enum(m_context->inputs[2]->get_element_type()) << ", "
        << (prologue == "rmsnorm" ? "NNF_B200_PROLOGUE_RMSNORM" : "NNF_B200_PROLOGUE_NONE") << ", "
-       << (epilogue == "bias" ? "NNF_B200_EPILOGUE_BIAS"
-                              : epilogue == "silu_mul" ? "NNF_B200_EPILOGUE_SILU_MUL" : "NNF_B200_EPILOGUE_NONE")
-       << ", " << rms_eps << "f, NNF_B200_KERNEL_AUTO, 0, 0, {0, 0}};\n";
+       << epilogue_enum(epilogue) << ", " << rms_eps << "f, NNF_B200_KERNEL_AUTO, 0, 0, {0, 0}};\n";
     lu << "const nnf_b200_qweight w = {input1, input2, input3};\n";
     if (epilogue == "silu_mul")
     {

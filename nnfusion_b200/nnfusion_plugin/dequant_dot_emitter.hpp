@@ -4,6 +4,7 @@
 #pragma once
 #include "../cuda_emitter.hpp"
 #include "../cuda_langunit.hpp"
+#include "nnf_b200_langunit.hpp"
 
 namespace nnfusion
 {

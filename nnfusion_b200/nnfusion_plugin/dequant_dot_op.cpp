@@ -5,7 +5,10 @@
 //
 // Inputs : 0 X [M,K] (f16 / f32), 1 Wq (u8; [N,K] for 8-bit, [N,K/2] for packed 4-bit), 2 scale [N,K/group],
 //          3 zero-point (u8, packed like Wq for 4-bit), then optionally, in this order,
-//          gain [K] (prologue = "rmsnorm"), bias [N] (epilogue = "bias"), or Wq2, scale2, zp2 (epilogue = "silu_mul").
+//          gain [K] (prologue = "rmsnorm"), bias [N] (epilogue = "bias"), an addend [M,N] of the output's type
+//          (epilogue = "add": MatMulAdd with its full-size C, generic_op_define/MatMulAdd.cpp:6-35), or
+//          Wq2, scale2, zp2 (epilogue = "silu_mul").
+// Attribute out_dtype ("", "float", "half"): element type of Y; empty keeps the element type of X.
 #include "nnfusion/core/operators/generic_op/generic_op.hpp"
 
 REGISTER_OP(DequantDot)
@@ -20,7 +23,7 @@ REGISTER_OP(DequantDot)
         const int group = config["group_size"];
         const std::string pro = config["prologue"], epi = config["epilogue"];
         return (bits == 4 || bits == 8) && group >= 0 && (pro == "none" || pro == "rmsnorm") &&
-               (epi == "none" || epi == "bias" || epi == "silu_mul");
+               (epi == "none" || epi == "bias" || epi == "silu_mul" || epi == "add");
     })
     .infershape([](std::shared_ptr<graph::GNode> gnode) -> void {
         auto op = static_pointer_cast<nnfusion::op::GenericOp>(gnode->get_op_ptr());
@@ -35,5 +38,21 @@ REGISTER_OP(DequantDot)
         const size_t k_stored = (bits == 4) ? w_shape[1] * 2 : w_shape[1];
         NNFUSION_CHECK(k == k_stored) << "Contraction sizes of X and Wq differ.";
         nnfusion::Shape out{x_shape[0], w_shape[0]};
-        gnode->set_output_type_and_shape(0, gnode->get_input_element_type(0), out);
+        const std::string out_dtype = cfg["out_dtype"];
+        nnfusion::element::Type out_type = gnode->get_input_element_type(0);
+        if (out_dtype == "float")
+            out_type = nnfusion::element::f32;
+        else if (out_dtype == "half")
+            out_type = nnfusion::element::f16;
+        else
+            NNFUSION_CHECK(out_dtype.empty()) << "DequantDot: out_dtype must be \"\", \"float\" or \"half\".";
+        const std::string epi = cfg["epilogue"];
+        if (epi == "add")
+        {
+            const size_t slot = 4 + (std::string(cfg["prologue"]) == "rmsnorm" ? 1 : 0);
+            NNFUSION_CHECK(gnode->get_input_size() > slot) << "DequantDot: the add epilogue takes an [M,N] addend.";
+            NNFUSION_CHECK(gnode->get_input_shape(slot) == out && gnode->get_input_element_type(slot) == out_type)
+                << "DequantDot: the addend must have the output's shape and element type.";
+        }
+        gnode->set_output_type_and_shape(0, out_type, out);
     });
