@@ -1391,8 +1391,7 @@ static cudaError_t gemv_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& 
                                  const nnf_b200_peers* peers, cudaStream_t stream)
 {
     if (plan.direct)
-        return peers ? cudaErrorInvalidValue
-                     : gemv_direct_dispatch(d, plan, x, w, w2, gain, bias, y, status, workspace, stream);
+        return gemv_direct_dispatch(d, plan, x, w, w2, gain, bias, y, status, workspace, stream, peers);
     GemvParams p{};
     fill_params(p, d, plan, x, w, w2, gain, bias, y, status, workspace, peers);
     return dispatch(d.w_bits, plan, p, plan.splits * plan.ctas_per_split, stream);

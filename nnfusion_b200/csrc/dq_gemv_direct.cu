@@ -78,6 +78,12 @@ struct DirectParams
     // a 64-byte unit's quantisation group = unit / group_units, done as a multiplication
     int group_units;
     uint32_t group_magic; // ceil(2^32 / group_units); exact for units below 2^16
+    // Sum over the ranks of a tensor-parallel group inside this launch (ar_world > 1): see "exchange" in the kernel.
+    const char* ar_bufs[8]; // every rank's fp32 partial-output buffer (two halves), own included, as mapped here
+    uint32_t* ar_flags[8];  // every rank's flag words [row tile][sender], then one call counter per row tile
+    size_t ar_half_stride;  // bytes between the two halves of a buffer
+    uint32_t ar_epoch;      // call number from the host, or 0: counted in the words after the flags
+    int ar_rank, ar_world;
 };
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -191,7 +197,7 @@ struct DirectSmem
         bars = 0;
         red = sizeof(float) * (size_t)warps * batch * sets * mb * 8 * tq * 4;
         ss = sizeof(float) * ((size_t)warps * 8 * mb + 8 * mb);
-        flags = sizeof(int) * kBatch;
+        flags = sizeof(int) * (2 * kBatch + 4); // last-arriver flags, call numbers, "all peers answered"
         xsm = (size_t)warps * xfrag_bytes;
         total = params + bars + red + ss + flags + xsm;
     }
@@ -308,7 +314,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     float* ss_cta = ss_w + nwarps * MPAD;                               // [MPAD]
     int* last_flag = reinterpret_cast<int*>(smem_raw + p.off_flags);    // [kBatch]
     // [warp][unit][xs][fragment pair][lane] x 8 bytes: B fragments of batch rows 8..15
-    const uint32_t xsm_s = smem_u32(last_flag + kBatch) + (uint32_t)(warp * p.xfrag_bytes) + (uint32_t)lane * 8u;
+    const uint32_t xsm_s = smem_u32(last_flag + 2 * kBatch + 4) + (uint32_t)(warp * p.xfrag_bytes) + (uint32_t)lane * 8u;
     const uint32_t pbuf_s = smem_u32(pbuf);
     const uint32_t pbatch_bytes = (uint32_t)(p.batch * SETS * pset_bytes); // one batch's parameters
     const uint32_t pzp_off = (uint32_t)(p.batch * p.scale_tile_bytes);     // zero-points follow the batch's scales
@@ -758,11 +764,103 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
         return v;
     };
 
+    // ---- exchange: summing over the ranks of a tensor-parallel group inside this launch (ar_world > 1)
+    // Every rank runs this kernel with the same launch shape, so the CTA that holds the final sum of a row tile here
+    // (for splits == 1 the tile's own CTA, otherwise the split that arrived last) has one partner per rank.  It
+    // writes its fp32 sums into this rank's peer-visible buffer, tells every peer "tile t, call e" with one release
+    // store per peer, waits (bounded) for the peers' words for the same tile, reads their sums with plain peer loads
+    // and adds everything in rank order: every rank stores the same bits.  Calls alternate between the two halves
+    // of the buffers (half = e & 1): a rank can be one call ahead of a peer that is still reading a tile, never two,
+    // because the same tile's flag of the call in between is needed first.  Nothing here waits on a CTA of this GPU,
+    // and the peers' CTAs announce before they wait, so no cycle of waits can form.  A wait that gives up raises
+    // the status word; the tile is then left unwritten.
+    const bool ar = !DUAL && p.ar_world > 1;
+    uint32_t* const ep_s = reinterpret_cast<uint32_t*>(last_flag) + kBatch; // [kBatch] call number per tile
+    int* const ar_ok = reinterpret_cast<int*>(ep_s + kBatch);
+    auto ar_begin = [&](int first, int count, bool by_last_flag) {
+        uint32_t* counters = p.ar_flags[p.ar_rank] + (size_t)p.row_tiles * 8;
+        if (tid < count && (!by_last_flag || last_flag[tid] != 0))
+        {
+            uint32_t e = p.ar_epoch;
+            if (e == 0)
+            {
+                e = __ldcg(counters + tile0 + first + tid) + 1; // only the CTA that finishes the tile touches it
+                if (e == 0)
+                    e = 2; // 0 means "count for me": skip it, keeping the parity
+            }
+            ep_s[tid] = e;
+        }
+        if (tid == 0)
+            *ar_ok = 1;
+        __syncthreads();
+    };
+    auto ar_put = [&](int j, int m, int n, float v) {
+        *reinterpret_cast<float*>(const_cast<char*>(p.ar_bufs[p.ar_rank]) + (size_t)(ep_s[j] & 1u) * p.ar_half_stride +
+                                  ((size_t)m * p.N + n) * sizeof(float)) = v;
+    };
+    auto ar_end = [&](int first, int count, bool by_last_flag) {
+        auto owns = [&](int j) { return !by_last_flag || last_flag[j] != 0; };
+        uint32_t* counters = p.ar_flags[p.ar_rank] + (size_t)p.row_tiles * 8;
+        // this rank's sums are ordered before the announcements by the barrier and the release stores (cumulative
+        // over what the barrier made visible to the storing thread)
+        __syncthreads();
+        if (tid < count * p.ar_world) // thread (tile j, peer r): announce, then wait
+        {
+            const int j = tid / p.ar_world, r = tid - j * p.ar_world;
+            if (r != p.ar_rank && owns(j))
+            {
+                const int rt = tile0 + first + j;
+                const uint32_t e = ep_s[j];
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ar_flags[r] + (size_t)rt * 8 + p.ar_rank), "r"(e)
+                             : "memory");
+                const uint32_t* mine = p.ar_flags[p.ar_rank] + (size_t)rt * 8 + r;
+                bool seen = false;
+                for (uint32_t i = 0; i < (1u << 19) && !seen; i++) // roughly 0.4 s
+                {
+                    uint32_t v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+                    seen = (int32_t)(v - e) >= 0;
+                    if (!seen)
+                        __nanosleep(40);
+                }
+                if (!seen)
+                {
+                    *ar_ok = 0;
+                    atomicExch(p.status, 1);
+                }
+            }
+        }
+        if (p.ar_epoch == 0 && tid < count && owns(tid))
+            __stcg(counters + tile0 + first + tid, ep_s[tid]);
+        __syncthreads();
+        if (!*ar_ok)
+            return;
+        for (int idx = tid; idx < count * per_tile; idx += nthreads) // everybody's sums in rank order
+        {
+            const int j = idx >> pt_shift, e = idx & (per_tile - 1);
+            if (!owns(j))
+                continue;
+            int row, m, o;
+            decode(e, row, m, o);
+            const int n = (tile0 + first + j) * 16 + row;
+            if (m < p.M && n < p.N)
+            {
+                const size_t off = (size_t)(ep_s[j] & 1u) * p.ar_half_stride + ((size_t)m * p.N + n) * sizeof(float);
+                float v = 0.f;
+                for (int r = 0; r < p.ar_world; r++)
+                    v += __ldcv(reinterpret_cast<const float*>(p.ar_bufs[r] + off));
+                store_y(m, n, finish(v, 0.f, 0.f, m, n));
+            }
+        }
+    };
+
     // Add up the warps' partial sums of the local tiles [first, first + count) and write the results out.
     // (the caller brackets it with the CTA's barriers)
     auto flush = [&](int first, int count) {
         if (p.splits == 1)
         {
+            if (ar)
+                ar_begin(first, count, false);
             for (int idx = tid; idx < count * per_tile; idx += nthreads)
             {
                 const int j = idx >> pt_shift, e = idx & (per_tile - 1);
@@ -770,9 +868,16 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 decode(e, row, m, o);
                 const int n = (tile0 + first + j) * 16 + row;
                 if (m < p.M && n < p.N)
-                    store_y(m, n, finish(sum_warps(j, 0, e), DUAL ? sum_warps(j, 1, e) : 0.f,
-                                         p.rmsnorm ? ss_cta[m] : 0.f, m, n));
+                {
+                    if (ar)
+                        ar_put(j, m, n, sum_warps(j, 0, e));
+                    else
+                        store_y(m, n, finish(sum_warps(j, 0, e), DUAL ? sum_warps(j, 1, e) : 0.f,
+                                             p.rmsnorm ? ss_cta[m] : 0.f, m, n));
+                }
             }
+            if (ar)
+                ar_end(first, count, false);
         }
         else
         {
@@ -811,6 +916,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
             }
             __syncthreads();
             __threadfence();
+            if (ar)
+                ar_begin(first, count, true);
             // 3. fixed-order sum over the splits
             for (int idx = tid; idx < count * per_tile; idx += nthreads)
             {
@@ -833,9 +940,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                         if (p.rmsnorm)
                             ssum += __ldcg(slot + SETS * MB * 128 + m);
                     }
-                    store_y(m, n, finish(a0, a1, ssum, m, n));
+                    if (ar)
+                        ar_put(j, m, n, a0);
+                    else
+                        store_y(m, n, finish(a0, a1, ssum, m, n));
                 }
             }
+            if (ar)
+                ar_end(first, count, true);
         }
     };
 
@@ -1069,9 +1181,23 @@ bool gemv_direct_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, Ge
 
 cudaError_t gemv_direct_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& plan, const void* x,
                                  const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
-                                 const void* bias, void* y, int* status, void* workspace, cudaStream_t stream)
+                                 const void* bias, void* y, int* status, void* workspace, cudaStream_t stream,
+                                 const nnf_b200_peers* peers)
 {
     DirectParams p{};
+    if (peers && peers->world > 1)
+    {
+        if (plan.dual)
+            return cudaErrorInvalidValue;
+        for (int r = 0; r < peers->world; r++)
+        {
+            p.ar_bufs[r] = static_cast<const char*>(peers->bufs[r]);
+            p.ar_flags[r] = static_cast<uint32_t*>(peers->flags[r]);
+        }
+        p.ar_half_stride = peers->half_stride_bytes;
+        p.ar_epoch = peers->epoch;
+        p.ar_rank = peers->rank, p.ar_world = peers->world;
+    }
     const int ue = (d.w_bits == 4) ? 128 : 64;
     p.wq[0] = static_cast<const uint8_t*>(w->wq);
     p.scale[0] = w->scale;

@@ -237,8 +237,7 @@ size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_l
         return 0;
     if (pick_kernel(*desc) == NNF_B200_KERNEL_GEMV)
     {
-        // The larger of what the two small-M kernels ask for: which of them runs is settled per call (the sum over
-        // ranks inside the launch is served by the ring kernel only).
+        // The larger of what the two small-M kernels ask for (the ring kernel serves NNF_B200_FLAG_EXACT_ZP).
         nnf::GemvPlan plan, ring;
         std::string why;
         if (nnf::gemv_plan(ctx, *desc, &plan, &why) != NNF_B200_OK)
@@ -411,7 +410,7 @@ static int linear_impl(nnf_b200_ctx* ctx, void* stream, const nnf_b200_linear_de
     {
         nnf::GemvPlan plan;
         std::string why;
-        rc = nnf::gemv_plan(ctx, d, &plan, &why, peers == nullptr);
+        rc = nnf::gemv_plan(ctx, d, &plan, &why);
         if (rc != NNF_B200_OK)
             return nnf::set_error(ctx, rc, why);
         if (plan.workspace_bytes > 0 && (!workspace || workspace_bytes < plan.workspace_bytes))

@@ -71,13 +71,14 @@ void overlap_attribute(cudaLaunchAttribute* attr, unsigned* count);
 const CUtensorMap* weight_tensor_map(nnf_b200_ctx* ctx, const void* base, int rows, int row_bytes, int box_bytes,
                                      int box_rows);
 
-// allow_direct = false keeps the plan on the ring kernel (the only one that sums over ranks inside the launch).
+// allow_direct = false keeps the plan on the ring kernel (the one that takes the zero-points out before the multiply).
 int gemv_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan, std::string* why,
               bool allow_direct = true);
 bool gemv_direct_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, GemvPlan* plan);
 cudaError_t gemv_direct_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& plan, const void* x,
                                  const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
-                                 const void* bias, void* y, int* status, void* workspace, cudaStream_t stream);
+                                 const void* bias, void* y, int* status, void* workspace, cudaStream_t stream,
+                                 const nnf_b200_peers* peers = nullptr);
 int gemv_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const GemvPlan& plan,
                 const void* x, const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain,
                 const void* bias, void* y, void* workspace, const nnf_b200_peers* peers = nullptr);
