@@ -3,9 +3,12 @@
 The reference's front door traces a ``torch.nn.Module`` to ONNX, compiles it and swaps the module's ``forward`` for
 the compiled runtime (``nnfusion.jit``: ``src/python/nnfusion/jit.py``; ``Session`` / ``Executor``:
 ``src/python/nnfusion/session.py``, ``src/python/nnfusion/executor.py:70-243``).  Its compiler cannot be built in
-this environment, so the graph stage is skipped here: ``QuantLinear`` modules -- the Cast / Sub / Mul / Gemm pattern
-of a dequantised linear, held packed -- are bound directly to ``nnf_b200_linear`` nodes, and ``jit`` wraps a module
-the way the reference's decorator does (same call signature, torch tensors in and out, raw device pointers below).
+this environment, so its place is taken by the two ends of it that this package has: ``export_onnx`` writes a
+``QuantLinear`` module as the ONNX graph an exporter would produce for it (Cast -> Sub -> Mul -> Gemm,
+``onnx_writer.py``), ``compile_onnx`` reads such a file, folds the pattern the way the plugin's fold pass does and
+returns the module bound to one ``nnf_b200_linear`` node.  ``jit`` wraps a module the way the reference's decorator
+does (same call signature, torch tensors in and out, raw device pointers below), optionally sending every
+``QuantLinear`` through that file stage.
 """
 from __future__ import annotations
 
@@ -14,7 +17,7 @@ from typing import Optional
 import numpy as np
 import torch
 
-from . import synth
+from . import onnx_writer, synth
 from .linear import DequantDot, DeviceWeight
 
 
@@ -76,13 +79,45 @@ class QuantLinear(torch.nn.Module):
         return y.reshape(*lead, self.out_features)
 
 
-def jit(module: torch.nn.Module) -> torch.nn.Module:
+def export_onnx(m: QuantLinear, path: str, M: int, dtype: torch.dtype = torch.float16) -> None:
+    """Writes ``m`` as the un-fused ONNX graph Y[M,N] = X[M,K] . ((Cast(Wq) - Cast(zp)) * scale)^T (+ bias)."""
+    host = synth.QuantLinear.from_packed(m.out_features, m.in_features, m.bits, m.group_size,
+                                         m.wq.cpu().numpy(), m.scale.cpu().numpy(), m.zp.cpu().numpy())
+    np_dtype = np.float16 if dtype == torch.float16 else np.float32
+    bias = m.bias.detach().cpu().numpy() if m.bias is not None else None
+    onnx_writer.write_dequant_linear(path, host, M, np_dtype, bias)
+
+
+def compile_onnx(path: str, bits: int = 8, device: str = "cuda") -> QuantLinear:
+    """Reads an ONNX file holding the dequantised-linear pattern, folds it into one node and returns the module that
+    runs it on ``device``.  ``bits`` = 4 packs the weights two per byte again (the file holds one byte per element)."""
+    w, bias, _ = onnx_writer.fold_dequant_linear(onnx_writer.read_model(path), bits)
+    return QuantLinear.from_host(w, None if bias is None else bias.astype(np.float32)).to(device)
+
+
+def jit(module: torch.nn.Module, onnx_dir: Optional[str] = None) -> torch.nn.Module:
     """Prepare ``module`` for inference through this library: binds every ``QuantLinear`` inside it to its fused
     node (so the first call does not pay for it) and switches gradients off.  Returns the module, callable as
-    before -- the reference's ``nnfusion.jit`` keeps the same contract."""
+    before -- the reference's ``nnfusion.jit`` keeps the same contract.  With ``onnx_dir`` every ``QuantLinear`` is
+    first exported to ``<onnx_dir>/<name>.onnx`` and replaced by what ``compile_onnx`` makes of that file, the way
+    the reference goes through a file between tracing and compiling."""
+    import os
     module.eval()
     for p in module.parameters():
         p.requires_grad_(False)
+    if onnx_dir is not None:
+        os.makedirs(onnx_dir, exist_ok=True)
+        for name, m in list(module.named_modules()):
+            if isinstance(m, QuantLinear) and name:
+                path = os.path.join(onnx_dir, name.replace(".", "_") + ".onnx")
+                dtype = torch.float16 if m.scale.dtype == torch.float16 else torch.float32
+                export_onnx(m, path, 1, dtype)
+                compiled = compile_onnx(path, m.bits, str(m.wq.device))
+                parent = module
+                *head, leaf = name.split(".")
+                for part in head:
+                    parent = getattr(parent, part)
+                setattr(parent, leaf, compiled)
     for m in module.modules():
         if isinstance(m, QuantLinear) and m.wq.is_cuda:
             m.node()

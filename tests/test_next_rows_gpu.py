@@ -23,8 +23,9 @@ def test_constants_from_disk_run_unchanged(tmp_path):
     assert orc.max_rel_err(y, oracle_linear(x, w)) <= TOL_F16
 
 
+@pytest.mark.parametrize("via_onnx", [False, True])
 @pytest.mark.parametrize("M", [1, 33])
-def test_front_door_allclose(M):
+def test_front_door_allclose(M, via_onnx, tmp_path):
     # shaped like the reference's test/python/test_jit.py:8-40: the wrapped module against plain PyTorch
     import torch
     from nnfusion_b200.jit import QuantLinear, jit
@@ -41,7 +42,15 @@ def test_front_door_allclose(M):
         def forward(self, x):
             return self.fc2(torch.relu(self.fc1(x)))
 
-    net = jit(Net().cuda())
+    # via_onnx: every quantised linear goes module -> ONNX file (Cast / Sub / Mul / Gemm) -> fold -> fused node
+    net = jit(Net().cuda(), onnx_dir=str(tmp_path) if via_onnx else None)
+    if via_onnx:
+        import os
+        from nnfusion_b200 import onnx_writer
+        assert sorted(os.listdir(tmp_path)) == ["fc1.onnx", "fc2.onnx"]
+        ops = [n["op_type"] for n in onnx_writer.read_model(str(tmp_path / "fc2.onnx"))["graph"]["nodes"]]
+        assert ops == ["Reshape", "Cast", "Cast", "Sub", "Mul", "Reshape", "Gemm"]
+        np.testing.assert_array_equal(net.fc1.wq.cpu().numpy(), w1.wq)      # the same packed bytes come back
     x = torch.from_numpy(synth.make_x(rng, M, 256, np.float16)).cuda().reshape(M, 1, 256)
     y = net(x)
     assert y.shape == (M, 1, 128) and y.dtype == torch.float16
