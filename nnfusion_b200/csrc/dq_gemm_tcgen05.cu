@@ -470,6 +470,50 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
         atomicExch(p.status, 1);
 }
 
+// Pre-pass for activations the tensor-core kernel does not take as they are: fp32 rows are rounded to fp16, and with
+// the RMSNorm prologue every row is scaled by rsqrt(mean(x^2) + eps) * gain on the way (fp32 arithmetic, one
+// rounding).  One CTA per row; the row is read twice when it has to be normalised (the second time from L2).
+// Replaces the reference's Multiply -> Sum -> Divide -> Add -> Rsqrt -> Multiply chain in front of the Dot
+// (reduce: src/nnfusion/core/kernels/cuda_gpu/kernels/reduce.hpp:18-600) and its Convert.
+template <bool XF32>
+__global__ void __launch_bounds__(256) prep_activations_kernel(const void* x, const float* gain, __half* out, int K,
+                                                               float eps)
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ float part[8];
+    const size_t row = blockIdx.x;
+    auto load = [&](int k) -> float {
+        return XF32 ? static_cast<const float*>(x)[row * K + k] : __half2float(static_cast<const __half*>(x)[row * K + k]);
+    };
+    float r = 1.f;
+    if (gain != nullptr)
+    {
+        float ss = 0.f;
+        for (int k = threadIdx.x; k < K; k += blockDim.x)
+        {
+            const float v = load(k);
+            ss += v * v;
+        }
+        for (int o = 16; o > 0; o >>= 1)
+            ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if ((threadIdx.x & 31) == 0)
+            part[threadIdx.x >> 5] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) // fixed order: repeatable
+            tot += part[w];
+        r = 1.0f / sqrtf(tot / (float)K + eps);
+    }
+    for (int k = threadIdx.x; k < K; k += blockDim.x)
+    {
+        float v = load(k) * r;
+        if (gain != nullptr)
+            v *= gain[k];
+        out[row * K + k] = __float2half_rn(v);
+    }
+}
+
 template <int WBITS, bool DUAL>
 cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap& tw0, const CUtensorMap& tw1,
                    int grid, cudaStream_t stream)
@@ -503,24 +547,20 @@ int gemm_configure(nnf_b200_ctx*)
     return NNF_B200_OK;
 }
 
-size_t gemm_workspace_bytes(const nnf_b200_ctx*, const nnf_b200_linear_desc&)
+// fp32 activations and the RMSNorm prologue go through a pre-pass that writes fp16 [M,K] into the workspace.
+static bool needs_prepass(const nnf_b200_linear_desc& d)
 {
-    return 0;
+    return d.x_dtype == NNF_B200_F32 || d.prologue == NNF_B200_PROLOGUE_RMSNORM;
+}
+
+size_t gemm_workspace_bytes(const nnf_b200_ctx*, const nnf_b200_linear_desc& d)
+{
+    return needs_prepass(d) ? ((size_t)d.M * d.K * sizeof(__half) + 255) / 256 * 256 : 0;
 }
 
 int gemm_supported(const nnf_b200_ctx*, const nnf_b200_linear_desc& d, std::string* why)
 {
     const int group = d.group_size > 0 ? d.group_size : d.K;
-    if (d.x_dtype != NNF_B200_F16)
-    {
-        *why = "tensor-core kernel takes fp16 activations";
-        return NNF_B200_ENOTSUP;
-    }
-    if (d.prologue != NNF_B200_PROLOGUE_NONE)
-    {
-        *why = "tensor-core kernel has no RMSNorm prologue";
-        return NNF_B200_ENOTSUP;
-    }
     if (d.K % 64 != 0 || group % 64 != 0 || d.K % group != 0)
     {
         *why = "K and group_size must be multiples of 64 and K a multiple of group_size";
@@ -535,9 +575,28 @@ int gemm_supported(const nnf_b200_ctx*, const nnf_b200_linear_desc& d, std::stri
 }
 
 int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_desc& d, const void* x,
-                const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void*, const void* bias, void* y, void*,
-                size_t)
+                const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias, void* y,
+                void* workspace, size_t workspace_bytes)
 {
+    if (needs_prepass(d))
+    {
+        const size_t need = gemm_workspace_bytes(ctx, d);
+        if (!workspace || workspace_bytes < need)
+            return set_error(ctx, NNF_B200_EWORKSPACE,
+                             "workspace of " + std::to_string(need) + " bytes required (fp16 copy of the activations)");
+        __half* xh = static_cast<__half*>(workspace);
+        const float* g = d.prologue == NNF_B200_PROLOGUE_RMSNORM ? static_cast<const float*>(gain) : nullptr;
+        (void)cudaGetLastError();
+        if (d.x_dtype == NNF_B200_F32)
+            prep_activations_kernel<true><<<d.M, 256, 0, stream>>>(x, g, xh, d.K, d.rms_eps);
+        else
+            prep_activations_kernel<false><<<d.M, 256, 0, stream>>>(x, g, xh, d.K, d.rms_eps);
+        cudaError_t pe = cudaGetLastError();
+        if (pe != cudaSuccess)
+            return set_error(ctx, NNF_B200_ECUDA, std::string("prep_activations launch: ") + cudaGetErrorString(pe));
+        ctx->launches++;
+        x = xh;
+    }
     const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
     const int bx = dual ? 128 : 256;
     const int row_bytes = d.w_bits == 4 ? d.K / 2 : d.K;

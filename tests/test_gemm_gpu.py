@@ -80,13 +80,52 @@ def test_config3_prefill_m256_full_size(N, K):
     _check(y, oracle_linear(x, w), TOL_F16, tight=2e-3)
 
 
-def test_unsupported_combinations_are_refused():
-    from nnfusion_b200.linear import NNFB200Error
-    x, w = synth.u4g128(35, 32, 128, 256, x_dtype=np.float32)
-    with pytest.raises(NNFB200Error) as e:
-        gpu_linear(x, w, kernel=L.KERNEL_GEMM)
-    assert e.value.status == L.ENOTSUP
-    x, w = synth.u4g128(36, 32, 128, 256)
-    with pytest.raises(NNFB200Error) as e:
-        gpu_linear(x, w, gain=np.ones(256, np.float32), kernel=L.KERNEL_GEMM)
-    assert e.value.status == L.ENOTSUP
+@pytest.mark.parametrize("M", [32, 300])
+def test_fp32_activations_through_the_prepass(M):
+    """fp32 x (and fp32 y): a pre-pass rounds the activations to fp16 once, then the tensor-core kernel runs.  The
+    fp32 path's tolerance of 1e-3 still holds (one rounding of x and one of the scale to fp16: a few 1e-4)."""
+    x, w = synth.u4g128(35 + M, M, 136, 1024, x_dtype=np.float32)
+    y = gpu_linear(x, w, kernel=L.KERNEL_GEMM)
+    assert y.dtype == np.float32
+    err = orc.max_rel_err(y, oracle_linear(x, w))
+    assert err <= 1e-3, err
+
+
+@pytest.mark.parametrize("M", [64, 256])
+def test_config1_format_large_m(M):
+    """Configuration 1's operand types (x fp32, uint8 weights, fp32 per-channel scale) at M above the small-M kernel's
+    range, through automatic dispatch."""
+    rng = np.random.Generator(np.random.PCG64(36))
+    x = synth.make_x(rng, M, 4096, np.float32)
+    w = synth.make_weights(rng, 512, 4096, 8, 4096, np.float32, (0.001, 0.01), (120, 137))
+    y = gpu_linear(x, w)
+    err = orc.max_rel_err(y, oracle_linear(x, w))
+    assert err <= 1e-3, err
+
+
+@pytest.mark.parametrize("xdt", [np.float16, np.float32])
+@pytest.mark.parametrize("M,dual", [(40, False), (130, True)])
+def test_rmsnorm_prologue_through_the_prepass(M, dual, xdt):
+    rng = np.random.Generator(np.random.PCG64(37))
+    K, N = 1024, 264
+    x = synth.make_x(rng, M, K, xdt)
+    gain = rng.uniform(0.9, 1.1, K).astype(np.float32)
+    wg = synth.make_weights(rng, N, K, 4, 128)
+    wu = synth.make_weights(rng, N, K, 4, 128) if dual else None
+    y = gpu_linear(x, wg, wu, gain=gain, kernel=L.KERNEL_GEMM)
+    _check(y, oracle_linear(x, wg, wu, gain=gain), TOL_F16, tight=3e-3)
+
+
+def test_prepass_needs_its_workspace():
+    import ctypes
+    import torch
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+    x, w = synth.u4g128(38, 32, 128, 256, x_dtype=np.float32)
+    op = DequantDot(DeviceWeight.from_host(w), kernel=L.KERNEL_GEMM)
+    tx = torch.from_numpy(x).cuda()
+    d = op.desc(32, tx.dtype)
+    assert int(op.ctx.lib.nnf_b200_linear_workspace_bytes(op.ctx.handle, ctypes.byref(d))) >= 32 * 256 * 2
+    y = torch.empty((32, 128), dtype=torch.float32, device="cuda")
+    rc = op.ctx.lib.nnf_b200_linear(op.ctx.handle, torch.cuda.current_stream().cuda_stream, ctypes.byref(d),
+                                    tx.data_ptr(), ctypes.byref(op._abi_w), None, None, None, y.data_ptr(), None, 0)
+    assert rc == L.EWORKSPACE
