@@ -159,11 +159,15 @@ NNF_B200_API int nnf_b200_sm_count(const nnf_b200_ctx* ctx);
 
 /* Bytes of scratch the described call needs (0 if none).  The emitter requests
  * it with KernelEmitter::allocate_tensor so that it is planned into the static
- * pool (src/nnfusion/core/kernels/kernel_emitter.cpp:282-319).  The scratch must
- * be zero-filled once before its first use (nnf_b200_workspace_reset); every
- * call leaves it zeroed again.  Calls that share one scratch buffer must not
- * overlap on the device.  ctx may be NULL (a 148-SM device is assumed), for sizing
- * at code-generation time. */
+ * pool (src/nnfusion/core/kernels/kernel_emitter.cpp:282-319).  It holds arrival
+ * counters in front of partial sums (K split over CTAs at M <= 16; output tiles
+ * shared by persistent CTAs above that, where it also holds the fp16 copy of fp32
+ * or RMS-normalised activations).  The scratch must be zero-filled once before
+ * its first use (nnf_b200_workspace_reset); every call leaves its counters zeroed
+ * again, so calls of one descriptor can follow one another on the same buffer;
+ * zero-fill it again before it serves another descriptor.  Calls that share one
+ * scratch buffer must not overlap on the device.  ctx may be NULL (a 148-SM device
+ * is assumed), for sizing at code-generation time. */
 NNF_B200_API size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc);
 
 /* Launch shape the library would use for a descriptor, for tuning and reporting:

@@ -50,7 +50,7 @@ struct Cfg
     static constexpr int ASTAGES = STAGES;
     static constexpr int KB_PER_CHUNK = (WBITS == 4) ? 4 : 2; // k-blocks per 128-byte raw chunk
     static constexpr int RAW_BYTES = (WBITS == 4) ? 32 : 64;  // raw bytes per row and k-block
-    static constexpr int DQ_GROUPS = 2;                       // groups of 4 warps alternating k-blocks
+    static constexpr int DQ_GROUPS = DUAL ? 2 : 4;            // groups of 4 warps that take the k-blocks in turn
     static constexpr int DQ_WARPS = 4 * DQ_GROUPS * SETS;
     static constexpr int THREADS = (DQ_WARPS + 3) * 32;
     static constexpr int X_STAGE_BYTES = BX * 128;
@@ -58,11 +58,13 @@ struct Cfg
     static constexpr int A_COL0 = SETS * BX;     // first TMEM column of the A stages
     static constexpr int A_STAGE_COLS = BK / 2;  // 64 fp16 per lane = 32 columns
     static constexpr int TMEM_COLS = 512;
-    static constexpr int NUM_BARRIERS = 2 * STAGES + 2 * SETS * WSTAGES + 1;
+    // full / empty per ring stage, full / empty per raw-weight stage and set, then: accumulator full, accumulator
+    // drained, partial sums written, ticket known
+    static constexpr int NUM_BARRIERS = 2 * STAGES + 2 * SETS * WSTAGES + 4;
     static constexpr size_t SMEM_BYTES =
         1024 + (size_t)XSTAGES * X_STAGE_BYTES + (size_t)SETS * WSTAGES * W_STAGE_BYTES + NUM_BARRIERS * 8 + 64;
+    static constexpr int SLOT_FLOATS = SETS * BX * BN; // one tile's accumulators as fp32: a partial sum in the workspace
     static_assert(A_COL0 + SETS * ASTAGES * A_STAGE_COLS <= TMEM_COLS, "tensor memory budget");
-    static_assert(KB_PER_CHUNK % DQ_GROUPS == 0, "every group must touch every raw chunk");
 };
 
 struct GemmParams
@@ -72,12 +74,16 @@ struct GemmParams
     const float* bias;
     void* y;
     int* status;
+    uint32_t* counters; // [tiles] arrivals at a tile that several CTAs share; zero before and after a launch
+    float* slots;       // [2 * CTAs][SLOT_FLOATS] partial sums of shared tiles
     int M, N, K;
     int group, G, zp_row_bytes;
     int y_f32, scale_f32, has_bias;
     int has_addend; // bias points at an [M,N] tensor of y's type instead of fp32 [N]
-    int m_tiles;
-    int fast_store; // fp16 y, N a multiple of 8, y 16-byte aligned: the tile is written in 16-byte pieces
+    int m_tiles;    // batch tiles; tile t covers batch tile t % m_tiles of weight-row tile t / m_tiles
+    int tiles;      // output tiles in all
+    int kbpg_shift; // log2(group_size / 64) if that is a power of two, else -1
+    int cpt;        // raw chunks (the unit of work) per tile: ceil(K / 64 / KB_PER_CHUNK)
 };
 
 constexpr uint32_t kGemmSpin = 1u << 22;
@@ -95,6 +101,14 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     }
     *abort_flag = 1;
     return false;
+}
+
+// For whole warps (the conversion warps): every lane waits, and the warp agrees on the outcome, so that the lanes stay
+// together for the warp-level hand-offs that follow.
+__device__ __forceinline__ bool warp_wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    const bool ok = wait_or_abort(bar, parity, abort_flag);
+    return __all_sync(0xffffffffu, ok);
 }
 
 // Same for the thread that issues the MMAs: it is the kernel's critical path, so it polls without backing off.
@@ -118,6 +132,55 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr)
            (2ull << 61);
 }
 
+// The CTA's share of the launch: units [u_begin, u_end) of tiles * cpt raw chunks, walked as segments that each lie
+// inside one tile.  Every role of the CTA walks the same list.
+struct Segment
+{
+    int tile;     // output tile
+    int c0, c1;   // raw chunks [c0, c1) of the tile
+    int kb0, kb1; // k-blocks [kb0, kb1)
+    bool whole;   // the CTA computes the tile alone
+};
+
+template <int KB_PER_CHUNK>
+struct WorkList
+{
+    int u, u_end; // tiles * cpt fits 31 bits (checked on the host)
+    __device__ WorkList(const GemmParams& p)
+    {
+        const long long U = (long long)p.tiles * p.cpt;
+        u = (int)((long long)blockIdx.x * U / gridDim.x);
+        u_end = (int)((long long)(blockIdx.x + 1) * U / gridDim.x);
+    }
+    __device__ bool next(const GemmParams& p, Segment& s)
+    {
+        if (u >= u_end)
+            return false;
+        s.tile = u / p.cpt;
+        s.c0 = u - s.tile * p.cpt;
+        s.c1 = min(p.cpt, s.c0 + (u_end - u));
+        s.kb0 = s.c0 * KB_PER_CHUNK;
+        s.kb1 = min(p.K / 64, s.c1 * KB_PER_CHUNK);
+        s.whole = s.c0 == 0 && s.c1 == p.cpt;
+        u += s.c1 - s.c0;
+        return true;
+    }
+};
+
+// The CTA whose share holds unit u: the largest c with floor(c * U / G) <= u.
+__device__ __forceinline__ int cta_of_unit(long long u, long long U, int G)
+{
+    return (int)(((u + 1) * G + U - 1) / U) - 1;
+}
+
+// Where CTA c keeps its partial sum of tile t: slot 2c if t is the first tile of its share, else 2c + 1 (a share has
+// at most two tiles that it does not compute alone, its first and its last).
+__device__ __forceinline__ int slot_of(int c, int t, long long U, int G, int cpt)
+{
+    const int first_tile = (int)(((long long)c * U / G) / cpt);
+    return 2 * c + (t == first_tile ? 0 : 1);
+}
+
 template <int WBITS, bool DUAL>
 __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     dq_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x,
@@ -132,6 +195,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     uint64_t* bars = reinterpret_cast<uint64_t*>(wsm + (size_t)SETS * C::WSTAGES * C::W_STAGE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARRIERS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile uint32_t* ticket_slot = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
 
     const uint32_t bar0 = smem_u32(bars);
     // full(s): the x tile has landed (TMA transaction bytes) and every conversion thread has stored its row of
@@ -140,29 +204,33 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     auto empty = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
     auto full_w = [&](int set, int s) { return bar0 + 8u * (2 * C::STAGES + set * C::WSTAGES + s); };
     auto empty_w = [&](int set, int s) { return bar0 + 8u * (2 * C::STAGES + SETS * C::WSTAGES + set * C::WSTAGES + s); };
-    const uint32_t acc_full = bar0 + 8u * (C::NUM_BARRIERS - 1);
+    const uint32_t acc_full = bar0 + 8u * (C::NUM_BARRIERS - 4);     // a segment's MMAs have completed
+    const uint32_t acc_empty = bar0 + 8u * (C::NUM_BARRIERS - 3);    // every conversion thread has read its part of D
+    const uint32_t part_done = bar0 + 8u * (C::NUM_BARRIERS - 2);    // every conversion thread has written its partial sums
+    const uint32_t ticket_ready = bar0 + 8u * (C::NUM_BARRIERS - 1); // the tile's arrival count is in ticket_slot
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m_tile = blockIdx.x % p.m_tiles, n_tile = blockIdx.x / p.m_tiles;
-    const int m0 = m_tile * C::BX, n0 = n_tile * C::BN;
     const int KB = p.K / C::BK;
     constexpr int TMA_WARP = C::DQ_WARPS, MMA_WARP = C::DQ_WARPS + 1, TMAW_WARP = C::DQ_WARPS + 2;
 
-    // ---------------------------------------------------------------- set-up
+    // ---------------------------------------------------------------- set-up (once per CTA)
     if (tid == 0)
     {
         for (int s = 0; s < C::STAGES; s++)
         {
-            mbar_init(full(s), SETS * 128 + 1);
+            mbar_init(full(s), SETS * 128 + 1); // every conversion thread's row and the x tile
             mbar_init(empty(s), 1);
         }
         for (int set = 0; set < SETS; set++)
             for (int s = 0; s < C::WSTAGES; s++)
             {
                 mbar_init(full_w(set, s), 1);
-                mbar_init(empty_w(set, s), 4 * C::DQ_GROUPS * 32);
+                mbar_init(empty_w(set, s), C::KB_PER_CHUNK * 128); // 128 rows read per k-block of the chunk
             }
         mbar_init(acc_full, 1);
+        mbar_init(acc_empty, C::DQ_WARPS * 32);
+        mbar_init(part_done, C::DQ_WARPS * 32);
+        mbar_init(ticket_ready, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -175,6 +243,8 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    WorkList<C::KB_PER_CHUNK> work(p);
+    Segment sg;
 
     if (warp == TMA_WARP)
     {
@@ -182,15 +252,20 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
         if (lane == 0)
         {
             bool ok = true;
-            for (int kb = 0; kb < KB && ok; kb++)
+            uint32_t it = 0; // k-blocks of this CTA so far: ring position
+            while (ok && work.next(p, sg))
             {
-                const int s = kb % C::XSTAGES;
-                const uint32_t ph = (uint32_t)(kb / C::XSTAGES) & 1u;
-                ok = wait_or_abort(empty(s), ph ^ 1u, abort_flag);
-                if (!ok)
-                    break;
-                mbar_arrive_expect_tx(full(s), C::X_STAGE_BYTES);
-                tma_load_2d(smem_u32(xs + (size_t)s * C::X_STAGE_BYTES), &tmap_x, full(s), kb * C::BK, m0);
+                const int m0 = (sg.tile % p.m_tiles) * C::BX;
+                for (int kb = sg.kb0; kb < sg.kb1; kb++, it++)
+                {
+                    const int s = it % C::XSTAGES;
+                    const uint32_t ph = (it / C::XSTAGES) & 1u;
+                    ok = wait_or_abort(empty(s), ph ^ 1u, abort_flag);
+                    if (!ok)
+                        break;
+                    mbar_arrive_expect_tx(full(s), C::X_STAGE_BYTES);
+                    tma_load_2d(smem_u32(xs + (size_t)s * C::X_STAGE_BYTES), &tmap_x, full(s), kb * C::BK, m0);
+                }
             }
         }
     }
@@ -202,19 +277,23 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
         if (lane == 0)
         {
             bool ok = true;
-            const int chunks = (KB + C::KB_PER_CHUNK - 1) / C::KB_PER_CHUNK;
-            for (int chunk = 0; chunk < chunks && ok; chunk++)
+            uint32_t wc = 0; // chunks of this CTA so far
+            while (ok && work.next(p, sg))
             {
-                const int s = chunk % C::WSTAGES;
-                const uint32_t ph = (uint32_t)(chunk / C::WSTAGES) & 1u;
-                for (int set = 0; set < SETS && ok; set++)
+                const int n0 = (sg.tile / p.m_tiles) * C::BN;
+                for (int chunk = sg.c0; chunk < sg.c1 && ok; chunk++, wc++)
                 {
-                    ok = wait_or_abort(empty_w(set, s), ph ^ 1u, abort_flag);
-                    if (!ok)
-                        break;
-                    mbar_arrive_expect_tx(full_w(set, s), C::W_STAGE_BYTES);
-                    tma_load_2d(smem_u32(wsm + (size_t)(set * C::WSTAGES + s) * C::W_STAGE_BYTES),
-                                set == 0 ? &tmap_w0 : &tmap_w1, full_w(set, s), chunk * 128, n0);
+                    const int s = wc % C::WSTAGES;
+                    const uint32_t ph = (wc / C::WSTAGES) & 1u;
+                    for (int set = 0; set < SETS && ok; set++)
+                    {
+                        ok = wait_or_abort(empty_w(set, s), ph ^ 1u, abort_flag);
+                        if (!ok)
+                            break;
+                        mbar_arrive_expect_tx(full_w(set, s), C::W_STAGE_BYTES);
+                        tma_load_2d(smem_u32(wsm + (size_t)(set * C::WSTAGES + s) * C::W_STAGE_BYTES),
+                                    set == 0 ? &tmap_w0 : &tmap_w1, full_w(set, s), chunk * 128, n0);
+                    }
                 }
             }
         }
@@ -227,27 +306,41 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
             // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = BX, M = 128
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(C::BX >> 3) << 17) | ((uint32_t)(C::BN >> 4) << 24);
             bool ok = true;
-            for (int kb = 0; kb < KB && ok; kb++)
+            uint32_t it = 0, si = 0;
+            while (ok && work.next(p, sg))
             {
-                const int sx = kb % C::STAGES, sa = sx;
-                ok = wait_hot(full(sx), (uint32_t)(kb / C::STAGES) & 1u, abort_flag);
-                if (!ok)
-                    break;
-                tcgen05_fence_after();
-                const uint32_t xaddr = smem_u32(xs + (size_t)sx * C::X_STAGE_BYTES);
-#pragma unroll
-                for (int set = 0; set < SETS; set++)
+                if (si > 0)
                 {
-                    const uint32_t d_tmem = tmem_base + (uint32_t)(set * C::BX);
-                    const uint32_t a_tmem = tmem_base + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS);
-#pragma unroll
-                    for (int kk = 0; kk < C::BK / 16; kk++)
-                        tcgen05_mma_ts(d_tmem, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
-                                       (kb | kk) != 0 ? 1u : 0u);
+                    // the accumulator still holds the previous segment until the conversion warps have read it
+                    ok = wait_hot(acc_empty, (si - 1) & 1u, abort_flag);
+                    if (!ok)
+                        break;
+                    tcgen05_fence_after();
                 }
-                tcgen05_commit(empty(sx)); // arrives when the MMAs above have consumed the stage
+                for (int kb = sg.kb0; kb < sg.kb1; kb++, it++)
+                {
+                    const int sx = it % C::STAGES, sa = sx;
+                    ok = wait_hot(full(sx), (it / C::STAGES) & 1u, abort_flag);
+                    if (!ok)
+                        break;
+                    tcgen05_fence_after();
+                    const uint32_t xaddr = smem_u32(xs + (size_t)sx * C::X_STAGE_BYTES);
+#pragma unroll
+                    for (int set = 0; set < SETS; set++)
+                    {
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(set * C::BX);
+                        const uint32_t a_tmem = tmem_base + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS);
+#pragma unroll
+                        for (int kk = 0; kk < C::BK / 16; kk++)
+                            tcgen05_mma_ts(d_tmem, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
+                                           (kb != sg.kb0 || kk != 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty(sx)); // arrives when the MMAs above have consumed the stage
+                }
+                if (ok)
+                    tcgen05_commit(acc_full);
+                si++;
             }
-            tcgen05_commit(acc_full);
         }
     }
     else
@@ -257,153 +350,179 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
         const int grp = (warp >> 2) % C::DQ_GROUPS;
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;           // row of the tile = TMEM lane
-        const int n = min(n0 + r, p.N - 1);          // rows past N read the last row's parameters, never stored
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int kb_per_group = p.group / C::BK;
-        const uint32_t wsm_s = smem_u32(wsm), xs_s = smem_u32(xs);
+        const uint32_t wsm_s = smem_u32(wsm);
+        constexpr int PEERS = C::DQ_WARPS / 4;       // warps per TMEM lane quarter
+        const int peer = warp >> 2;                  // 0 .. PEERS-1
         bool ok = true;
+        uint32_t it_base = 0; // k-blocks of this CTA before the segment in hand: ring position of its first one
+        uint32_t wc_base = 0; // raw chunks likewise
+        uint32_t si = 0, npart = 0;
 
-        auto load_scale = [&](int gidx) -> float {
-            const size_t i = (size_t)n * p.G + gidx;
-            return p.scale_f32 ? __ldg(static_cast<const float*>(p.scale[set]) + i)
-                               : __half2float(__ldg(static_cast<const __half*>(p.scale[set]) + i));
-        };
-        auto load_zp = [&](int gidx) -> uint32_t {
-            if (WBITS == 4)
-                return (__ldg(p.zp[set] + (size_t)n * p.zp_row_bytes + (gidx >> 1)) >> (4 * (gidx & 1))) & 0xF;
-            return __ldg(p.zp[set] + (size_t)n * p.G + gidx);
-        };
-        // (scale, zero-point) of the k-block in hand and, prefetched one iteration ahead, of the next one: the
-        // loads complete while the current k-block is converted.
-        float sc = 0.f, sc_next = 0.f;
-        uint32_t zq = 0, zq_next = 0;
-        if (grp < KB)
+        // Scales and zero-points: the raw words of this group's next two k-blocks wait in registers, in two sets
+        // that take turns.  Nothing touches a loaded word before its k-block is converted (a move, a shift or a
+        // conversion right after the load would make the thread sit out the whole load latency there), and the first
+        // two of a segment are asked for before the previous segment's accumulator is read back.
+        struct RawParams
         {
-            sc_next = load_scale(grp / kb_per_group);
-            zq_next = load_zp(grp / kb_per_group);
-        }
-
-        // Raw bytes of k-block kb -> 64 fp16 (q - zp) * scale in k order: register i holds k = 2i (low half) and
-        // k = 2i + 1 (high half).  Returns false if the wait for the raw chunk was aborted.
-        auto convert = [&](int kb, uint32_t (&a)[32]) -> bool {
-            const int chunk = kb / C::KB_PER_CHUNK, j = kb % C::KB_PER_CHUNK, sw = chunk % C::WSTAGES;
-            sc = sc_next, zq = zq_next;
-            {
-                const int kb_n = kb + C::DQ_GROUPS;
-                if (kb_n < KB && kb_n / kb_per_group != kb / kb_per_group)
-                {
-                    sc_next = load_scale(kb_n / kb_per_group);
-                    zq_next = load_zp(kb_n / kb_per_group);
-                }
-            }
-            if (j < C::DQ_GROUPS) // first k-block of this chunk for this thread
-                if (!wait_or_abort(full_w(set, sw), (uint32_t)(chunk / C::WSTAGES) & 1u, abort_flag))
-                    return false;
-            // this row's raw bytes: 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
-            const uint32_t row = wsm_s + (uint32_t)((set * C::WSTAGES + sw) * C::W_STAGE_BYTES + r * 128);
-            constexpr int NV = C::RAW_BYTES / 16;
-            uint4 raw[NV];
-#pragma unroll
-            for (int v = 0; v < NV; v++)
-                raw[v] = lds128(row + (uint32_t)(((j * NV + v) ^ (r & 7)) * 16));
-            if (j + C::DQ_GROUPS >= C::KB_PER_CHUNK || kb + C::DQ_GROUPS >= KB)
-                mbar_arrive(empty_w(set, sw)); // last read of this chunk by this thread
-
-            const __half2 s2 = __float2half2_rn(sc);
-            if (WBITS == 4)
-            {
-                const uint32_t zc = (0x6400u | zq) | ((0x5400u | (zq << 4)) << 16); // (1024 + zp, 64 + zp)
-#pragma unroll
-                for (int v = 0; v < NV; v++)
-                {
-                    const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
-#pragma unroll
-                    for (int wi = 0; wi < 4; wi++)
-#pragma unroll
-                        for (int b = 0; b < 4; b++)
-                        {
-                            // byte b of the word holds elements 2b (bits 0-3) and 2b+1 (bits 4-7)
-                            uint32_t t = __byte_perm(w4[wi], 0u, 0x1111u * b);
-                            asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(t), "n"(0x00F0000Fu), "n"(0x54006400u));
-                            __half2 h = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<const __half2*>(&zc));
-                            h = __hmul2(h, s2);
-                            a[(v * 4 + wi) * 4 + b] = *reinterpret_cast<uint32_t*>(&h);
-                        }
-                }
-            }
+            uint32_t s, z;
+            int g;
+        };
+        RawParams pa{0, 0, 0}, pb{0, 0, 0};
+        // rows past N read the last row's parameters, never stored
+        auto row_of = [&](int tile) { return min((tile / p.m_tiles) * C::BN + r, p.N - 1); };
+        auto ask = [&](int n, int kb, int kb_last, RawParams& q) {
+            const int kbc = min(kb, kb_last);
+            q.g = p.kbpg_shift >= 0 ? (kbc >> p.kbpg_shift) : kbc / kb_per_group;
+            const size_t i = (size_t)n * p.G + q.g;
+            if (p.scale_f32)
+                q.s = __ldg(static_cast<const uint32_t*>(p.scale[set]) + i);
             else
+                q.s = __ldg(static_cast<const unsigned short*>(p.scale[set]) + i);
+            q.z = WBITS == 4 ? __ldg(p.zp[set] + (size_t)n * p.zp_row_bytes + (q.g >> 1)) : __ldg(p.zp[set] + i);
+        };
+        bool asked = false;
+
+        while (ok && work.next(p, sg))
+        {
+            const int n = row_of(sg.tile);
+            if (!asked)
             {
-                const uint32_t zc = (0x6400u | zq) * 0x00010001u; // 1024 + zp in both halves
+                ask(n, sg.kb0 + grp, sg.kb1 - 1, pa);
+                ask(n, sg.kb0 + grp + C::DQ_GROUPS, sg.kb1 - 1, pb);
+            }
+
+            // One k-block: raw bytes -> 64 fp16 (q - zp) * scale in k order (register i holds k = 2i in its low half
+            // and k = 2i + 1 in its high half) -> this thread's row of the A stage in tensor memory -> tell the MMA
+            // thread.  The group's k-block after next gets its parameters asked for on the way.
+            auto one = [&](int kb, RawParams& q) -> bool {
+                const int chunk = kb / C::KB_PER_CHUNK, j = kb % C::KB_PER_CHUNK;
+                const uint32_t wci = wc_base + (uint32_t)(chunk - sg.c0);
+                const int sw = wci % C::WSTAGES;
+                if (!wait_or_abort(full_w(set, sw), (wci / C::WSTAGES) & 1u, abort_flag))
+                    return false;
+                // this row's raw bytes: 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
+                const uint32_t row = wsm_s + (uint32_t)((set * C::WSTAGES + sw) * C::W_STAGE_BYTES + r * 128);
+                constexpr int NV = C::RAW_BYTES / 16;
+                uint4 raw[NV];
 #pragma unroll
                 for (int v = 0; v < NV; v++)
+                    raw[v] = lds128(row + (uint32_t)(((j * NV + v) ^ (r & 7)) * 16));
+                // One arrival per k-block read; the tile's last k-block also stands in for the k-blocks that a
+                // short last chunk does not have.
+                mbar_arrive_n(empty_w(set, sw), kb == KB - 1 ? (uint32_t)(C::KB_PER_CHUNK - j) : 1u);
+
+                const float sc = p.scale_f32 ? __uint_as_float(q.s) : __half2float(__ushort_as_half((unsigned short)q.s));
+                const uint32_t zq = WBITS == 4 ? (q.z >> (4 * (q.g & 1))) & 0xFu : q.z;
+                ask(n, kb + 2 * C::DQ_GROUPS, sg.kb1 - 1, q);
+                const __half2 s2 = __float2half2_rn(sc);
+                uint32_t a[32];
+                if (WBITS == 4)
                 {
-                    const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
+                    const uint32_t zc = (0x6400u | zq) | ((0x5400u | (zq << 4)) << 16); // (1024 + zp, 64 + zp)
 #pragma unroll
-                    for (int wi = 0; wi < 4; wi++)
+                    for (int v = 0; v < NV; v++)
+                    {
+                        const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
 #pragma unroll
-                        for (int b = 0; b < 2; b++)
-                        {
-                            uint32_t t = __byte_perm(w4[wi], 0x64646464u, b ? 0x4342 : 0x4140); // 1024 + (b0, b1)
-                            __half2 h = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<const __half2*>(&zc));
-                            h = __hmul2(h, s2);
-                            a[(v * 4 + wi) * 2 + b] = *reinterpret_cast<uint32_t*>(&h);
-                        }
+                        for (int wi = 0; wi < 4; wi++)
+#pragma unroll
+                            for (int b = 0; b < 4; b++)
+                            {
+                                // byte b of the word holds elements 2b (bits 0-3) and 2b+1 (bits 4-7)
+                                uint32_t t = __byte_perm(w4[wi], 0u, 0x1111u * b);
+                                asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(t) : "r"(t), "n"(0x00F0000Fu), "n"(0x54006400u));
+                                __half2 h = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<const __half2*>(&zc));
+                                h = __hmul2(h, s2);
+                                a[(v * 4 + wi) * 4 + b] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                    }
+                }
+                else
+                {
+                    const uint32_t zc = (0x6400u | zq) * 0x00010001u; // 1024 + zp in both halves
+#pragma unroll
+                    for (int v = 0; v < NV; v++)
+                    {
+                        const uint32_t w4[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
+#pragma unroll
+                        for (int wi = 0; wi < 4; wi++)
+#pragma unroll
+                            for (int b = 0; b < 2; b++)
+                            {
+                                uint32_t t = __byte_perm(w4[wi], 0x64646464u, b ? 0x4342 : 0x4140); // 1024 + (b0, b1)
+                                __half2 h = __hsub2(*reinterpret_cast<__half2*>(&t), *reinterpret_cast<const __half2*>(&zc));
+                                h = __hmul2(h, s2);
+                                a[(v * 4 + wi) * 2 + b] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                    }
+                }
+                // hand the converted k-block to the tensor core: wait for the A stage, store, publish
+                const uint32_t itv = it_base + (uint32_t)(kb - sg.kb0);
+                const int sa = itv % C::ASTAGES;
+                if (!wait_or_abort(empty(sa), ((itv / C::ASTAGES) & 1u) ^ 1u, abort_flag))
+                    return false;
+                tcgen05_fence_after();
+                tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS), a);
+                tcgen05_wait_st();
+                tcgen05_fence_before();
+                mbar_arrive(full(sa));
+                return true;
+            };
+            // The groups take the k-blocks in turn.  A group's warps sit on different schedulers next to the other
+            // groups' warps, which hide one another's waits: no second register buffer.
+            for (int kb = sg.kb0 + grp; ok && kb < sg.kb1; kb += 2 * C::DQ_GROUPS)
+            {
+                ok = one(kb, pa);
+                if (ok && kb + C::DQ_GROUPS < sg.kb1)
+                    ok = one(kb + C::DQ_GROUPS, pb);
+            }
+            it_base += (uint32_t)(sg.kb1 - sg.kb0);
+            wc_base += (uint32_t)(sg.c1 - sg.c0);
+            {
+                WorkList<C::KB_PER_CHUNK> ahead = work;
+                Segment nx;
+                asked = ahead.next(p, nx);
+                if (asked)
+                {
+                    const int n_next = row_of(nx.tile);
+                    ask(n_next, nx.kb0 + grp, nx.kb1 - 1, pa);
+                    ask(n_next, nx.kb0 + grp + C::DQ_GROUPS, nx.kb1 - 1, pb);
                 }
             }
-            return true;
-        };
-        // Hand the converted k-block to the tensor core: wait for the A stage, store to tensor memory.
-        auto stage = [&](int kb, const uint32_t (&a)[32]) -> bool {
-            const int sa = kb % C::ASTAGES;
-            if (!wait_or_abort(empty(sa), ((uint32_t)(kb / C::ASTAGES) & 1u) ^ 1u, abort_flag))
-                return false;
-            tcgen05_fence_after();
-            tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS), a);
-            return true;
-        };
-        auto publish = [&](int kb) {
-            tcgen05_wait_st();
-            tcgen05_fence_before();
-            mbar_arrive(full(kb % C::ASTAGES));
-        };
-        // Two register buffers: while the tensor-memory store of one k-block drains, the next one is converted.
-        uint32_t a0[32], a1[32];
-        int kb = grp;
-        if (kb < KB)
-            ok = convert(kb, a0);
-        while (ok && kb < KB)
-        {
-            const int kb1 = kb + C::DQ_GROUPS, kb2 = kb1 + C::DQ_GROUPS;
-            if (!(ok = stage(kb, a0)))
-                break;
-            if (kb1 < KB && !(ok = convert(kb1, a1)))
-                break;
-            publish(kb);
-            if (kb1 >= KB)
-                break;
-            if (!(ok = stage(kb1, a1)))
-                break;
-            if (kb2 < KB && !(ok = convert(kb2, a0)))
-                break;
-            publish(kb1);
-            kb = kb2;
-        }
 
-        // ------------------------------------------------------------ epilogue
-        // D holds y transposed (lane = weight row n, column = batch row m).  With fp16 output the tile is turned
-        // around through shared memory (the x ring is idle by now) so that y is written in 16-byte pieces along n;
-        // otherwise every value is stored on its own.
-        if (ok)
-            ok = wait_or_abort(acc_full, 0u, abort_flag);
-        if (ok)
-            tcgen05_fence_after();
-        {
-            constexpr int PEERS = C::DQ_WARPS / 4;   // warps per TMEM lane quarter
-            const int peer = warp >> 2;              // 0 .. PEERS-1
-            const int nrow = n0 + r;
-            const float bias = (p.has_bias && nrow < p.N) ? __ldg(p.bias + nrow) : 0.f;
-            // the tile is staged in the x ring as [BX][128] halves, row m = 256 bytes
+            // -------------------------------------------------------- the segment's accumulator
+            // D holds y transposed (lane = weight row n, column = batch row m): for one m the 32 lanes of a warp
+            // hold 32 consecutive n.  A tile computed by this CTA alone goes through the epilogue to y; a shared
+            // tile's accumulator goes to this CTA's slot in the workspace as fp32, and the CTA that arrives last
+            // at the tile adds the slots in the order of the K ranges and writes y.
             if (ok)
+                ok = wait_or_abort(acc_full, si & 1u, abort_flag);
+            si++;
+            if (!ok)
+                break;
+            tcgen05_fence_after();
+            const int nrow = (sg.tile / p.m_tiles) * C::BN + r, m0 = (sg.tile % p.m_tiles) * C::BX;
+            const float bias = (p.has_bias && nrow < p.N) ? __ldg(p.bias + nrow) : 0.f;
+            auto emit = [&](int ml, float v, float u) {
+                const int m = m0 + ml;
+                if (DUAL)
+                    v = v * (1.0f / (1.0f + expf(-v))) * u;
+                v += bias;
+                if (m < p.M && nrow < p.N)
+                {
+                    const size_t at = (size_t)m * p.N + nrow;
+                    if (p.has_addend)
+                        v += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[at]
+                                     : __half2float(reinterpret_cast<const __half*>(p.bias)[at]);
+                    if (p.y_f32)
+                        static_cast<float*>(p.y)[at] = v;
+                    else
+                        static_cast<__half*>(p.y)[at] = __float2half_rn(v);
+                }
+            };
+            if (sg.whole)
             {
                 for (int cb = peer; cb < C::BX / 32; cb += PEERS)
                 {
@@ -412,46 +531,171 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                     if (DUAL)
                         tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::BX + cb * 32), d1);
                     tcgen05_wait_ld();
+                    if (cb + PEERS >= C::BX / 32)
+                    {
+                        tcgen05_fence_before();
+                        mbar_arrive(acc_empty); // this thread's last read of D: the next segment may overwrite it
+                    }
+#pragma unroll
+                    for (int jx = 0; jx < 32; jx++)
+                        emit(cb * 32 + jx, __uint_as_float(d0[jx]), DUAL ? __uint_as_float(d1[jx]) : 0.f);
+                }
+            }
+            else
+            {
+                const long long U = (long long)p.tiles * p.cpt;
+                const int G = (int)gridDim.x;
+                const int c_first = cta_of_unit((long long)sg.tile * p.cpt, U, G);
+                const int c_last = cta_of_unit((long long)(sg.tile + 1) * p.cpt - 1, U, G);
+                const uint32_t pieces = (uint32_t)(c_last - c_first + 1);
+                float* mine = p.slots + (size_t)slot_of((int)blockIdx.x, sg.tile, U, G, p.cpt) * C::SLOT_FLOATS;
+                for (int cb = peer; cb < C::BX / 32; cb += PEERS)
+                {
+                    uint32_t d0[32], d1[32];
+                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(cb * 32), d0);
+                    if (DUAL)
+                        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::BX + cb * 32), d1);
+                    tcgen05_wait_ld();
+                    if (cb + PEERS >= C::BX / 32)
+                    {
+                        tcgen05_fence_before();
+                        mbar_arrive(acc_empty);
+                    }
 #pragma unroll
                     for (int jx = 0; jx < 32; jx++)
                     {
-                        const int ml = cb * 32 + jx, m = m0 + ml;
-                        float v = __uint_as_float(d0[jx]);
+                        const int ml = cb * 32 + jx;
+                        mine[(size_t)ml * C::BN + r] = __uint_as_float(d0[jx]);
                         if (DUAL)
-                        {
-                            const float u = __uint_as_float(d1[jx]);
-                            v = v * (1.0f / (1.0f + expf(-v))) * u;
-                        }
-                        v += bias;
-                        if (p.has_addend && m < p.M && nrow < p.N)
-                            v += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[(size_t)m * p.N + nrow]
-                                         : __half2float(reinterpret_cast<const __half*>(p.bias)[(size_t)m * p.N + nrow]);
-                        if (p.fast_store)
-                            sts16(xs_s + (uint32_t)((ml * 128 + r) * 2), __half_as_ushort(__float2half_rn(v)));
-                        else if (m < p.M && nrow < p.N)
-                        {
-                            if (p.y_f32)
-                                static_cast<float*>(p.y)[(size_t)m * p.N + nrow] = v;
-                            else
-                                static_cast<__half*>(p.y)[(size_t)m * p.N + nrow] = __float2half_rn(v);
-                        }
+                            mine[(size_t)(C::BX + ml) * C::BN + r] = __uint_as_float(d1[jx]);
                     }
                 }
-            }
-            if (p.fast_store)
-            {
-                // all conversion warps (and only they) meet here, whether or not they got this far unharmed
-                asm volatile("bar.sync 1, %0;" ::"n"(C::DQ_WARPS * 32) : "memory");
-                if (!*abort_flag)
+                __threadfence();
+                mbar_arrive(part_done);
+                if (warp == 0)
                 {
-                    const int t = warp * 32 + lane; // 0 .. DQ_WARPS*32-1
-                    for (int c = t; c < C::BX * 16; c += C::DQ_WARPS * 32)
+                    // The whole warp waits (a lane spinning on its own while its warp-mates spin on another barrier
+                    // starves), then one lane takes the ticket.
+                    const bool landed = warp_wait_or_abort(part_done, npart & 1u, abort_flag);
+                    if (lane == 0 && landed)
                     {
-                        const int ml = c >> 4, nc = (c & 15) * 8;
-                        const int m = m0 + ml, n = n0 + nc;
-                        if (m < p.M && n < p.N)
-                            *reinterpret_cast<uint4*>(static_cast<__half*>(p.y) + (size_t)m * p.N + n) =
-                                lds128(xs_s + (uint32_t)((ml * 128 + nc) * 2));
+                        __threadfence(); // the partial sums of all threads before the ticket
+                        const uint32_t before = atomicAdd(p.counters + sg.tile, 1u);
+                        __threadfence();
+                        if (before == pieces - 1)
+                            p.counters[sg.tile] = 0u; // leave the counter zeroed for the next call
+                        *ticket_slot = before;
+                        mbar_arrive(ticket_ready);
+                    }
+                    __syncwarp();
+                }
+                ok = wait_or_abort(ticket_ready, npart & 1u, abort_flag);
+                npart++;
+                if (!ok)
+                    break;
+                if (*ticket_slot == pieces - 1)
+                {
+                    // Last to arrive: add the tile's slots in the order of their K ranges and write y.  Nothing ties
+                    // a thread to a tensor-memory lane here, so every thread takes four neighbouring weight rows of
+                    // one batch row at a time (16-byte loads), four such pieces and two slots per round trip.
+                    __threadfence();
+                    constexpr int NT = C::DQ_WARPS * 32;        // threads at work
+                    constexpr int Q = C::BX * C::BN / 4;        // float4 per weight set in a slot
+                    static_assert(Q % (NT * 4) == 0, "four pieces per thread and pass");
+                    const int n_base = (sg.tile / p.m_tiles) * C::BN;
+                    const bool vec = (p.N % 4 == 0) && !p.has_addend &&
+                                     (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
+                    for (int q0 = warp * 32 + lane; q0 < Q; q0 += NT * 4)
+                    {
+                        float4 v[4], u[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            v[j] = make_float4(0.f, 0.f, 0.f, 0.f), u[j] = v[j];
+                        for (int c = c_first; c <= c_last; c += 2) // fixed order: repeatable
+                        {
+                            const bool two = c + 1 <= c_last;
+                            const float4* s0 = reinterpret_cast<const float4*>(
+                                p.slots + (size_t)slot_of(c, sg.tile, U, G, p.cpt) * C::SLOT_FLOATS);
+                            const float4* s1 = reinterpret_cast<const float4*>(
+                                p.slots + (size_t)slot_of(two ? c + 1 : c, sg.tile, U, G, p.cpt) * C::SLOT_FLOATS);
+                            float4 a0[4], a1[4], b0[4], b1[4];
+#pragma unroll
+                            for (int j = 0; j < 4; j++)
+                            {
+                                a0[j] = __ldcg(s0 + q0 + j * NT);
+                                a1[j] = __ldcg(s1 + q0 + j * NT);
+                                if (DUAL)
+                                {
+                                    b0[j] = __ldcg(s0 + Q + q0 + j * NT);
+                                    b1[j] = __ldcg(s1 + Q + q0 + j * NT);
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; j++)
+                            {
+                                v[j].x += a0[j].x, v[j].y += a0[j].y, v[j].z += a0[j].z, v[j].w += a0[j].w;
+                                if (two)
+                                    v[j].x += a1[j].x, v[j].y += a1[j].y, v[j].z += a1[j].z, v[j].w += a1[j].w;
+                                if (DUAL)
+                                {
+                                    u[j].x += b0[j].x, u[j].y += b0[j].y, u[j].z += b0[j].z, u[j].w += b0[j].w;
+                                    if (two)
+                                        u[j].x += b1[j].x, u[j].y += b1[j].y, u[j].z += b1[j].z, u[j].w += b1[j].w;
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                        {
+                            const int f = (q0 + j * NT) * 4;    // float index inside the set: [batch row][weight row]
+                            const int ml = f / C::BN, nl = f % C::BN;
+                            const int m = m0 + ml, n4 = n_base + nl;
+                            const float vv[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                            const float uu[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
+                            float o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++)
+                            {
+                                float w = vv[e];
+                                if (DUAL)
+                                    w = w * (1.0f / (1.0f + expf(-w))) * uu[e];
+                                if (p.has_bias && n4 + e < p.N)
+                                    w += __ldg(p.bias + n4 + e);
+                                o[e] = w;
+                            }
+                            if (m >= p.M)
+                                continue;
+                            if (vec && n4 + 3 < p.N)
+                            {
+                                const size_t at = (size_t)m * p.N + n4;
+                                if (p.y_f32)
+                                    *reinterpret_cast<float4*>(static_cast<float*>(p.y) + at) = make_float4(o[0], o[1], o[2], o[3]);
+                                else
+                                {
+                                    const __half2 h0 = __floats2half2_rn(o[0], o[1]), h1 = __floats2half2_rn(o[2], o[3]);
+                                    uint2 pk;
+                                    pk.x = *reinterpret_cast<const uint32_t*>(&h0), pk.y = *reinterpret_cast<const uint32_t*>(&h1);
+                                    *reinterpret_cast<uint2*>(static_cast<__half*>(p.y) + at) = pk;
+                                }
+                            }
+                            else
+                            {
+#pragma unroll
+                                for (int e = 0; e < 4; e++)
+                                    if (n4 + e < p.N)
+                                    {
+                                        const size_t at = (size_t)m * p.N + n4 + e;
+                                        float w = o[e];
+                                        if (p.has_addend)
+                                            w += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[at]
+                                                         : __half2float(reinterpret_cast<const __half*>(p.bias)[at]);
+                                        if (p.y_f32)
+                                            static_cast<float*>(p.y)[at] = w;
+                                        else
+                                            static_cast<__half*>(p.y)[at] = __float2half_rn(w);
+                                    }
+                            }
+                        }
                     }
                 }
             }
@@ -553,9 +797,37 @@ static bool needs_prepass(const nnf_b200_linear_desc& d)
     return d.x_dtype == NNF_B200_F32 || d.prologue == NNF_B200_PROLOGUE_RMSNORM;
 }
 
-size_t gemm_workspace_bytes(const nnf_b200_ctx*, const nnf_b200_linear_desc& d)
+// How a launch is laid out: persistent CTAs share tiles * chunks-per-tile units of work evenly; the workspace holds
+// the arrival counters of the tiles, two partial-sum slots per CTA and, when needed, the fp16 copy of x.
+struct GemmLayout
 {
-    return needs_prepass(d) ? ((size_t)d.M * d.K * sizeof(__half) + 255) / 256 * 256 : 0;
+    int bx, m_tiles, n_tiles, tiles, cpt, grid;
+    size_t counter_bytes, slot_bytes, prepass_bytes;
+    size_t total() const { return counter_bytes + slot_bytes + prepass_bytes; }
+};
+
+static GemmLayout gemm_layout(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d)
+{
+    GemmLayout L{};
+    const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
+    L.bx = dual ? 128 : 256;
+    L.m_tiles = (d.M + L.bx - 1) / L.bx;
+    L.n_tiles = (d.N + 127) / 128;
+    L.tiles = L.m_tiles * L.n_tiles;
+    const int kb_per_chunk = d.w_bits == 4 ? 4 : 2;
+    L.cpt = (d.K / 64 + kb_per_chunk - 1) / kb_per_chunk;
+    const long long units = (long long)L.tiles * L.cpt;
+    const int sms = ctx ? ctx->sm_count : 148;
+    L.grid = (int)(units < sms ? units : sms);
+    L.counter_bytes = ((size_t)L.tiles * sizeof(uint32_t) + 255) / 256 * 256;
+    L.slot_bytes = (size_t)2 * L.grid * 128 * 256 * sizeof(float); // SETS * BX * BN is 128 * 256 in both variants
+    L.prepass_bytes = needs_prepass(d) ? ((size_t)d.M * d.K * sizeof(__half) + 255) / 256 * 256 : 0;
+    return L;
+}
+
+size_t gemm_workspace_bytes(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d)
+{
+    return gemm_layout(ctx, d).total();
 }
 
 int gemm_supported(const nnf_b200_ctx*, const nnf_b200_linear_desc& d, std::string* why)
@@ -578,13 +850,17 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
                 const nnf_b200_qweight* w, const nnf_b200_qweight* w2, const void* gain, const void* bias, void* y,
                 void* workspace, size_t workspace_bytes)
 {
+    const GemmLayout L = gemm_layout(ctx, d);
+    if (!workspace || workspace_bytes < L.total())
+        return set_error(ctx, NNF_B200_EWORKSPACE,
+                         "workspace of " + std::to_string(L.total()) +
+                             " bytes required (tile counters, partial sums of shared tiles, fp16 copy of the activations)");
+    if (reinterpret_cast<uintptr_t>(workspace) & 15u)
+        return set_error(ctx, NNF_B200_EALIGN, "the workspace must be 16-byte aligned");
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
     if (needs_prepass(d))
     {
-        const size_t need = gemm_workspace_bytes(ctx, d);
-        if (!workspace || workspace_bytes < need)
-            return set_error(ctx, NNF_B200_EWORKSPACE,
-                             "workspace of " + std::to_string(need) + " bytes required (fp16 copy of the activations)");
-        __half* xh = static_cast<__half*>(workspace);
+        __half* xh = reinterpret_cast<__half*>(ws + L.counter_bytes + L.slot_bytes);
         const float* g = d.prologue == NNF_B200_PROLOGUE_RMSNORM ? static_cast<const float*>(gain) : nullptr;
         (void)cudaGetLastError();
         if (d.x_dtype == NNF_B200_F32)
@@ -598,7 +874,7 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
         x = xh;
     }
     const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
-    const int bx = dual ? 128 : 256;
+    const int bx = L.bx;
     const int row_bytes = d.w_bits == 4 ? d.K / 2 : d.K;
     GemmParams p{};
     p.scale[0] = w->scale;
@@ -619,9 +895,15 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     p.scale_f32 = d.scale_dtype == NNF_B200_F32;
     p.has_addend = d.epilogue == NNF_B200_EPILOGUE_ADD;
     p.has_bias = bias != nullptr && !p.has_addend;
-    p.m_tiles = (d.M + bx - 1) / bx;
-    p.fast_store = !p.y_f32 && d.N % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0;
-    const int n_tiles = (d.N + 127) / 128;
+    p.m_tiles = L.m_tiles;
+    p.tiles = L.tiles;
+    p.cpt = L.cpt;
+    p.kbpg_shift = -1;
+    for (int sh = 0; sh < 31; sh++)
+        if ((p.group / 64) == (1 << sh))
+            p.kbpg_shift = sh;
+    p.counters = reinterpret_cast<uint32_t*>(ws);
+    p.slots = reinterpret_cast<float*>(ws + L.counter_bytes);
 
     // x: fp16 [M][K], boxes of BX rows x 64 elements (the tensor map is not cached: x moves between calls)
     alignas(64) CUtensorMap tx;
@@ -639,7 +921,7 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     if (!tw0 || !tw1)
         return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
 
-    const int grid = p.m_tiles * n_tiles;
+    const int grid = L.grid;
     cudaError_t e;
     if (d.w_bits == 4)
         e = dual ? launch<4, true>(p, tx, tw0v, tw1v, grid, stream) : launch<4, false>(p, tx, tw0v, tw1v, grid, stream);

@@ -129,3 +129,48 @@ def test_prepass_needs_its_workspace():
     rc = op.ctx.lib.nnf_b200_linear(op.ctx.handle, torch.cuda.current_stream().cuda_stream, ctypes.byref(d),
                                     tx.data_ptr(), ctypes.byref(op._abi_w), None, None, None, y.data_ptr(), None, 0)
     assert rc == L.EWORKSPACE
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Persistent CTAs that share tiles: the work of a launch is cut evenly into raw-chunk units, so tiles at the seams
+# are computed by two or more CTAs and added in a fixed order by the last one to arrive.
+
+@pytest.mark.parametrize("M,N,K,bits", [
+    (256, 1024, 4096, 4),     # 8 tiles of 16 chunks on 128 CTAs: every tile is shared by 16 CTAs
+    (300, 2000, 2048, 4),     # ragged M and N, 32 tiles of 8 chunks: seams inside most tiles
+    (520, 1280, 1024, 8),     # uint8 weights (two k-blocks per chunk)
+    (64, 128, 320, 4),        # K / 64 = 5: the tile's last chunk holds one k-block, which only one group converts
+    (96, 256, 192, 8),        # the same for uint8: three k-blocks, two per chunk
+    (40, 128, 64, 4),         # a single k-block
+])
+def test_shared_tiles(M, N, K, bits):
+    rng = np.random.Generator(np.random.PCG64(41 + M))
+    x = synth.make_x(rng, M, K, np.float16)
+    w = synth.make_weights(rng, N, K, bits, 64 if K % 128 else 128)
+    _check(gpu_linear(x, w, kernel=L.KERNEL_GEMM), oracle_linear(x, w), TOL_F16, tight=2e-3)
+
+
+def test_shared_tiles_silu_mul_and_bias():
+    rng = np.random.Generator(np.random.PCG64(42))
+    M, N, K = 200, 1100, 2048
+    x = synth.make_x(rng, M, K, np.float16)
+    wg = synth.make_weights(rng, N, K, 4, 128)
+    wu = synth.make_weights(rng, N, K, 4, 128)
+    _check(gpu_linear(x, wg, wu, kernel=L.KERNEL_GEMM), oracle_linear(x, wg, wu), TOL_F16, tight=3e-3)
+    bias = rng.standard_normal(N).astype(np.float32)
+    _check(gpu_linear(x, wg, bias=bias, kernel=L.KERNEL_GEMM), oracle_linear(x, wg, bias=bias), TOL_F16, tight=2e-3)
+
+
+def test_repeated_calls_share_one_workspace_and_agree_bitwise():
+    """The arrival counters are left zeroed by every launch, and the order in which shared tiles are added does not
+    depend on which CTA arrives last: the same call twice on one workspace gives the same bits."""
+    import torch
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+    x, w = synth.u4g128(43, 256, 1024, 4096)
+    op = DequantDot(DeviceWeight.from_host(w), kernel=L.KERNEL_GEMM)
+    tx = torch.from_numpy(x).cuda()
+    y0 = op(tx).clone()
+    for _ in range(5):
+        y1 = op(tx)
+        assert torch.equal(y0, y1)
+    op.ctx.device_status()
