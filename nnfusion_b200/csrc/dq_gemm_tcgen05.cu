@@ -7,23 +7,26 @@
 // elementwise_fused.cpp:42-189) followed by cublasHgemm / cublasSgemm behind cuda::Dot
 // (src/nnfusion/core/kernels/cuda_gpu/kernels/dot.cpp:103-125,264-363).
 //
-// The CTA computes a transposed output tile  D[128 weight rows, BX batch rows] = Wdq[128, K] . X[BX, K]^T  so
+// A tile of the output is computed transposed,  D[128 weight rows, 256 batch rows] = Wdq[128, K] . X[256, K]^T,  so
 // that the dequantised weights are the MMA's A operand and can be handed to the tensor core through TENSOR MEMORY
-// instead of shared memory:
-//   * warps "TMA" : one thread streams x tiles (BX rows x 64 fp16, 128-byte swizzle, the MMA's B operand), another
+// instead of shared memory.  One persistent CTA per SM; the launch's work, tiles x raw chunks of K, is cut into equal
+// shares, so that a tile at a seam is computed by two or more CTAs: each writes its fp32 partial sums to a slot of the
+// workspace, and the one that arrives last at the tile adds the slots in the order of their K ranges (bitwise
+// repeatable) and runs the epilogue.  Roles inside a CTA:
+//   * warps "TMA" : one thread streams x tiles (256 rows x 64 fp16, 128-byte swizzle, the MMA's B operand), another
 //                   raw packed-weight chunks (128 rows x 128 bytes, 128-byte swizzle), into shared-memory rings;
 //   * warps "DQ"  : thread r owns weight row r of the tile = TMEM lane r.  Per 64-element k-block it reads its 32
 //                   (uint4) or 64 (uint8) bytes from the raw ring, turns them into fp16 (q - zp) * scale with the
 //                   exponent trick (PRMT + LOP3 + HSUB2 + HMUL2 per pair, exact integer before the scale), and
-//                   writes the 32 packed registers into the A stage in TMEM with tcgen05.st.  Two groups of four
-//                   warps alternate k-blocks so that the conversion keeps ahead of the tensor core;
+//                   writes the 32 packed registers into the A stage in TMEM with tcgen05.st.  Four groups of four
+//                   warps take the k-blocks in turn, so that the conversion keeps ahead of the tensor core;
 //   * warp "MMA"  : one thread issues tcgen05.mma.kind::f16 (A from TMEM, B from the shared-memory descriptor,
-//                   fp32 accumulator D in TMEM, 128 x BX x 16 per instruction) and releases stages with
+//                   fp32 accumulator D in TMEM, 128 x 256 x 16 per instruction) and releases stages with
 //                   tcgen05.commit;
-//   * epilogue    : the DQ warps read D with tcgen05.ld, apply bias or SiLU(gate) * up, convert and store y.
-// With the SiLU * mul epilogue the CTA carries two weight sets (gate, up), two accumulators of 128 columns each
-// and BX = 128.  Every mbarrier wait is bounded; on a time-out the CTA raises a status flag, skips its remaining
-// work, and still frees its tensor memory.
+//   * epilogue    : the DQ warps read D with tcgen05.ld, apply bias / addend / SiLU(gate) * up, convert and store y.
+// SiLU(x . Wg^T) * (x . Wu^T) runs as two launches: the first leaves the gate products in y, the second multiplies
+// SiLU of what it finds in y into its own products.  Every mbarrier wait is bounded; on a time-out the CTA raises a
+// status flag, skips its remaining work, and still frees its tensor memory.
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -35,42 +38,39 @@ namespace
 {
 using namespace nnf::ptx;
 
-template <int WBITS, bool DUAL>
+template <int WBITS>
 struct Cfg
 {
-    static constexpr int SETS = DUAL ? 2 : 1;
-    static constexpr int BN = 128;              // weight rows per CTA  (UMMA M, TMEM lanes)
-    static constexpr int BX = DUAL ? 128 : 256; // batch rows per CTA   (UMMA N, accumulator columns per set)
+    static constexpr int BN = 128;              // weight rows per tile  (UMMA M, TMEM lanes)
+    static constexpr int BX = 256;              // batch rows per tile   (UMMA N, accumulator columns)
     static constexpr int BK = 64;               // k-block: one 128-byte swizzle row of fp16
     // One ring index for the x tile in shared memory and the converted weights in tensor memory: the MMA thread
     // then has a single barrier to wait for and a single one to release per k-block.
-    static constexpr int STAGES = DUAL ? 4 : 5;
-    static constexpr int XSTAGES = STAGES;
+    static constexpr int STAGES = 5;
     static constexpr int WSTAGES = 3;
-    static constexpr int ASTAGES = STAGES;
     static constexpr int KB_PER_CHUNK = (WBITS == 4) ? 4 : 2; // k-blocks per 128-byte raw chunk
     static constexpr int RAW_BYTES = (WBITS == 4) ? 32 : 64;  // raw bytes per row and k-block
-    static constexpr int DQ_GROUPS = DUAL ? 2 : 4;            // groups of 4 warps that take the k-blocks in turn
-    static constexpr int DQ_WARPS = 4 * DQ_GROUPS * SETS;
+    static constexpr int DQ_GROUPS = 4;                       // groups of 4 warps that take the k-blocks in turn
+    static constexpr int DQ_WARPS = 4 * DQ_GROUPS;
     static constexpr int THREADS = (DQ_WARPS + 3) * 32;
     static constexpr int X_STAGE_BYTES = BX * 128;
     static constexpr int W_STAGE_BYTES = BN * 128;
-    static constexpr int A_COL0 = SETS * BX;     // first TMEM column of the A stages
+    static constexpr int A_COL0 = BX;            // first TMEM column of the A stages
     static constexpr int A_STAGE_COLS = BK / 2;  // 64 fp16 per lane = 32 columns
     static constexpr int TMEM_COLS = 512;
-    // full / empty per ring stage, full / empty per raw-weight stage and set, then: accumulator full, accumulator
-    // drained, partial sums written, ticket known
-    static constexpr int NUM_BARRIERS = 2 * STAGES + 2 * SETS * WSTAGES + 4;
+    // full / empty per ring stage, full / empty per raw-weight stage, then: accumulator full, accumulator drained,
+    // partial sums written, ticket known
+    static constexpr int NUM_BARRIERS = 2 * STAGES + 2 * WSTAGES + 4;
     static constexpr size_t SMEM_BYTES =
-        1024 + (size_t)XSTAGES * X_STAGE_BYTES + (size_t)SETS * WSTAGES * W_STAGE_BYTES + NUM_BARRIERS * 8 + 64;
-    static constexpr int SLOT_FLOATS = SETS * BX * BN; // one tile's accumulators as fp32: a partial sum in the workspace
-    static_assert(A_COL0 + SETS * ASTAGES * A_STAGE_COLS <= TMEM_COLS, "tensor memory budget");
+        1024 + (size_t)STAGES * X_STAGE_BYTES + (size_t)WSTAGES * W_STAGE_BYTES + NUM_BARRIERS * 8 + 64;
+    static constexpr int SLOT_FLOATS = BX * BN; // one tile's accumulator as fp32: a partial sum in the workspace
+    static_assert(A_COL0 + STAGES * A_STAGE_COLS <= TMEM_COLS, "tensor memory budget");
 };
 
 struct GemmParams
 {
-    const void* scale[2];
-    const uint8_t* zp[2];
+    const void* scale;
+    const uint8_t* zp;
     const float* bias;
     void* y;
     int* status;
@@ -82,6 +82,7 @@ struct GemmParams
     int has_addend; // bias points at an [M,N] tensor of y's type instead of fp32 [N]
     int m_tiles;    // batch tiles; tile t covers batch tile t % m_tiles of weight-row tile t / m_tiles
     int tiles;      // output tiles in all
+    int whole_tiles; // every tile is computed by one CTA (no partial sums)
     int kbpg_shift; // log2(group_size / 64) if that is a power of two, else -1
     int cpt;        // raw chunks (the unit of work) per tile: ceil(K / 64 / KB_PER_CHUNK)
 };
@@ -101,14 +102,6 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     }
     *abort_flag = 1;
     return false;
-}
-
-// For whole warps (the conversion warps): every lane waits, and the warp agrees on the outcome, so that the lanes stay
-// together for the warp-level hand-offs that follow.
-__device__ __forceinline__ bool warp_wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag)
-{
-    const bool ok = wait_or_abort(bar, parity, abort_flag);
-    return __all_sync(0xffffffffu, ok);
 }
 
 // Same for the thread that issues the MMAs: it is the kernel's critical path, so it polls without backing off.
@@ -132,7 +125,7 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t smem_addr)
            (2ull << 61);
 }
 
-// The CTA's share of the launch: units [u_begin, u_end) of tiles * cpt raw chunks, walked as segments that each lie
+// The CTA's share of the launch: units [u, u_end) of tiles * cpt raw chunks, walked as segments that each lie
 // inside one tile.  Every role of the CTA walks the same list.
 struct Segment
 {
@@ -148,9 +141,11 @@ struct WorkList
     int u, u_end; // tiles * cpt fits 31 bits (checked on the host)
     __device__ WorkList(const GemmParams& p)
     {
-        const long long U = (long long)p.tiles * p.cpt;
-        u = (int)((long long)blockIdx.x * U / gridDim.x);
-        u_end = (int)((long long)(blockIdx.x + 1) * U / gridDim.x);
+        // whole tiles only: the shares are cut at tile boundaries
+        const long long U = p.whole_tiles ? (long long)p.tiles : (long long)p.tiles * p.cpt;
+        const int scale = p.whole_tiles ? p.cpt : 1;
+        u = (int)((long long)blockIdx.x * U / gridDim.x) * scale;
+        u_end = (int)((long long)(blockIdx.x + 1) * U / gridDim.x) * scale;
     }
     __device__ bool next(const GemmParams& p, Segment& s)
     {
@@ -181,29 +176,57 @@ __device__ __forceinline__ int slot_of(int c, int t, long long U, int G, int cpt
     return 2 * c + (t == first_tile ? 0 : 1);
 }
 
-template <int WBITS, bool DUAL>
-__global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
-    dq_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x,
-                   const __grid_constant__ CUtensorMap tmap_w0, const __grid_constant__ CUtensorMap tmap_w1)
+// One finished value on its way to y: SiLU(gate) * v when a gate value is given, bias of the weight row (0 without),
+// full-size addend, conversion.
+__device__ __forceinline__ void store_value(const GemmParams& p, int m, int n, float v, bool gated, float g, float bias)
 {
-    using C = Cfg<WBITS, DUAL>;
-    constexpr int SETS = C::SETS;
+    const size_t at = (size_t)m * p.N + n;
+    if (gated)
+        v *= __fdividef(g, 1.0f + __expf(-g)); // SiLU(g) = g / (1 + e^-g); both intrinsics are good to ~1e-6 relative
+    v += bias;
+    if (p.has_addend)
+        v += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[at]
+                     : __half2float(reinterpret_cast<const __half*>(p.bias)[at]);
+    if (p.y_f32)
+        static_cast<float*>(p.y)[at] = v;
+    else
+        static_cast<__half*>(p.y)[at] = __float2half_rn(v);
+}
+
+// The gate product that an earlier launch left at y[m, n], as raw bits (fp32, or fp16 in the low half).
+__device__ __forceinline__ uint32_t gate_bits(const GemmParams& p, int m, int n)
+{
+    const size_t at = (size_t)m * p.N + n;
+    return p.y_f32 ? static_cast<const uint32_t*>(p.y)[at] : (uint32_t)static_cast<const unsigned short*>(p.y)[at];
+}
+__device__ __forceinline__ float gate_value(const GemmParams& p, uint32_t bits)
+{
+    return p.y_f32 ? __uint_as_float(bits) : __half2float(__ushort_as_half((unsigned short)bits));
+}
+
+// GATED: y holds the gate products of an earlier launch (the second half of SiLU(gate) * up).
+template <int WBITS, bool GATED>
+__global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
+    dq_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x,
+                   const __grid_constant__ CUtensorMap tmap_w)
+{
+    using C = Cfg<WBITS>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* xs = base;                                             // [XSTAGES][BX][128 B]
-    uint8_t* wsm = xs + (size_t)C::XSTAGES * C::X_STAGE_BYTES;      // [SETS][WSTAGES][128][128 B]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(wsm + (size_t)SETS * C::WSTAGES * C::W_STAGE_BYTES);
+    uint8_t* xs = base;                                             // [STAGES][BX][128 B]
+    uint8_t* wsm = xs + (size_t)C::STAGES * C::X_STAGE_BYTES;       // [WSTAGES][128][128 B]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(wsm + (size_t)C::WSTAGES * C::W_STAGE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::NUM_BARRIERS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile uint32_t* ticket_slot = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
 
     const uint32_t bar0 = smem_u32(bars);
     // full(s): the x tile has landed (TMA transaction bytes) and every conversion thread has stored its row of
-    // the stage (SETS * 128 arrivals); empty(s): the MMAs that read the stage have completed (tcgen05.commit).
+    // the stage (128 arrivals); empty(s): the MMAs that read the stage have completed (tcgen05.commit).
     auto full = [&](int s) { return bar0 + 8u * s; };
     auto empty = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
-    auto full_w = [&](int set, int s) { return bar0 + 8u * (2 * C::STAGES + set * C::WSTAGES + s); };
-    auto empty_w = [&](int set, int s) { return bar0 + 8u * (2 * C::STAGES + SETS * C::WSTAGES + set * C::WSTAGES + s); };
+    auto full_w = [&](int s) { return bar0 + 8u * (2 * C::STAGES + s); };
+    auto empty_w = [&](int s) { return bar0 + 8u * (2 * C::STAGES + C::WSTAGES + s); };
     const uint32_t acc_full = bar0 + 8u * (C::NUM_BARRIERS - 4);     // a segment's MMAs have completed
     const uint32_t acc_empty = bar0 + 8u * (C::NUM_BARRIERS - 3);    // every conversion thread has read its part of D
     const uint32_t part_done = bar0 + 8u * (C::NUM_BARRIERS - 2);    // every conversion thread has written its partial sums
@@ -218,15 +241,14 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     {
         for (int s = 0; s < C::STAGES; s++)
         {
-            mbar_init(full(s), SETS * 128 + 1); // every conversion thread's row and the x tile
+            mbar_init(full(s), 128 + 1); // every row of the stage and the x tile
             mbar_init(empty(s), 1);
         }
-        for (int set = 0; set < SETS; set++)
-            for (int s = 0; s < C::WSTAGES; s++)
-            {
-                mbar_init(full_w(set, s), 1);
-                mbar_init(empty_w(set, s), C::KB_PER_CHUNK * 128); // 128 rows read per k-block of the chunk
-            }
+        for (int s = 0; s < C::WSTAGES; s++)
+        {
+            mbar_init(full_w(s), 1);
+            mbar_init(empty_w(s), C::KB_PER_CHUNK * 128); // 128 rows read per k-block of the chunk
+        }
         mbar_init(acc_full, 1);
         mbar_init(acc_empty, C::DQ_WARPS * 32);
         mbar_init(part_done, C::DQ_WARPS * 32);
@@ -258,8 +280,8 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 const int m0 = (sg.tile % p.m_tiles) * C::BX;
                 for (int kb = sg.kb0; kb < sg.kb1; kb++, it++)
                 {
-                    const int s = it % C::XSTAGES;
-                    const uint32_t ph = (it / C::XSTAGES) & 1u;
+                    const int s = it % C::STAGES;
+                    const uint32_t ph = (it / C::STAGES) & 1u;
                     ok = wait_or_abort(empty(s), ph ^ 1u, abort_flag);
                     if (!ok)
                         break;
@@ -281,19 +303,15 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
             while (ok && work.next(p, sg))
             {
                 const int n0 = (sg.tile / p.m_tiles) * C::BN;
-                for (int chunk = sg.c0; chunk < sg.c1 && ok; chunk++, wc++)
+                for (int chunk = sg.c0; chunk < sg.c1; chunk++, wc++)
                 {
                     const int s = wc % C::WSTAGES;
                     const uint32_t ph = (wc / C::WSTAGES) & 1u;
-                    for (int set = 0; set < SETS && ok; set++)
-                    {
-                        ok = wait_or_abort(empty_w(set, s), ph ^ 1u, abort_flag);
-                        if (!ok)
-                            break;
-                        mbar_arrive_expect_tx(full_w(set, s), C::W_STAGE_BYTES);
-                        tma_load_2d(smem_u32(wsm + (size_t)(set * C::WSTAGES + s) * C::W_STAGE_BYTES),
-                                    set == 0 ? &tmap_w0 : &tmap_w1, full_w(set, s), chunk * 128, n0);
-                    }
+                    ok = wait_or_abort(empty_w(s), ph ^ 1u, abort_flag);
+                    if (!ok)
+                        break;
+                    mbar_arrive_expect_tx(full_w(s), C::W_STAGE_BYTES);
+                    tma_load_2d(smem_u32(wsm + (size_t)s * C::W_STAGE_BYTES), &tmap_w, full_w(s), chunk * 128, n0);
                 }
             }
         }
@@ -319,23 +337,18 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 }
                 for (int kb = sg.kb0; kb < sg.kb1; kb++, it++)
                 {
-                    const int sx = it % C::STAGES, sa = sx;
-                    ok = wait_hot(full(sx), (it / C::STAGES) & 1u, abort_flag);
+                    const int s = it % C::STAGES;
+                    ok = wait_hot(full(s), (it / C::STAGES) & 1u, abort_flag);
                     if (!ok)
                         break;
                     tcgen05_fence_after();
-                    const uint32_t xaddr = smem_u32(xs + (size_t)sx * C::X_STAGE_BYTES);
+                    const uint32_t xaddr = smem_u32(xs + (size_t)s * C::X_STAGE_BYTES);
+                    const uint32_t a_tmem = tmem_base + (uint32_t)(C::A_COL0 + s * C::A_STAGE_COLS);
 #pragma unroll
-                    for (int set = 0; set < SETS; set++)
-                    {
-                        const uint32_t d_tmem = tmem_base + (uint32_t)(set * C::BX);
-                        const uint32_t a_tmem = tmem_base + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS);
-#pragma unroll
-                        for (int kk = 0; kk < C::BK / 16; kk++)
-                            tcgen05_mma_ts(d_tmem, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
-                                           (kb != sg.kb0 || kk != 0) ? 1u : 0u);
-                    }
-                    tcgen05_commit(empty(sx)); // arrives when the MMAs above have consumed the stage
+                    for (int kk = 0; kk < C::BK / 16; kk++)
+                        tcgen05_mma_ts(tmem_base, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
+                                       (kb != sg.kb0 || kk != 0) ? 1u : 0u);
+                    tcgen05_commit(empty(s)); // arrives when the MMAs above have consumed the stage
                 }
                 if (ok)
                     tcgen05_commit(acc_full);
@@ -346,15 +359,12 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
     else
     {
         // ------------------------------------------------------------ dequantise into tensor memory
-        const int set = DUAL ? warp / (4 * C::DQ_GROUPS) : 0;
-        const int grp = (warp >> 2) % C::DQ_GROUPS;
+        const int grp = warp >> 2;                   // 0 .. DQ_GROUPS-1
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;           // row of the tile = TMEM lane
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
         const int kb_per_group = p.group / C::BK;
         const uint32_t wsm_s = smem_u32(wsm);
-        constexpr int PEERS = C::DQ_WARPS / 4;       // warps per TMEM lane quarter
-        const int peer = warp >> 2;                  // 0 .. PEERS-1
         bool ok = true;
         uint32_t it_base = 0; // k-blocks of this CTA before the segment in hand: ring position of its first one
         uint32_t wc_base = 0; // raw chunks likewise
@@ -377,10 +387,10 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
             q.g = p.kbpg_shift >= 0 ? (kbc >> p.kbpg_shift) : kbc / kb_per_group;
             const size_t i = (size_t)n * p.G + q.g;
             if (p.scale_f32)
-                q.s = __ldg(static_cast<const uint32_t*>(p.scale[set]) + i);
+                q.s = __ldg(static_cast<const uint32_t*>(p.scale) + i);
             else
-                q.s = __ldg(static_cast<const unsigned short*>(p.scale[set]) + i);
-            q.z = WBITS == 4 ? __ldg(p.zp[set] + (size_t)n * p.zp_row_bytes + (q.g >> 1)) : __ldg(p.zp[set] + i);
+                q.s = __ldg(static_cast<const unsigned short*>(p.scale) + i);
+            q.z = WBITS == 4 ? __ldg(p.zp + (size_t)n * p.zp_row_bytes + (q.g >> 1)) : __ldg(p.zp + i);
         };
         bool asked = false;
 
@@ -400,10 +410,10 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 const int chunk = kb / C::KB_PER_CHUNK, j = kb % C::KB_PER_CHUNK;
                 const uint32_t wci = wc_base + (uint32_t)(chunk - sg.c0);
                 const int sw = wci % C::WSTAGES;
-                if (!wait_or_abort(full_w(set, sw), (wci / C::WSTAGES) & 1u, abort_flag))
+                if (!wait_or_abort(full_w(sw), (wci / C::WSTAGES) & 1u, abort_flag))
                     return false;
                 // this row's raw bytes: 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
-                const uint32_t row = wsm_s + (uint32_t)((set * C::WSTAGES + sw) * C::W_STAGE_BYTES + r * 128);
+                const uint32_t row = wsm_s + (uint32_t)(sw * C::W_STAGE_BYTES + r * 128);
                 constexpr int NV = C::RAW_BYTES / 16;
                 uint4 raw[NV];
 #pragma unroll
@@ -411,7 +421,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                     raw[v] = lds128(row + (uint32_t)(((j * NV + v) ^ (r & 7)) * 16));
                 // One arrival per k-block read; the tile's last k-block also stands in for the k-blocks that a
                 // short last chunk does not have.
-                mbar_arrive_n(empty_w(set, sw), kb == KB - 1 ? (uint32_t)(C::KB_PER_CHUNK - j) : 1u);
+                mbar_arrive_n(empty_w(sw), kb == KB - 1 ? (uint32_t)(C::KB_PER_CHUNK - j) : 1u);
 
                 const float sc = p.scale_f32 ? __uint_as_float(q.s) : __half2float(__ushort_as_half((unsigned short)q.s));
                 const uint32_t zq = WBITS == 4 ? (q.z >> (4 * (q.g & 1))) & 0xFu : q.z;
@@ -460,11 +470,11 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 }
                 // hand the converted k-block to the tensor core: wait for the A stage, store, publish
                 const uint32_t itv = it_base + (uint32_t)(kb - sg.kb0);
-                const int sa = itv % C::ASTAGES;
-                if (!wait_or_abort(empty(sa), ((itv / C::ASTAGES) & 1u) ^ 1u, abort_flag))
+                const int sa = itv % C::STAGES;
+                if (!wait_or_abort(empty(sa), ((itv / C::STAGES) & 1u) ^ 1u, abort_flag))
                     return false;
                 tcgen05_fence_after();
-                tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + (set * C::ASTAGES + sa) * C::A_STAGE_COLS), a);
+                tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + sa * C::A_STAGE_COLS), a);
                 tcgen05_wait_st();
                 tcgen05_fence_before();
                 mbar_arrive(full(sa));
@@ -496,49 +506,66 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
             // D holds y transposed (lane = weight row n, column = batch row m): for one m the 32 lanes of a warp
             // hold 32 consecutive n.  A tile computed by this CTA alone goes through the epilogue to y; a shared
             // tile's accumulator goes to this CTA's slot in the workspace as fp32, and the CTA that arrives last
-            // at the tile adds the slots in the order of the K ranges and writes y.
+            // at the tile adds the slots in the order of their K ranges and writes y.  Each warp reads its two
+            // 32-column pieces of D with both loads in flight, then lets the MMA thread have the accumulator back.
+            const int n_base = (sg.tile / p.m_tiles) * C::BN, m0 = (sg.tile % p.m_tiles) * C::BX;
+            const int nrow = n_base + r;
+            static_assert(C::BX / 32 == 2 * C::DQ_GROUPS, "two 32-column pieces per warp");
+            const int col0 = grp * 32, col1 = (grp + C::DQ_GROUPS) * 32;
+            // With the gate products in y, those of the first piece are asked for before the accumulator is ready.
+            const float bias = (p.has_bias && nrow < p.N) ? __ldg(p.bias + nrow) : 0.f;
+            const bool gated = GATED && sg.whole;
+            uint32_t gb[GATED ? 32 : 1] = {};
+            // (rows and columns past the edge read the last valid ones: plain loads whose results nothing touches
+            // until the values are needed)
+            auto ask_gates = [&](int col) {
+                if (GATED && gated)
+                {
+                    const int nn = min(nrow, p.N - 1);
+                    if (p.y_f32)
+                    {
+#pragma unroll
+                        for (int jx = 0; jx < (GATED ? 32 : 1); jx++)
+                            gb[jx] = static_cast<const uint32_t*>(p.y)[(size_t)min(m0 + col + jx, p.M - 1) * p.N + nn];
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int jx = 0; jx < (GATED ? 32 : 1); jx++)
+                            gb[jx] = static_cast<const unsigned short*>(p.y)[(size_t)min(m0 + col + jx, p.M - 1) * p.N + nn];
+                    }
+                }
+            };
+            ask_gates(col0);
             if (ok)
                 ok = wait_or_abort(acc_full, si & 1u, abort_flag);
             si++;
             if (!ok)
                 break;
             tcgen05_fence_after();
-            const int nrow = (sg.tile / p.m_tiles) * C::BN + r, m0 = (sg.tile % p.m_tiles) * C::BX;
-            const float bias = (p.has_bias && nrow < p.N) ? __ldg(p.bias + nrow) : 0.f;
-            auto emit = [&](int ml, float v, float u) {
-                const int m = m0 + ml;
-                if (DUAL)
-                    v = v * (1.0f / (1.0f + expf(-v))) * u;
-                v += bias;
-                if (m < p.M && nrow < p.N)
-                {
-                    const size_t at = (size_t)m * p.N + nrow;
-                    if (p.has_addend)
-                        v += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[at]
-                                     : __half2float(reinterpret_cast<const __half*>(p.bias)[at]);
-                    if (p.y_f32)
-                        static_cast<float*>(p.y)[at] = v;
-                    else
-                        static_cast<__half*>(p.y)[at] = __float2half_rn(v);
-                }
-            };
             if (sg.whole)
             {
-                for (int cb = peer; cb < C::BX / 32; cb += PEERS)
+                uint32_t d[32];
+                tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col0, d);
+                tcgen05_wait_ld();
+                if (nrow < p.N)
                 {
-                    uint32_t d0[32], d1[32];
-                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(cb * 32), d0);
-                    if (DUAL)
-                        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::BX + cb * 32), d1);
-                    tcgen05_wait_ld();
-                    if (cb + PEERS >= C::BX / 32)
-                    {
-                        tcgen05_fence_before();
-                        mbar_arrive(acc_empty); // this thread's last read of D: the next segment may overwrite it
-                    }
 #pragma unroll
                     for (int jx = 0; jx < 32; jx++)
-                        emit(cb * 32 + jx, __uint_as_float(d0[jx]), DUAL ? __uint_as_float(d1[jx]) : 0.f);
+                        if (m0 + col0 + jx < p.M)
+                            store_value(p, m0 + col0 + jx, nrow, __uint_as_float(d[jx]), gated, gate_value(p, gb[GATED ? jx : 0]), bias);
+                }
+                ask_gates(col1);
+                tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col1, d);
+                tcgen05_wait_ld();
+                tcgen05_fence_before();
+                mbar_arrive(acc_empty); // this thread's last read of D: the next segment may overwrite it
+                if (nrow < p.N)
+                {
+#pragma unroll
+                    for (int jx = 0; jx < 32; jx++)
+                        if (m0 + col1 + jx < p.M)
+                            store_value(p, m0 + col1 + jx, nrow, __uint_as_float(d[jx]), gated, gate_value(p, gb[GATED ? jx : 0]), bias);
                 }
             }
             else
@@ -549,26 +576,20 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 const int c_last = cta_of_unit((long long)(sg.tile + 1) * p.cpt - 1, U, G);
                 const uint32_t pieces = (uint32_t)(c_last - c_first + 1);
                 float* mine = p.slots + (size_t)slot_of((int)blockIdx.x, sg.tile, U, G, p.cpt) * C::SLOT_FLOATS;
-                for (int cb = peer; cb < C::BX / 32; cb += PEERS)
                 {
-                    uint32_t d0[32], d1[32];
-                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(cb * 32), d0);
-                    if (DUAL)
-                        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(C::BX + cb * 32), d1);
+                    uint32_t d[32];
+                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col0, d);
                     tcgen05_wait_ld();
-                    if (cb + PEERS >= C::BX / 32)
-                    {
-                        tcgen05_fence_before();
-                        mbar_arrive(acc_empty);
-                    }
 #pragma unroll
                     for (int jx = 0; jx < 32; jx++)
-                    {
-                        const int ml = cb * 32 + jx;
-                        mine[(size_t)ml * C::BN + r] = __uint_as_float(d0[jx]);
-                        if (DUAL)
-                            mine[(size_t)(C::BX + ml) * C::BN + r] = __uint_as_float(d1[jx]);
-                    }
+                        mine[(size_t)(col0 + jx) * C::BN + r] = __uint_as_float(d[jx]);
+                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col1, d);
+                    tcgen05_wait_ld();
+                    tcgen05_fence_before();
+                    mbar_arrive(acc_empty);
+#pragma unroll
+                    for (int jx = 0; jx < 32; jx++)
+                        mine[(size_t)(col1 + jx) * C::BN + r] = __uint_as_float(d[jx]);
                 }
                 __threadfence();
                 mbar_arrive(part_done);
@@ -576,7 +597,7 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 {
                     // The whole warp waits (a lane spinning on its own while its warp-mates spin on another barrier
                     // starves), then one lane takes the ticket.
-                    const bool landed = warp_wait_or_abort(part_done, npart & 1u, abort_flag);
+                    const bool landed = __all_sync(0xffffffffu, wait_or_abort(part_done, npart & 1u, abort_flag));
                     if (lane == 0 && landed)
                     {
                         __threadfence(); // the partial sums of all threads before the ticket
@@ -597,20 +618,20 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                 {
                     // Last to arrive: add the tile's slots in the order of their K ranges and write y.  Nothing ties
                     // a thread to a tensor-memory lane here, so every thread takes four neighbouring weight rows of
-                    // one batch row at a time (16-byte loads), four such pieces and two slots per round trip.
+                    // one batch row at a time (16-byte loads), four such positions and two slots per round trip
+                    // to L2.
                     __threadfence();
                     constexpr int NT = C::DQ_WARPS * 32;        // threads at work
-                    constexpr int Q = C::BX * C::BN / 4;        // float4 per weight set in a slot
-                    static_assert(Q % (NT * 4) == 0, "four pieces per thread and pass");
-                    const int n_base = (sg.tile / p.m_tiles) * C::BN;
-                    const bool vec = (p.N % 4 == 0) && !p.has_addend &&
+                    constexpr int Q = C::SLOT_FLOATS / 4;       // float4 per slot
+                    static_assert(Q % (NT * 4) == 0, "four positions per thread and pass");
+                    const bool vec = (p.N % 4 == 0) && !p.has_addend && !GATED &&
                                      (reinterpret_cast<uintptr_t>(p.y) & 15u) == 0;
                     for (int q0 = warp * 32 + lane; q0 < Q; q0 += NT * 4)
                     {
-                        float4 v[4], u[4];
+                        float4 v[4];
 #pragma unroll
                         for (int j = 0; j < 4; j++)
-                            v[j] = make_float4(0.f, 0.f, 0.f, 0.f), u[j] = v[j];
+                            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                         for (int c = c_first; c <= c_last; c += 2) // fixed order: repeatable
                         {
                             const bool two = c + 1 <= c_last;
@@ -618,17 +639,12 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                                 p.slots + (size_t)slot_of(c, sg.tile, U, G, p.cpt) * C::SLOT_FLOATS);
                             const float4* s1 = reinterpret_cast<const float4*>(
                                 p.slots + (size_t)slot_of(two ? c + 1 : c, sg.tile, U, G, p.cpt) * C::SLOT_FLOATS);
-                            float4 a0[4], a1[4], b0[4], b1[4];
+                            float4 a0[4], a1[4];
 #pragma unroll
                             for (int j = 0; j < 4; j++)
                             {
                                 a0[j] = __ldcg(s0 + q0 + j * NT);
                                 a1[j] = __ldcg(s1 + q0 + j * NT);
-                                if (DUAL)
-                                {
-                                    b0[j] = __ldcg(s0 + Q + q0 + j * NT);
-                                    b1[j] = __ldcg(s1 + Q + q0 + j * NT);
-                                }
                             }
 #pragma unroll
                             for (int j = 0; j < 4; j++)
@@ -636,37 +652,24 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
                                 v[j].x += a0[j].x, v[j].y += a0[j].y, v[j].z += a0[j].z, v[j].w += a0[j].w;
                                 if (two)
                                     v[j].x += a1[j].x, v[j].y += a1[j].y, v[j].z += a1[j].z, v[j].w += a1[j].w;
-                                if (DUAL)
-                                {
-                                    u[j].x += b0[j].x, u[j].y += b0[j].y, u[j].z += b0[j].z, u[j].w += b0[j].w;
-                                    if (two)
-                                        u[j].x += b1[j].x, u[j].y += b1[j].y, u[j].z += b1[j].z, u[j].w += b1[j].w;
-                                }
                             }
                         }
 #pragma unroll
                         for (int j = 0; j < 4; j++)
                         {
-                            const int f = (q0 + j * NT) * 4;    // float index inside the set: [batch row][weight row]
-                            const int ml = f / C::BN, nl = f % C::BN;
-                            const int m = m0 + ml, n4 = n_base + nl;
-                            const float vv[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-                            const float uu[4] = {u[j].x, u[j].y, u[j].z, u[j].w};
-                            float o[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++)
-                            {
-                                float w = vv[e];
-                                if (DUAL)
-                                    w = w * (1.0f / (1.0f + expf(-w))) * uu[e];
-                                if (p.has_bias && n4 + e < p.N)
-                                    w += __ldg(p.bias + n4 + e);
-                                o[e] = w;
-                            }
+                            const int f = (q0 + j * NT) * 4;    // float index in the slot: [batch row][weight row]
+                            const int m = m0 + f / C::BN, n4 = n_base + f % C::BN;
                             if (m >= p.M)
                                 continue;
+                            float o[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
                             if (vec && n4 + 3 < p.N)
                             {
+                                if (p.has_bias)
+                                {
+#pragma unroll
+                                    for (int e = 0; e < 4; e++)
+                                        o[e] += __ldg(p.bias + n4 + e);
+                                }
                                 const size_t at = (size_t)m * p.N + n4;
                                 if (p.y_f32)
                                     *reinterpret_cast<float4*>(static_cast<float*>(p.y) + at) = make_float4(o[0], o[1], o[2], o[3]);
@@ -683,17 +686,9 @@ __global__ void __launch_bounds__(Cfg<WBITS, DUAL>::THREADS, 1)
 #pragma unroll
                                 for (int e = 0; e < 4; e++)
                                     if (n4 + e < p.N)
-                                    {
-                                        const size_t at = (size_t)m * p.N + n4 + e;
-                                        float w = o[e];
-                                        if (p.has_addend)
-                                            w += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[at]
-                                                         : __half2float(reinterpret_cast<const __half*>(p.bias)[at]);
-                                        if (p.y_f32)
-                                            static_cast<float*>(p.y)[at] = w;
-                                        else
-                                            static_cast<__half*>(p.y)[at] = __float2half_rn(w);
-                                    }
+                                        store_value(p, m, n4 + e, o[e], GATED,
+                                                    GATED ? gate_value(p, gate_bits(p, m, n4 + e)) : 0.f,
+                                                    p.has_bias ? __ldg(p.bias + n4 + e) : 0.f);
                             }
                         }
                     }
@@ -758,11 +753,10 @@ __global__ void __launch_bounds__(256) prep_activations_kernel(const void* x, co
     }
 }
 
-template <int WBITS, bool DUAL>
-cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap& tw0, const CUtensorMap& tw1,
-                   int grid, cudaStream_t stream)
+template <int WBITS, bool GATED>
+cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap& tw, int grid, cudaStream_t stream)
 {
-    using C = Cfg<WBITS, DUAL>;
+    using C = Cfg<WBITS>;
     static bool configured[nnf::kMaxDevices] = {}; // the attribute belongs to the device that is current
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -772,14 +766,14 @@ cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap
         return cudaErrorInvalidDevice;
     if (!configured[dev])
     {
-        e = cudaFuncSetAttribute(dq_gemm_kernel<WBITS, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(dq_gemm_kernel<WBITS, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)C::SMEM_BYTES);
         if (e != cudaSuccess)
             return e;
         configured[dev] = true;
     }
     (void)cudaGetLastError();
-    dq_gemm_kernel<WBITS, DUAL><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, tx, tw0, tw1);
+    dq_gemm_kernel<WBITS, GATED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, tx, tw);
     return cudaGetLastError();
 }
 } // namespace
@@ -801,7 +795,7 @@ static bool needs_prepass(const nnf_b200_linear_desc& d)
 // the arrival counters of the tiles, two partial-sum slots per CTA and, when needed, the fp16 copy of x.
 struct GemmLayout
 {
-    int bx, m_tiles, n_tiles, tiles, cpt, grid;
+    int bx, m_tiles, n_tiles, tiles, cpt, grid, whole_tiles;
     size_t counter_bytes, slot_bytes, prepass_bytes;
     size_t total() const { return counter_bytes + slot_bytes + prepass_bytes; }
 };
@@ -809,8 +803,7 @@ struct GemmLayout
 static GemmLayout gemm_layout(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d)
 {
     GemmLayout L{};
-    const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
-    L.bx = dual ? 128 : 256;
+    L.bx = 256;
     L.m_tiles = (d.M + L.bx - 1) / L.bx;
     L.n_tiles = (d.N + 127) / 128;
     L.tiles = L.m_tiles * L.n_tiles;
@@ -818,9 +811,19 @@ static GemmLayout gemm_layout(const nnf_b200_ctx* ctx, const nnf_b200_linear_des
     L.cpt = (d.K / 64 + kb_per_chunk - 1) / kb_per_chunk;
     const long long units = (long long)L.tiles * L.cpt;
     const int sms = ctx ? ctx->sm_count : 148;
-    L.grid = (int)(units < sms ? units : sms);
+    // Shares cut anywhere (tiles at the seams cost a partial sum in the workspace, a ticket and a final addition:
+    // about 30 k-blocks' worth of time on top of the 8 of an epilogue) or at tile boundaries only (the CTA with the
+    // most tiles sets the time): whichever the estimate, in k-block times, favours.
+    const double kb = d.K / 64.0;
+    const double t_split = (double)L.tiles * kb / sms + 8.0 + 30.0;
+    const double t_whole = (double)((L.tiles + sms - 1) / sms) * (kb + 8.0);
+    L.whole_tiles = t_whole <= t_split;
+    if (L.whole_tiles)
+        L.grid = L.tiles < sms ? L.tiles : sms;
+    else
+        L.grid = (int)(units < sms ? units : sms);
     L.counter_bytes = ((size_t)L.tiles * sizeof(uint32_t) + 255) / 256 * 256;
-    L.slot_bytes = (size_t)2 * L.grid * 128 * 256 * sizeof(float); // SETS * BX * BN is 128 * 256 in both variants
+    L.slot_bytes = (size_t)2 * L.grid * 128 * 256 * sizeof(float); // two slots of one fp32 tile per CTA
     L.prepass_bytes = needs_prepass(d) ? ((size_t)d.M * d.K * sizeof(__half) + 255) / 256 * 256 : 0;
     return L;
 }
@@ -873,18 +876,9 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
         ctx->launches++;
         x = xh;
     }
-    const bool dual = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
-    const int bx = L.bx;
+    const bool silu_mul = d.epilogue == NNF_B200_EPILOGUE_SILU_MUL;
     const int row_bytes = d.w_bits == 4 ? d.K / 2 : d.K;
     GemmParams p{};
-    p.scale[0] = w->scale;
-    p.zp[0] = static_cast<const uint8_t*>(w->zp);
-    if (dual)
-    {
-        p.scale[1] = w2->scale;
-        p.zp[1] = static_cast<const uint8_t*>(w2->zp);
-    }
-    p.bias = static_cast<const float*>(bias);
     p.y = y;
     p.status = ctx->dev_status;
     p.M = d.M, p.N = d.N, p.K = d.K;
@@ -893,11 +887,10 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     p.zp_row_bytes = d.w_bits == 4 ? (p.G + 1) / 2 : p.G;
     p.y_f32 = d.y_dtype == NNF_B200_F32;
     p.scale_f32 = d.scale_dtype == NNF_B200_F32;
-    p.has_addend = d.epilogue == NNF_B200_EPILOGUE_ADD;
-    p.has_bias = bias != nullptr && !p.has_addend;
     p.m_tiles = L.m_tiles;
     p.tiles = L.tiles;
     p.cpt = L.cpt;
+    p.whole_tiles = L.whole_tiles;
     p.kbpg_shift = -1;
     for (int sh = 0; sh < 31; sh++)
         if ((p.group / 64) == (1 << sh))
@@ -905,31 +898,36 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
     p.counters = reinterpret_cast<uint32_t*>(ws);
     p.slots = reinterpret_cast<float*>(ws + L.counter_bytes);
 
-    // x: fp16 [M][K], boxes of BX rows x 64 elements (the tensor map is not cached: x moves between calls)
+    // x: fp16 [M][K], boxes of 256 rows x 64 elements (the tensor map is not cached: x moves between calls)
     alignas(64) CUtensorMap tx;
     if (!encode_tensor_map_2d(ctx->encode_tiled, &tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, x, (uint64_t)d.K,
-                              (uint64_t)d.M, (uint64_t)d.K * 2, 64, (uint32_t)bx, CU_TENSOR_MAP_SWIZZLE_128B))
+                              (uint64_t)d.M, (uint64_t)d.K * 2, 64, (uint32_t)L.bx, CU_TENSOR_MAP_SWIZZLE_128B))
         return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the activations");
-    // copied by value at once: a later lookup may empty the context's cache
-    alignas(64) CUtensorMap tw0v, tw1v;
-    const CUtensorMap* tw0 = weight_tensor_map(ctx, w->wq, d.N, row_bytes, 128, 128);
-    if (tw0)
-        tw0v = *tw0;
-    const CUtensorMap* tw1 = dual ? weight_tensor_map(ctx, w2->wq, d.N, row_bytes, 128, 128) : tw0;
-    if (tw1)
-        tw1v = *tw1;
-    if (!tw0 || !tw1)
-        return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
 
-    const int grid = L.grid;
-    cudaError_t e;
-    if (d.w_bits == 4)
-        e = dual ? launch<4, true>(p, tx, tw0v, tw1v, grid, stream) : launch<4, false>(p, tx, tw0v, tw1v, grid, stream);
-    else
-        e = dual ? launch<8, true>(p, tx, tw0v, tw1v, grid, stream) : launch<8, false>(p, tx, tw0v, tw1v, grid, stream);
-    if (e != cudaSuccess)
-        return set_error(ctx, NNF_B200_ECUDA, std::string("dq_gemm launch: ") + cudaGetErrorString(e));
-    ctx->launches++;
+    // SiLU(x . Wg^T) * (x . Wu^T): the gate products go to y first, the second launch folds them in.
+    const int passes = silu_mul ? 2 : 1;
+    for (int pass = 0; pass < passes; pass++)
+    {
+        const nnf_b200_qweight* wp = (silu_mul && pass == 1) ? w2 : w;
+        p.scale = wp->scale;
+        p.zp = static_cast<const uint8_t*>(wp->zp);
+        p.has_addend = d.epilogue == NNF_B200_EPILOGUE_ADD;
+        p.has_bias = bias != nullptr && !p.has_addend && !silu_mul;
+        p.bias = static_cast<const float*>(bias);
+        // copied by value at once: a later lookup may empty the context's cache
+        alignas(64) CUtensorMap twv;
+        const CUtensorMap* tw = weight_tensor_map(ctx, wp->wq, d.N, row_bytes, 128, 128);
+        if (!tw)
+            return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
+        twv = *tw;
+        const bool gated = silu_mul && pass == 1;
+        const cudaError_t e = d.w_bits == 4
+                                  ? (gated ? launch<4, true>(p, tx, twv, L.grid, stream) : launch<4, false>(p, tx, twv, L.grid, stream))
+                                  : (gated ? launch<8, true>(p, tx, twv, L.grid, stream) : launch<8, false>(p, tx, twv, L.grid, stream));
+        if (e != cudaSuccess)
+            return set_error(ctx, NNF_B200_ECUDA, std::string("dq_gemm launch: ") + cudaGetErrorString(e));
+        ctx->launches++;
+    }
     return NNF_B200_OK;
 }
 } // namespace nnf
