@@ -44,10 +44,12 @@ struct Cfg
     static constexpr int BN = 128;              // weight rows per tile  (UMMA M, TMEM lanes)
     static constexpr int BX = 256;              // batch rows per tile   (UMMA N, accumulator columns)
     static constexpr int BK = 64;               // k-block: one 128-byte swizzle row of fp16
-    // One ring index for the x tile in shared memory and the converted weights in tensor memory: the MMA thread
-    // then has a single barrier to wait for and a single one to release per k-block.
-    static constexpr int STAGES = 5;
-    static constexpr int WSTAGES = 3;
+    // One ring index for the x tile in shared memory and the converted weights in tensor memory, and one pair of
+    // barriers for every PAIR of k-blocks: the MMA thread, whose own time per k-block is what bounds the kernel,
+    // then waits once and releases once per eight MMAs.
+    static constexpr int PAIRS = 3;             // ring depth in pairs of k-blocks
+    static constexpr int STAGES = 2 * PAIRS;    // k-block stages
+    static constexpr int WSTAGES = 2;
     static constexpr int KB_PER_CHUNK = (WBITS == 4) ? 4 : 2; // k-blocks per 128-byte raw chunk
     static constexpr int RAW_BYTES = (WBITS == 4) ? 32 : 64;  // raw bytes per row and k-block
     static constexpr int DQ_GROUPS = 4;                       // groups of 4 warps that take the k-blocks in turn
@@ -60,7 +62,7 @@ struct Cfg
     static constexpr int TMEM_COLS = 512;
     // full / empty per ring stage, full / empty per raw-weight stage, then: accumulator full, accumulator drained,
     // partial sums written, ticket known
-    static constexpr int NUM_BARRIERS = 2 * STAGES + 2 * WSTAGES + 4;
+    static constexpr int NUM_BARRIERS = 2 * PAIRS + 2 * WSTAGES + 4;
     static constexpr size_t SMEM_BYTES =
         1024 + (size_t)STAGES * X_STAGE_BYTES + (size_t)WSTAGES * W_STAGE_BYTES + NUM_BARRIERS * 8 + 64;
     static constexpr int SLOT_FLOATS = BX * BN; // one tile's accumulator as fp32: a partial sum in the workspace
@@ -221,12 +223,13 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
     volatile uint32_t* ticket_slot = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
 
     const uint32_t bar0 = smem_u32(bars);
-    // full(s): the x tile has landed (TMA transaction bytes) and every conversion thread has stored its row of
-    // the stage (128 arrivals); empty(s): the MMAs that read the stage have completed (tcgen05.commit).
-    auto full = [&](int s) { return bar0 + 8u * s; };
-    auto empty = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
-    auto full_w = [&](int s) { return bar0 + 8u * (2 * C::STAGES + s); };
-    auto empty_w = [&](int s) { return bar0 + 8u * (2 * C::STAGES + C::WSTAGES + s); };
+    // full(q): the x tiles of pair q have landed (TMA transaction bytes) and every conversion thread has stored its
+    // row of both stages (2 * 128 arrivals; where a segment ends on a single k-block, its threads arrive twice);
+    // empty(q): the MMAs that read the pair have completed (tcgen05.commit).
+    auto full = [&](int q) { return bar0 + 8u * q; };
+    auto empty = [&](int q) { return bar0 + 8u * (C::PAIRS + q); };
+    auto full_w = [&](int s) { return bar0 + 8u * (2 * C::PAIRS + s); };
+    auto empty_w = [&](int s) { return bar0 + 8u * (2 * C::PAIRS + C::WSTAGES + s); };
     const uint32_t acc_full = bar0 + 8u * (C::NUM_BARRIERS - 4);     // a segment's MMAs have completed
     const uint32_t acc_empty = bar0 + 8u * (C::NUM_BARRIERS - 3);    // every conversion thread has read its part of D
     const uint32_t part_done = bar0 + 8u * (C::NUM_BARRIERS - 2);    // every conversion thread has written its partial sums
@@ -239,10 +242,10 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
     // ---------------------------------------------------------------- set-up (once per CTA)
     if (tid == 0)
     {
-        for (int s = 0; s < C::STAGES; s++)
+        for (int q = 0; q < C::PAIRS; q++)
         {
-            mbar_init(full(s), 128 + 1); // every row of the stage and the x tile
-            mbar_init(empty(s), 1);
+            mbar_init(full(q), 2 * 128 + 1); // every row of both stages and the x tiles
+            mbar_init(empty(q), 1);
         }
         for (int s = 0; s < C::WSTAGES; s++)
         {
@@ -274,19 +277,22 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
         if (lane == 0)
         {
             bool ok = true;
-            uint32_t it = 0; // k-blocks of this CTA so far: ring position
+            uint32_t pr = 0; // pairs of k-blocks of this CTA so far: ring position (every segment starts a pair)
             while (ok && work.next(p, sg))
             {
                 const int m0 = (sg.tile % p.m_tiles) * C::BX;
-                for (int kb = sg.kb0; kb < sg.kb1; kb++, it++)
+                for (int kb = sg.kb0; kb < sg.kb1; kb += 2, pr++)
                 {
-                    const int s = it % C::STAGES;
-                    const uint32_t ph = (it / C::STAGES) & 1u;
-                    ok = wait_or_abort(empty(s), ph ^ 1u, abort_flag);
+                    const int q = pr % C::PAIRS;
+                    const uint32_t ph = (pr / C::PAIRS) & 1u;
+                    ok = wait_or_abort(empty(q), ph ^ 1u, abort_flag);
                     if (!ok)
                         break;
-                    mbar_arrive_expect_tx(full(s), C::X_STAGE_BYTES);
-                    tma_load_2d(smem_u32(xs + (size_t)s * C::X_STAGE_BYTES), &tmap_x, full(s), kb * C::BK, m0);
+                    const int nkb = min(2, sg.kb1 - kb);
+                    mbar_arrive_expect_tx(full(q), (uint32_t)(nkb * C::X_STAGE_BYTES));
+                    for (int h = 0; h < nkb; h++)
+                        tma_load_2d(smem_u32(xs + (size_t)(2 * q + h) * C::X_STAGE_BYTES), &tmap_x, full(q),
+                                    (kb + h) * C::BK, m0);
                 }
             }
         }
@@ -324,7 +330,7 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
             // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = BX, M = 128
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(C::BX >> 3) << 17) | ((uint32_t)(C::BN >> 4) << 24);
             bool ok = true;
-            uint32_t it = 0, si = 0;
+            uint32_t pr = 0, si = 0;
             while (ok && work.next(p, sg))
             {
                 if (si > 0)
@@ -335,20 +341,25 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                         break;
                     tcgen05_fence_after();
                 }
-                for (int kb = sg.kb0; kb < sg.kb1; kb++, it++)
+                for (int kb = sg.kb0; kb < sg.kb1; kb += 2, pr++)
                 {
-                    const int s = it % C::STAGES;
-                    ok = wait_hot(full(s), (it / C::STAGES) & 1u, abort_flag);
+                    const int q = pr % C::PAIRS;
+                    ok = wait_hot(full(q), (pr / C::PAIRS) & 1u, abort_flag);
                     if (!ok)
                         break;
                     tcgen05_fence_after();
-                    const uint32_t xaddr = smem_u32(xs + (size_t)s * C::X_STAGE_BYTES);
-                    const uint32_t a_tmem = tmem_base + (uint32_t)(C::A_COL0 + s * C::A_STAGE_COLS);
+                    const int nkb = min(2, sg.kb1 - kb);
+                    for (int h = 0; h < nkb; h++)
+                    {
+                        const int s = 2 * q + h;
+                        const uint32_t xaddr = smem_u32(xs + (size_t)s * C::X_STAGE_BYTES);
+                        const uint32_t a_tmem = tmem_base + (uint32_t)(C::A_COL0 + s * C::A_STAGE_COLS);
 #pragma unroll
-                    for (int kk = 0; kk < C::BK / 16; kk++)
-                        tcgen05_mma_ts(tmem_base, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
-                                       (kb != sg.kb0 || kk != 0) ? 1u : 0u);
-                    tcgen05_commit(empty(s)); // arrives when the MMAs above have consumed the stage
+                        for (int kk = 0; kk < C::BK / 16; kk++)
+                            tcgen05_mma_ts(tmem_base, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
+                                           (kb + h != sg.kb0 || kk != 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty(q)); // arrives when the MMAs above have consumed the pair
                 }
                 if (ok)
                     tcgen05_commit(acc_full);
@@ -366,7 +377,7 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
         const int kb_per_group = p.group / C::BK;
         const uint32_t wsm_s = smem_u32(wsm);
         bool ok = true;
-        uint32_t it_base = 0; // k-blocks of this CTA before the segment in hand: ring position of its first one
+        uint32_t pr_base = 0; // pairs of k-blocks of this CTA before the segment in hand: ring position of its first
         uint32_t wc_base = 0; // raw chunks likewise
         uint32_t si = 0, npart = 0;
 
@@ -469,15 +480,17 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                     }
                 }
                 // hand the converted k-block to the tensor core: wait for the A stage, store, publish
-                const uint32_t itv = it_base + (uint32_t)(kb - sg.kb0);
-                const int sa = itv % C::STAGES;
-                if (!wait_or_abort(empty(sa), ((itv / C::STAGES) & 1u) ^ 1u, abort_flag))
+                const int rel = kb - sg.kb0;
+                const uint32_t prv = pr_base + (uint32_t)(rel >> 1);
+                const int pq = prv % C::PAIRS, sa = 2 * pq + (rel & 1);
+                if (!wait_or_abort(empty(pq), ((prv / C::PAIRS) & 1u) ^ 1u, abort_flag))
                     return false;
                 tcgen05_fence_after();
                 tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + sa * C::A_STAGE_COLS), a);
                 tcgen05_wait_st();
                 tcgen05_fence_before();
-                mbar_arrive(full(sa));
+                // a segment that ends on the first k-block of a pair: its threads also stand in for the second
+                mbar_arrive_n(full(pq), ((rel & 1) == 0 && kb == sg.kb1 - 1) ? 2u : 1u);
                 return true;
             };
             // The groups take the k-blocks in turn.  A group's warps sit on different schedulers next to the other
@@ -488,7 +501,7 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                 if (ok && kb + C::DQ_GROUPS < sg.kb1)
                     ok = one(kb + C::DQ_GROUPS, pb);
             }
-            it_base += (uint32_t)(sg.kb1 - sg.kb0);
+            pr_base += (uint32_t)((sg.kb1 - sg.kb0 + 1) >> 1);
             wc_base += (uint32_t)(sg.c1 - sg.c0);
             {
                 WorkList<C::KB_PER_CHUNK> ahead = work;
