@@ -62,10 +62,6 @@ __global__ void __launch_bounds__(kThreads, 4) decode_attention_kernel(const Att
     __shared__ float stat_s[2][4]; // per-warp maximum / sum
     __shared__ int last_s;
 
-    // The next launch on the stream may start as SMs become free; this one waits for the launch before it (which
-    // produced q, k, v; the cache rows it reads were written by earlier steps, but nothing is assumed about those).
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int half = lane >> 4, dg = lane & 15; // which of the warp's two rows, which 8 dimensions
     const int head = blockIdx.y, split = blockIdx.x;
@@ -73,6 +69,21 @@ __global__ void __launch_bounds__(kThreads, 4) decode_attention_kernel(const Att
     const int n_rows = p.position + 1;
     const int begin = split * p.chunk, end = min(begin + p.chunk, n_rows);
     const bool owns_new = begin <= p.position && p.position < end;
+    // Before anything else, and before the launch ahead of this one has finished: ask for the CTA's whole range of
+    // both caches to be brought into L2 (two bulk requests; a prefetch hands no values to anyone, so it may run
+    // ahead of the wait below).  HBM then streams from the first microsecond, and the register loads further down see
+    // L2 latency.
+    if (tid == 0 && end > begin)
+    {
+        const size_t first = ((size_t)kvh * p.capacity + begin) * kD;
+        const uint32_t bytes = (uint32_t)(end - begin) * kD * (uint32_t)sizeof(__half);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.k_cache + first), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v_cache + first), "r"(bytes) : "memory");
+    }
+    // The next launch on the stream may start as SMs become free; this one waits for the launch before it (which
+    // produced q, k, v; the cache rows it reads were written by earlier steps, but nothing is assumed about those).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- q first (a few bytes that everything waits for), then the first two passes of cache rows: nothing below
     // depends on those until the scores
