@@ -67,6 +67,8 @@ struct DirectParams
     int batch;       // row tiles between two reductions over the warps (<= kBatch)
     int tq;          // accumulator column pairs kept: 1, 2 or 4
     int bulk_params; // scales / zero-points of a batch arrive by bulk copy in shared memory
+    int range_params; // ... and only the columns of this CTA's K range (rows are whole 16-byte pieces)
+    int sc_row_bytes; // bytes of one row of scales
     int pmode;       // see the kernel's PMODE
     int scale_tile_bytes, zp_tile_bytes;
     int xfrag_bytes;    // shared memory per warp for the activation fragments of batch rows 8..15 (0 when M <= 8)
@@ -325,7 +327,42 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     // copy-engine request: the batch's data is complete once every thread has waited for its own groups and the CTA
     // has met at a barrier.
     auto copy_params = [&](int first, int count, int which) {
-        if (p.bulk_params && count > 0)
+        if (p.bulk_params && p.range_params && count > 0)
+        {
+            // K split over several CTAs: a CTA uses only the groups of its own slices.  Their bytes land where the
+            // whole rows would put them, so that nothing else changes; the other columns of the block stay unwritten.
+            // byte range of this CTA's groups inside a row of scales / of zero-points, widened to 16-byte pieces
+            // (worked out here, where it is needed, rather than kept in registers through the main loop)
+            const int e0 = slice0 * 2 * F::UE, e1 = min(p.K, (slice0 + my_slices) * 2 * F::UE); // a slice is two units
+            const int g0 = e0 / p.group, g1 = (e1 + p.group - 1) / p.group;
+            const int sb = p.scale_f32 ? 4 : 2;
+            const int sc_b0 = (g0 * sb) & ~15;
+            const int sc_pieces = (min(p.sc_row_bytes, (g1 * sb + 15) & ~15) - sc_b0) >> 4;
+            const int z0 = WBITS == 4 ? g0 >> 1 : g0, z1 = WBITS == 4 ? (g1 + 1) >> 1 : g1;
+            const int zp_b0 = z0 & ~15;
+            const int zp_pieces = (min(p.zp_row_bytes, (z1 + 15) & ~15) - zp_b0) >> 4;
+            const int rows = count * 16;
+            const int per_row = sc_pieces + zp_pieces;
+#pragma unroll
+            for (int s = 0; s < SETS; s++)
+            {
+                const uint32_t dst = pbuf_s + which * pbatch_bytes + s * (uint32_t)(p.batch * pset_bytes);
+                const size_t row0 = (size_t)(tile0 + first) * 16;
+                const char* sc_src = static_cast<const char*>(s == 0 ? p.scale[0] : p.scale[1]) + row0 * p.sc_row_bytes + sc_b0;
+                const uint8_t* zp_src = (s == 0 ? p.zp[0] : p.zp[1]) + row0 * p.zp_row_bytes + zp_b0;
+                for (int i = tid; i < rows * per_row; i += nthreads)
+                {
+                    const int row = i / per_row, c = i - row * per_row;
+                    if (c < sc_pieces)
+                        cp_async16(dst + (uint32_t)(row * p.sc_row_bytes + sc_b0 + c * 16),
+                                   sc_src + (size_t)row * p.sc_row_bytes + c * 16);
+                    else
+                        cp_async16(dst + pzp_off + (uint32_t)(row * p.zp_row_bytes + zp_b0 + (c - sc_pieces) * 16),
+                                   zp_src + (size_t)row * p.zp_row_bytes + (c - sc_pieces) * 16);
+                }
+            }
+        }
+        else if (p.bulk_params && count > 0)
         {
             const int nsc = (count * p.scale_tile_bytes) >> 4, nzp = (count * p.zp_tile_bytes) >> 4;
 #pragma unroll
@@ -1252,6 +1289,8 @@ cudaError_t gemv_direct_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& 
     }
     p.group_units = p.group / ue;
     p.group_magic = p.group_units > 1 ? (uint32_t)((0x100000000ull + p.group_units - 1) / p.group_units) : 0u;
+    p.sc_row_bytes = p.G * (p.scale_f32 ? 4 : 2);
+    p.range_params = p.bulk_params && plan.splits > 1 && p.sc_row_bytes % 16 == 0 && p.zp_row_bytes % 16 == 0;
     p.pmode = 0;
     if (p.bulk_params && d.w_bits == 4 && p.group == 128 && !p.scale_f32 && (p.G & 1) == 0)
         p.pmode = 1;

@@ -59,3 +59,22 @@ def test_pack_u4_host_helper(lib):
     bad = v.copy()
     bad[0, 0] = 16
     assert lib.nnf_b200_pack_u4(bad.tobytes(), 7, 33, out.ctypes.data_as(ctypes.c_char_p)) == L.EINVAL
+
+
+def test_workspace_sizes_without_a_device(lib):
+    """Sizing at code-generation time (no context: a 148-SM device is assumed).  Large M: the tiles' arrival counters,
+    two fp32 tile slots per persistent CTA, and the fp16 copy of the activations when there is a pre-pass."""
+    def need(M, N, K, x=L.F16, prologue=0):
+        d = L.LinearDesc(M=M, N=N, K=K, w_bits=4, group_size=128, x_dtype=x, y_dtype=x, scale_dtype=L.F16,
+                         prologue=prologue)
+        return int(lib.nnf_b200_linear_workspace_bytes(None, ctypes.byref(d)))
+    slots = 2 * 148 * 128 * 256 * 4
+    tiles = 16 * 86                                  # 4096 / 256 batch tiles x 11008 / 128 weight-row tiles
+    plain = need(4096, 11008, 4096)
+    assert plain == (tiles * 4 + 255) // 256 * 256 + slots
+    assert need(4096, 11008, 4096, x=L.F32) == plain + 4096 * 4096 * 2
+    assert need(4096, 11008, 4096, prologue=L.PROLOGUE_RMSNORM) == plain + 4096 * 4096 * 2
+    # a launch with fewer units of work than SMs uses fewer CTAs, hence fewer slots
+    assert need(32, 128, 256) == 256 + 2 * 1 * 128 * 256 * 4
+    # small M: split-K scratch only
+    assert need(1, 11008, 4096) < 1 << 20
