@@ -174,3 +174,67 @@ def test_repeated_calls_share_one_workspace_and_agree_bitwise():
         y1 = op(tx)
         assert torch.equal(y0, y1)
     op.ctx.device_status()
+
+
+def test_shared_tiles_odd_n_scalar_stores():
+    """N not a multiple of four: the CTA that adds a shared tile's slots stores element by element."""
+    rng = np.random.Generator(np.random.PCG64(44))
+    M, N, K = 300, 1001, 2048
+    x = synth.make_x(rng, M, K, np.float16)
+    w = synth.make_weights(rng, N, K, 4, 128)
+    _check(gpu_linear(x, w, kernel=L.KERNEL_GEMM), oracle_linear(x, w), TOL_F16, tight=2e-3)
+    _check(gpu_linear(x, w, kernel=L.KERNEL_GEMM, out_dtype=np.float32), oracle_linear(x, w, out_dtype=np.float32),
+           TOL_F16, tight=2e-3)
+
+
+@pytest.mark.parametrize("N", [1024, 1001])
+def test_shared_tiles_add_epilogue_in_place(N):
+    """The full-size addend (also when it is y itself) through whole and shared tiles."""
+    import torch
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+    rng = np.random.Generator(np.random.PCG64(45))
+    M, K = 270, 2048
+    x = synth.make_x(rng, M, K, np.float16)
+    w = synth.make_weights(rng, N, K, 4, 128)
+    c = rng.standard_normal((M, N)).astype(np.float16)
+    ref = (oracle_linear(x, w, out_dtype=np.float32).astype(np.float32) + c.astype(np.float32)).astype(np.float16)
+    op = DequantDot(DeviceWeight.from_host(w, "cuda:0"), add=True, kernel=L.KERNEL_GEMM)
+    tx, tc = torch.from_numpy(x).cuda(), torch.from_numpy(c).cuda()
+    y = op(tx, addend=tc)
+    torch.cuda.synchronize()
+    _check(y.cpu().numpy(), ref, TOL_F16, tight=2e-3)
+    y2 = op(tx, out=tc, addend=tc)           # in place
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(y2.cpu().numpy(), y.cpu().numpy())
+    op.ctx.device_status()
+
+
+def test_silu_mul_fp32_output_and_odd_n():
+    """SiLU(gate) * up as two launches that meet in y: fp32 y keeps the gate products in fp32; odd N takes the scalar
+    path of the CTA that adds a shared tile's slots."""
+    rng = np.random.Generator(np.random.PCG64(46))
+    M, N, K = 130, 1001, 2048
+    x = synth.make_x(rng, M, K, np.float16)
+    wg = synth.make_weights(rng, N, K, 4, 128)
+    wu = synth.make_weights(rng, N, K, 4, 128)
+    _check(gpu_linear(x, wg, wu, kernel=L.KERNEL_GEMM), oracle_linear(x, wg, wu), TOL_F16, tight=3e-3)
+    _check(gpu_linear(x, wg, wu, kernel=L.KERNEL_GEMM, out_dtype=np.float32),
+           oracle_linear(x, wg, wu, out_dtype=np.float32), TOL_F16, tight=3e-3)
+
+
+def test_output_padding_untouched_with_shared_tiles():
+    """NaN-filled guard rows around y stay NaN when tiles are shared and M, N are ragged."""
+    import torch
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+    x, w = synth.u4g128(47, 300, 1000, 2048)
+    op = DequantDot(DeviceWeight.from_host(w, "cuda:0"), kernel=L.KERNEL_GEMM)
+    tx = torch.from_numpy(x).cuda()
+    guard = 64
+    buf = torch.full((guard + 300 * 1000 + guard,), float("nan"), dtype=torch.float16, device="cuda")
+    y = buf[guard:guard + 300 * 1000].view(300, 1000)
+    op(tx, out=y)
+    torch.cuda.synchronize()
+    assert torch.isnan(buf[:guard]).all() and torch.isnan(buf[-guard:]).all()
+    assert not torch.isnan(y).any()
+    _check(y.cpu().numpy(), oracle_linear(x, w), TOL_F16, tight=2e-3)
+    op.ctx.device_status()
