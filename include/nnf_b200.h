@@ -301,12 +301,13 @@ NNF_B200_API int nnf_b200_allreduce_oneshot(nnf_b200_ctx* ctx, void* stream, int
  * y = sum over ranks r of x_r . dequant(W_r)^T (+ bias or addend, applied once, on the sum): the row-parallel
  * linear of a sharded layer and the all-reduce that follows it, as one kernel.  In the reference these are a Dot
  * kernel and cuda::SuperScalerAllReduce (src/nnfusion/core/kernels/cuda_gpu/kernels/allreduce.cpp:18-98).
- * The CTA that finishes a 16-row tile of the output writes its fp32 sums into this rank's peer-visible buffer,
- * announces the tile to every peer, waits (bounded) for their announcements of the same tile, reads their sums
- * with plain peer loads and adds in rank order, so every rank stores the same bits and the exchange of early
- * tiles overlaps the arithmetic of later ones.
+ * The CTA that finishes a 16-row tile of the output writes its fp32 sums into every rank's buffer (plain stores,
+ * over NVLink for the peers'), announces the tile to every peer, waits (bounded) for their announcements of the
+ * same tile, finds everybody's sums in its own memory and adds them in rank order, so every rank stores the same
+ * bits and the exchange of early tiles overlaps the arithmetic of later ones.
  *
- * peers->bufs[r] / flags[r]: rank r's buffer (two halves of M*N floats, half_stride_bytes apart) and flag words
+ * peers->bufs[r] / flags[r]: rank r's buffer (two halves of world * M * N floats, one M * N block per sender,
+ * half_stride_bytes apart) and flag words
  * (nnf_b200_linear_allreduce_flag_bytes(desc) bytes, zeroed once, never written by anyone else) as mapped into
  * this process.  peers->epoch: call number, from 1, +1 per call, the same on every rank -- or 0 to count on the
  * device (then a captured sequence with an even number of calls can be replayed).  Every rank calls with the same

@@ -804,11 +804,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     // ---- exchange: summing over the ranks of a tensor-parallel group inside this launch (ar_world > 1)
     // Every rank runs this kernel with the same launch shape, so the CTA that holds the final sum of a row tile here
     // (for splits == 1 the tile's own CTA, otherwise the split that arrived last) has one partner per rank.  It
-    // writes its fp32 sums into this rank's peer-visible buffer, tells every peer "tile t, call e" with one release
-    // store per peer, waits (bounded) for the peers' words for the same tile, reads their sums with plain peer loads
-    // and adds everything in rank order: every rank stores the same bits.  Calls alternate between the two halves
-    // of the buffers (half = e & 1): a rank can be one call ahead of a peer that is still reading a tile, never two,
-    // because the same tile's flag of the call in between is needed first.  Nothing here waits on a CTA of this GPU,
+    // writes its fp32 sums into EVERY rank's buffer (slot [sender] of the half in use: plain stores, over NVLink for
+    // the peers'), tells every peer "tile t, call e" with one release store per peer, waits (bounded) for the peers'
+    // words for the same tile, then finds everybody's sums in its own memory and adds them in rank order: every
+    // rank stores the same bits, and one NVLink hop (data and flag travel together) stands between a tile's last
+    // sum and its result.  Calls alternate between the two halves of the buffers (half = e & 1): a rank can be one
+    // call ahead of a peer that is still reading a tile, never two, because the same tile's flag of the call in
+    // between is needed first.  Nothing here waits on a CTA of this GPU,
     // and the peers' CTAs announce before they wait, so no cycle of waits can form.  A wait that gives up raises
     // the status word; the tile is then left unwritten.
     const bool ar = !DUAL && p.ar_world > 1;
@@ -831,15 +833,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
             *ar_ok = 1;
         __syncthreads();
     };
+    const size_t ar_slot = (size_t)p.M * p.N * sizeof(float); // one sender's sums inside a half
     auto ar_put = [&](int j, int m, int n, float v) {
-        *reinterpret_cast<float*>(const_cast<char*>(p.ar_bufs[p.ar_rank]) + (size_t)(ep_s[j] & 1u) * p.ar_half_stride +
-                                  ((size_t)m * p.N + n) * sizeof(float)) = v;
+        const size_t off = (size_t)(ep_s[j] & 1u) * p.ar_half_stride + (size_t)p.ar_rank * ar_slot +
+                           ((size_t)m * p.N + n) * sizeof(float);
+        for (int r = 0; r < p.ar_world; r++)
+            *reinterpret_cast<float*>(const_cast<char*>(p.ar_bufs[r]) + off) = v;
     };
     auto ar_end = [&](int first, int count, bool by_last_flag) {
         auto owns = [&](int j) { return !by_last_flag || last_flag[j] != 0; };
         uint32_t* counters = p.ar_flags[p.ar_rank] + (size_t)p.row_tiles * 8;
-        // this rank's sums are ordered before the announcements by the barrier and the release stores (cumulative
-        // over what the barrier made visible to the storing thread)
+        // this rank's sums (in every rank's memory) are ordered before the announcements by the barrier and the
+        // release stores (cumulative over what the barrier made visible to the storing thread)
         __syncthreads();
         if (tid < count * p.ar_world) // thread (tile j, peer r): announce, then wait
         {
@@ -882,10 +887,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
             const int n = (tile0 + first + j) * 16 + row;
             if (m < p.M && n < p.N)
             {
-                const size_t off = (size_t)(ep_s[j] & 1u) * p.ar_half_stride + ((size_t)m * p.N + n) * sizeof(float);
+                const char* half = p.ar_bufs[p.ar_rank] + (size_t)(ep_s[j] & 1u) * p.ar_half_stride +
+                                   ((size_t)m * p.N + n) * sizeof(float);
                 float v = 0.f;
                 for (int r = 0; r < p.ar_world; r++)
-                    v += __ldcv(reinterpret_cast<const float*>(p.ar_bufs[r] + off));
+                    v += __ldcv(reinterpret_cast<const float*>(half + (size_t)r * ar_slot));
                 store_y(m, n, finish(v, 0.f, 0.f, m, n));
             }
         }

@@ -381,8 +381,10 @@ int nnf_b200_linear_allreduce(nnf_b200_ctx* ctx, void* stream, const nnf_b200_li
         return nnf::set_error(ctx, NNF_B200_ENOTSUP,
                               "the fused sum over ranks serves the small-M kernel (M <= 16), fp16 output, no RMSNorm "
                               "prologue and no SiLU*mul epilogue");
-    if (peers->half_stride_bytes < (size_t)desc->M * desc->N * sizeof(float) || peers->half_stride_bytes % 16 != 0)
-        return nnf::set_error(ctx, NNF_B200_EINVAL, "half_stride_bytes must hold M*N floats and be a multiple of 16");
+    if (peers->half_stride_bytes < (size_t)peers->world * desc->M * desc->N * sizeof(float) ||
+        peers->half_stride_bytes % 16 != 0)
+        return nnf::set_error(ctx, NNF_B200_EINVAL,
+                              "half_stride_bytes must hold world * M * N floats and be a multiple of 16");
     for (int r = 0; r < peers->world; r++)
     {
         if (!peers->bufs[r] || !peers->flags[r])

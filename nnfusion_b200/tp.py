@@ -126,7 +126,7 @@ class PeerLinear:
         if self.world > 8:
             raise ValueError("the fused sum serves up to 8 ranks of one node")
         self.max_rows = max_rows
-        self.half = (max_rows * weight.N * 4 + 255) // 256 * 256
+        self.half = (self.world * max_rows * weight.N * 4 + 255) // 256 * 256   # every sender's sums, per half
         d = self.node.desc(1, torch.float16)
         flag_bytes = int(self.ctx.lib.nnf_b200_linear_allreduce_flag_bytes(ctypes.byref(d)))
         self.flag_off = 2 * self.half

@@ -154,8 +154,9 @@ def test_invalid_arguments():
 
 @pytest.mark.parametrize("M,N,K,world,rank", [(1, 272, 1024, 2, 0), (16, 96, 512, 3, 1), (3, 512, 4608, 4, 2)])
 def test_linear_with_fused_sum_over_ranks(M, N, K, world, rank):
-    """nnf_b200_linear_allreduce on one GPU: the peers' buffers hold known partial sums and their flags were set by
-    the host, so nothing waits; K = 4608 exercises split-K (the last-arriving split does the exchange)."""
+    """nnf_b200_linear_allreduce on one GPU: this rank's buffer holds known partial sums in the peers' slots (a rank
+    writes its sums into every rank's buffer) and their flags were set by the host, so nothing waits; K = 4608
+    exercises split-K (the last-arriving split does the exchange)."""
     import torch
     from nnfusion_b200 import _lib as L
     from nnfusion_b200 import synth
@@ -167,19 +168,20 @@ def test_linear_with_fused_sum_over_ranks(M, N, K, world, rank):
     w = synth.make_weights(rng, N, K, 4, 128)
     node = DequantDot(DeviceWeight.from_host(w, "cuda:0"))
     ctx = node.ctx
-    half = (M * N * 4 + 255) // 256 * 256
+    half = (world * M * N * 4 + 255) // 256 * 256       # one M x N block per sender
     d = node.desc(M, torch.float16)
     fb = int(ctx.lib.nnf_b200_linear_allreduce_flag_bytes(ctypes.byref(d)))
     others = [rng.standard_normal((M, N)).astype(np.float32) for _ in range(world)]
     bufs, flags = [], []
     for r in range(world):
         b = torch.zeros(2 * half // 4, dtype=torch.float32, device="cuda")
-        if r != rank:
-            b[: M * N] = torch.from_numpy(-others[r].reshape(-1)).cuda()                 # half 0: even calls
-            b[half // 4: half // 4 + M * N] = torch.from_numpy(others[r].reshape(-1)).cuda()  # half 1: odd calls
         bufs.append(b)
         f = torch.zeros(fb // 4, dtype=torch.int32, device="cuda")
         flags.append(f)
+    for r in range(world):
+        if r != rank:                                    # what peer r would have written into this rank's buffer
+            bufs[rank][r * M * N: (r + 1) * M * N] = torch.from_numpy(-others[r].reshape(-1)).cuda()   # half 0: even calls
+            bufs[rank][half // 4 + r * M * N: half // 4 + (r + 1) * M * N] = torch.from_numpy(others[r].reshape(-1)).cuda()
     tiles = (N + 15) // 16
     flags[rank][: tiles * 8].fill_(1000)      # the peers are far ahead: no wait in this test
     vp = ctypes.c_void_p
@@ -206,6 +208,10 @@ def test_linear_with_fused_sum_over_ranks(M, N, K, world, rank):
     for r in range(world):
         if r != rank:
             assert (flags[r].cpu().numpy()[: tiles * 8].reshape(tiles, 8)[:, rank] == 3).all()
+            # ... and left its own sums in the peer's buffer, slot `rank`, half 1 (call 3) and half 0 (call 2)
+            for h in (0, 1):
+                got = bufs[r].cpu().numpy()[h * (half // 4) + rank * M * N: h * (half // 4) + (rank + 1) * M * N]
+                assert np.abs(got.reshape(M, N) - own).max() / np.abs(own).max() <= 2e-3
 
 
 def test_fused_sum_rejects_what_it_does_not_serve():
