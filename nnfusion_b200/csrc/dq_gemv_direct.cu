@@ -416,8 +416,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
 #pragma unroll
     for (int l = 0; l < 2; l++)
     {
-        const uint32_t unit = (uint32_t)(2 * slice + l);
-        grp_of[l] = !unit_ok[l] ? 0 : (p.group_units == 1 ? (int)unit : (int)__umulhi(unit, p.group_magic));
+        // a unit that does not exist (a warp without a slice, the tail of the row) multiplies zero activations with
+        // the parameters of the CTA's first unit: finite numbers that are in shared memory whichever columns were
+        // copied
+        const uint32_t unit = (uint32_t)(unit_ok[l] ? 2 * slice + l : 2 * slice0);
+        grp_of[l] = p.group_units == 1 ? (int)unit : (int)__umulhi(unit, p.group_magic);
     }
     // Byte offsets of this lane's scales / zero-points inside a tile's parameter block: rows g and g + 8 of the
     // tile, groups of the two units of the slice.
