@@ -336,8 +336,8 @@ def run_decode_gemv(args, torch, sampler_index):
             e(xp, yp)
         ms_e2e = timed_plain_steps(torch, lambda i: entries[i % ncopies](xp, yp), e2e_steps, args.warmup)
         e2e_path = ("generated nnfusion_rt (nnfusion_b200.codegen, nvcc, linked against libnnf_b200.so) loaded the "
-                    "reference Executor's way; kernel_entry_host: pinned host x -> device, nnf_b200_linear, device y -> "
-                    "pinned host, stream sync, per step")
+                    "reference Executor's way; kernel_entry_host: pinned host x -> device (copy), nnf_b200_linear "
+                    "storing y straight into the pinned host buffer over PCIe, stream sync, per step")
     except Exception as e:  # no nvcc on this box, or the build failed: the node's own host entry instead
         sys.stderr.write(f"[bench] generated runtime unavailable ({e}); end-to-end leg through DequantDot.host_entry\n")
         for op in ops:

@@ -253,12 +253,32 @@ extern "C" int kernel_entry({entry_in}, {yt}* Result_0)
     return 0;
 }}
 
-// host buffers in, host buffers out (-fhost_entry): copies, the call, a synchronisation
+// Device address of a pinned, mapped host buffer (nullptr for pageable memory).
+static void* device_view_of_host(const void* p)
+{{
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess)
+    {{
+        (void)cudaGetLastError();
+        return nullptr;
+    }}
+    return a.type == cudaMemoryTypeHost ? a.devicePointer : nullptr;
+}}
+
+// host buffers in, host buffers out (-fhost_entry): the input is copied to the device, the node runs, the result comes
+// back, the stream is synchronised.  When the result buffer is pinned (mapped into the device's address space) the
+// node stores its result straight into it over PCIe, which saves the copy back; otherwise the result is copied.
 extern "C" int kernel_entry_host({xt}* Parameter_0_0_host{(', ' + yt + '* Parameter_4_0_host') if node.epilogue == 'add' else ''}, {yt}* Result_0_host)
 {{
     CUDA_SAFE_CALL(cudaMemcpyAsync(Parameter_0_0_dev, Parameter_0_0_host, {x_bytes}, cudaMemcpyHostToDevice, 0));
-{host_add}    kernel_entry(Parameter_0_0_dev{', addend_dev' if node.epilogue == 'add' else ''}, Result_5_0);
-    CUDA_SAFE_CALL(cudaMemcpyAsync(Result_0_host, Result_5_0, {y_bytes}, cudaMemcpyDeviceToHost, 0));
+{host_add}    {yt}* mapped = ({yt}*)device_view_of_host(Result_0_host);
+    if (mapped)
+        kernel_entry(Parameter_0_0_dev{', addend_dev' if node.epilogue == 'add' else ''}, mapped);
+    else
+    {{
+        kernel_entry(Parameter_0_0_dev{', addend_dev' if node.epilogue == 'add' else ''}, Result_5_0);
+        CUDA_SAFE_CALL(cudaMemcpyAsync(Result_0_host, Result_5_0, {y_bytes}, cudaMemcpyDeviceToHost, 0));
+    }}
     CUDA_SAFE_CALL(cudaStreamSynchronize(0));
     return 0;
 }}

@@ -78,3 +78,28 @@ def test_residual_add_epilogue_through_the_generated_runtime(tmp_path):
     want = (oracle_linear(x, w, out_dtype=np.float32) + c.astype(np.float32)).astype(np.float16)
     assert orc.max_rel_err(y, want) <= TOL_F16
     ex.close()
+
+
+def test_host_entry_writes_into_pinned_result_buffers(tmp_path):
+    """kernel_entry_host with a pinned result buffer: the node stores its result straight into host memory (no copy
+    back); with a pageable one the result is copied.  Same bits either way, fresh inputs on every call."""
+    import torch
+    rng = np.random.Generator(np.random.PCG64(2))
+    M, N, K = 1, 1024, 2048
+    w = synth.make_weights(rng, N, K, 4, 128)
+    rt = _project(tmp_path, codegen.DequantDotNode("DequantDot_0", M, w))
+    ex = runtime_loader.RuntimeExecutor(rt)
+    assert ex.host_entry
+    xh = torch.empty((M, K), dtype=torch.float16).pin_memory()
+    yh = torch.empty((M, N), dtype=torch.float16).pin_memory()
+    for call in range(4):
+        x = synth.make_x(rng, M, K, np.float16)
+        xh.copy_(torch.from_numpy(x))
+        yh.fill_(float("nan"))
+        assert ex({"x": runtime_loader.feed_torch(xh)}, {"y": runtime_loader.feed_torch(yh)}) == 0
+        err = orc.max_rel_err(yh.numpy().copy(), oracle_linear(x, w))
+        assert err <= TOL_F16, (call, err)
+    y2 = np.full((M, N), np.nan, np.float16)           # pageable: the copy path
+    assert ex({"x": runtime_loader.feed_numpy(x)}, {"y": runtime_loader.feed_numpy(y2)}) == 0
+    np.testing.assert_array_equal(y2, yh.numpy())
+    ex.close()
