@@ -859,6 +859,14 @@ int gemm_supported(const nnf_b200_ctx*, const nnf_b200_linear_desc& d, std::stri
         *why = "weight rows must be a multiple of 16 bytes";
         return NNF_B200_ENOTSUP;
     }
+    // the kernel counts its units of work (tiles x raw chunks of K) in 32-bit integers
+    const long long tiles = (long long)((d.M + 255) / 256) * ((d.N + 127) / 128);
+    const long long chunks = (d.K / 64 + (d.w_bits == 4 ? 3 : 1)) / (d.w_bits == 4 ? 4 : 2);
+    if (tiles * chunks >= (1ll << 31) || tiles >= (1ll << 30))
+    {
+        *why = "M * N * K is beyond what one launch counts";
+        return NNF_B200_ENOTSUP;
+    }
     return NNF_B200_OK;
 }
 
