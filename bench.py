@@ -367,6 +367,46 @@ def run_decode_gemv(args, torch, sampler_index):
     return out, ops, x, y
 
 
+def run_config1_gemv(args, torch, sampler_index):
+    """Configuration 1, the reference's own CPU-runnable case: X f32 [16,4096], W u8 [4096,4096], one f32 scale and
+    one u8 zero-point per output row, Y f32.  Same contract as the headline; the end-to-end leg goes through
+    DequantDot.host_entry (pinned host x -> device, the call, y -> pinned host as one graph launch, then a sync)."""
+    from nnfusion_b200.linear import DequantDot, default_context
+    N, K, M, ncopies = 4096, 4096, 16, 12
+    ctx = default_context(torch.cuda.current_device())
+    ops = [DequantDot(rand_device_weight(torch, N, K, bits=8, group=K, scale_dtype=torch.float32)) for _ in range(ncopies)]
+    x = torch.randn(M, K, device="cuda")
+    y = torch.empty(M, N, device="cuda")
+    ctx.launch_count(reset=True)
+    with ClockSampler(sampler_index) as cs:
+        ms = timed_graph_steps(torch, [(lambda op=op: op(x, y)) for op in ops], args.steps, args.warmup)
+    ctx.device_status()
+    bytes_step = linear_bytes(M, N, K, bits=8, group=K, act_bytes=4, scale_bytes=4)
+    value = bytes_step * args.steps / (ms * 1e-3) / 1e9
+    xh, yh = torch.randn(M, K).pin_memory(), torch.empty(M, N).pin_memory()
+    for op in ops:
+        op.host_entry(xh, yh)
+    e2e_steps = min(args.steps, 2000)
+    ms_e2e = timed_plain_steps(torch, lambda i: ops[i % ncopies].host_entry(xh, yh), e2e_steps, args.warmup)
+    peaks = measured_peaks()
+    return {
+        "metric": "u8_perchannel_f32_m16_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
+        "ms_per_step": ms / args.steps, "repeats": REPEATS, "dtype": "f32", "scaling": "weak",
+        "config": {"workload": "config1_gemv: X f32 [16,4096], W u8 per-channel [4096,4096], f32 scales, Y f32, f32 accumulate",
+                   "algorithmic_bytes_per_step": bytes_step,
+                   "l2": f"rotation over {ncopies} weight copies ({ncopies * bytes_step / 1e6:.0f} MB) larger than L2",
+                   "launch": "CUDA graph replay of the C-ABI calls"},
+        "roofline": {"bound": "hbm", "achieved": round(value, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(value / peaks["hbm_gbs"], 4), "traffic": None,
+                     "peak_source": f"of {peaks['source']}", "kernel": "dq_gemv_direct_kernel<8,2,true,false,2,2,false>"},
+        "e2e": {"value": round(bytes_step * e2e_steps / (ms_e2e * 1e-3) / 1e9, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": M * K * 4, "d2h_bytes_per_step": M * N * 4, "ms_per_step": ms_e2e / e2e_steps,
+                "steps": e2e_steps, "path": "DequantDot.host_entry: pinned host x -> device, nnf_b200_linear, device y -> "
+                                            "pinned host (one graph launch), stream sync, per step"},
+        "gpu_launches": args.steps, "clocks": cs.summary(),
+    }
+
+
 def generated_runtimes(torch, ops, M, ncopies):
     """One generated nnfusion_rt instance per weight copy of `ops` (the weights are read back from the device and
     written as the project's Constant/*.bin): generated and built once, the shared object copied per instance."""
@@ -773,7 +813,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", default="auto", choices=["auto", "decode_gemv", "mlp70b_decode", "prefill_gemm", "layer7b_decode"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "decode_gemv", "mlp70b_decode", "prefill_gemm", "layer7b_decode", "config1_gemv"])
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements at 1 GPU")
     args = ap.parse_args()
 
@@ -846,6 +886,8 @@ def main():
             out = run_prefill_gemm(args, torch, local_rank)
         elif workload == "layer7b_decode":
             out = run_layer7b(args, torch, local_rank)
+        elif workload == "config1_gemv":
+            out = run_config1_gemv(args, torch, local_rank)
         else:
             out = run_mlp70b(args, torch, local_rank, rank, world, dist)
         if rank == 0:
@@ -858,6 +900,11 @@ def main():
                     sec, n, cores, kind = cpu_reference_gemv(10.0, 344, 4096, 4096)
                     v, unit = 2.0 * 4096 * 344 * 4096 / sec / 1e12, "TFLOP/s"
                     sample = "344 of 11008 weight rows, M = 4096, ~10 s"
+                elif workload == "config1_gemv":
+                    sec, n, cores, kind = cpu_reference_gemv(10.0, 512, 4096, 16)
+                    v, unit = linear_bytes(16, 512, 4096, bits=8, group=4096, act_bytes=4, scale_bytes=4) / sec / 1e9, "GB/s"
+                    sample = ("512 of 4096 weight rows, M = 16 (the dequant graph on group-128 uint4 test data: the "
+                              "element-wise kernels and the SGEMM see the same fp32 sizes), ~10 s of calls")
                 elif workload == "mlp70b_decode":
                     sec, n, cores, kind = cpu_reference_gemv(10.0, 896, 8192, 1)
                     v, unit = linear_bytes(1, 896, 8192) / sec / 1e9, "GB/s"
