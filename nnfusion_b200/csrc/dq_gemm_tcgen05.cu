@@ -184,7 +184,7 @@ __device__ __forceinline__ void store_value(const GemmParams& p, int m, int n, f
 {
     const size_t at = (size_t)m * p.N + n;
     if (gated)
-        v *= __fdividef(g, 1.0f + __expf(-g)); // SiLU(g) = g / (1 + e^-g); both intrinsics are good to ~1e-6 relative
+        v *= g > -80.f ? __fdividef(g, 1.0f + __expf(-g)) : 0.f; // SiLU(g) = g / (1 + e^-g), ~1e-6 relative; 0 far left
     v += bias;
     if (p.has_addend)
         v += p.y_f32 ? reinterpret_cast<const float*>(p.bias)[at]
@@ -201,9 +201,13 @@ __device__ __forceinline__ uint32_t gate_bits(const GemmParams& p, int m, int n)
     const size_t at = (size_t)m * p.N + n;
     return p.y_f32 ? static_cast<const uint32_t*>(p.y)[at] : (uint32_t)static_cast<const unsigned short*>(p.y)[at];
 }
+// (a gate product that left the fp16 range on its way through y comes back as the largest fp16 number, so that SiLU
+// stays finite: SiLU(-inf) would be -inf / inf)
 __device__ __forceinline__ float gate_value(const GemmParams& p, uint32_t bits)
 {
-    return p.y_f32 ? __uint_as_float(bits) : __half2float(__ushort_as_half((unsigned short)bits));
+    if (p.y_f32)
+        return __uint_as_float(bits);
+    return fminf(fmaxf(__half2float(__ushort_as_half((unsigned short)bits)), -65504.f), 65504.f);
 }
 
 // GATED: y holds the gate products of an earlier launch (the second half of SiLU(gate) * up).
