@@ -4,6 +4,7 @@ import ctypes
 import numpy as np
 import pytest
 
+from nnfusion_b200 import _lib as L
 from nnfusion_b200 import synth
 from oracle import oracle as orc
 from tests.util import TOL_F16, TOL_F32, gpu_linear, oracle_linear
@@ -194,3 +195,21 @@ def test_output_padding_untouched():
     out = big.cpu().numpy()
     assert np.isnan(out[150:]).all()
     _check(out[:150].reshape(3, 50), oracle_linear(x, w), TOL_F16, tight=1.5e-3)
+
+
+@pytest.mark.parametrize("K", [2304, 4480, 7168, 11008])
+@pytest.mark.parametrize("M,N,bits,group,xdt,dual", [
+    (1, 4096, 4, 128, np.float16, False), (1, 1008, 4, 128, np.float16, True),
+    (3, 272, 8, 64, np.float32, False), (16, 1024, 4, 128, np.float16, False)])
+def test_k_split_with_idle_warps_after_other_kernels_used_shared_memory(K, M, N, bits, group, xdt, dual):
+    """K values whose 128-byte slices do not divide evenly over the CTAs that share a row: some warps have no slice,
+    and CTAs copy only their own columns of the scales and zero-points.  A large-M call first leaves arbitrary bit
+    patterns in shared memory, so a warp that multiplied zero activations with parameters nobody copied would show."""
+    rng = np.random.Generator(np.random.PCG64(500 + K + M))
+    xg = (rng.standard_normal((64, 256)) * 1e4).astype(np.float16)
+    gpu_linear(xg, synth.make_weights(rng, 256, 256, 8, 64), kernel=L.KERNEL_GEMM)
+    x = synth.make_x(rng, M, K, xdt)
+    sd = np.float32 if xdt == np.float32 else np.float16
+    w = synth.make_weights(rng, N, K, bits, group, sd)
+    w2 = synth.make_weights(rng, N, K, bits, group, sd) if dual else None
+    _check(gpu_linear(x, w, w2), oracle_linear(x, w, w2), TOL_F32 if xdt == np.float32 else TOL_F16)
