@@ -395,23 +395,31 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
             int g;
         };
         RawParams pa{0, 0, 0}, pb{0, 0, 0};
-        // rows past N read the last row's parameters, never stored
-        auto row_of = [&](int tile) { return min((tile / p.m_tiles) * C::BN + r, p.N - 1); };
-        auto ask = [&](int n, int kb, int kb_last, RawParams& q) {
+        // This thread's row of scales and of zero-points (rows past N read the last row's, never stored).
+        struct RowParams
+        {
+            const char* scale;
+            const uint8_t* zp;
+        };
+        auto row_of = [&](int tile) {
+            const size_t n = (size_t)min((tile / p.m_tiles) * C::BN + r, p.N - 1);
+            return RowParams{static_cast<const char*>(p.scale) + n * p.G * (p.scale_f32 ? 4 : 2),
+                             p.zp + n * (WBITS == 4 ? p.zp_row_bytes : p.G)};
+        };
+        auto ask = [&](const RowParams& n, int kb, int kb_last, RawParams& q) {
             const int kbc = min(kb, kb_last);
             q.g = p.kbpg_shift >= 0 ? (kbc >> p.kbpg_shift) : kbc / kb_per_group;
-            const size_t i = (size_t)n * p.G + q.g;
             if (p.scale_f32)
-                q.s = __ldg(static_cast<const uint32_t*>(p.scale) + i);
+                q.s = __ldg(reinterpret_cast<const uint32_t*>(n.scale) + q.g);
             else
-                q.s = __ldg(static_cast<const unsigned short*>(p.scale) + i);
-            q.z = WBITS == 4 ? __ldg(p.zp + (size_t)n * p.zp_row_bytes + (q.g >> 1)) : __ldg(p.zp + i);
+                q.s = __ldg(reinterpret_cast<const unsigned short*>(n.scale) + q.g);
+            q.z = __ldg(n.zp + (WBITS == 4 ? q.g >> 1 : q.g));
         };
         bool asked = false;
 
         while (ok && work.next(p, sg))
         {
-            const int n = row_of(sg.tile);
+            const RowParams n = row_of(sg.tile);
             if (!asked)
             {
                 ask(n, sg.kb0 + grp, sg.kb1 - 1, pa);
@@ -513,7 +521,7 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                 asked = ahead.next(p, nx);
                 if (asked)
                 {
-                    const int n_next = row_of(nx.tile);
+                    const RowParams n_next = row_of(nx.tile);
                     ask(n_next, nx.kb0 + grp, nx.kb1 - 1, pa);
                     ask(n_next, nx.kb0 + grp + C::DQ_GROUPS, nx.kb1 - 1, pb);
                 }
