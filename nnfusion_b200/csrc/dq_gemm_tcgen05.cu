@@ -334,7 +334,17 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
             // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = BX, M = 128
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(C::BX >> 3) << 17) | ((uint32_t)(C::BN >> 4) << 24);
             bool ok = true;
-            uint32_t pr = 0, si = 0;
+            uint32_t si = 0;
+            // Ring position kept as (slot, phase) with the slot's addresses carried along: this one thread feeds the
+            // tensor core next to four busy conversion warps on its scheduler, so every instruction it does not
+            // need to issue between two MMAs is tensor time.
+            int q = 0;
+            uint32_t phase = 0;
+            const uint64_t xdesc0 = smem_desc_k_sw128(smem_u32(xs));
+            const uint32_t a_tmem0 = tmem_base + (uint32_t)C::A_COL0;
+            uint64_t xdesc = xdesc0;  // of slot q: two stages of x ...
+            uint32_t a_tmem = a_tmem0; // ... and two stages of converted weights
+            uint32_t bar_full = full(0), bar_empty = empty(0);
             while (ok && work.next(p, sg))
             {
                 if (si > 0)
@@ -345,25 +355,38 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                         break;
                     tcgen05_fence_after();
                 }
-                for (int kb = sg.kb0; kb < sg.kb1; kb += 2, pr++)
+                uint32_t accumulate = 0u; // the segment's first MMA overwrites D
+                for (int kb = sg.kb0; kb < sg.kb1; kb += 2)
                 {
-                    const int q = pr % C::PAIRS;
-                    ok = wait_hot(full(q), (pr / C::PAIRS) & 1u, abort_flag);
+                    ok = wait_hot(bar_full, phase, abort_flag);
                     if (!ok)
                         break;
                     tcgen05_fence_after();
-                    const int nkb = min(2, sg.kb1 - kb);
-                    for (int h = 0; h < nkb; h++)
+                    // (the descriptor's address field counts 16-byte units: stage and k step are plain additions)
+#pragma unroll
+                    for (int kk = 0; kk < C::BK / 16; kk++)
                     {
-                        const int s = 2 * q + h;
-                        const uint32_t xaddr = smem_u32(xs + (size_t)s * C::X_STAGE_BYTES);
-                        const uint32_t a_tmem = tmem_base + (uint32_t)(C::A_COL0 + s * C::A_STAGE_COLS);
+                        tcgen05_mma_ts(tmem_base, a_tmem + kk * 8, xdesc + (uint64_t)(kk * 2), idesc, accumulate);
+                        accumulate = 1u;
+                    }
+                    if (kb + 1 < sg.kb1)
+                    {
 #pragma unroll
                         for (int kk = 0; kk < C::BK / 16; kk++)
-                            tcgen05_mma_ts(tmem_base, a_tmem + kk * 8, smem_desc_k_sw128(xaddr + kk * 32), idesc,
-                                           (kb + h != sg.kb0 || kk != 0) ? 1u : 0u);
+                            tcgen05_mma_ts(tmem_base, a_tmem + C::A_STAGE_COLS + kk * 8,
+                                           xdesc + (uint64_t)((C::X_STAGE_BYTES >> 4) + kk * 2), idesc, 1u);
                     }
-                    tcgen05_commit(empty(q)); // arrives when the MMAs above have consumed the pair
+                    tcgen05_commit(bar_empty); // arrives when the MMAs above have consumed the pair
+                    if (++q == C::PAIRS)
+                    {
+                        q = 0, phase ^= 1u;
+                        xdesc = xdesc0, a_tmem = a_tmem0, bar_full = full(0), bar_empty = empty(0);
+                    }
+                    else
+                    {
+                        xdesc += (uint64_t)(2 * (C::X_STAGE_BYTES >> 4)), a_tmem += 2 * C::A_STAGE_COLS;
+                        bar_full += 8u, bar_empty += 8u;
+                    }
                 }
                 if (ok)
                     tcgen05_commit(acc_full);
