@@ -53,6 +53,7 @@ struct GemvPlan
     int xfrag_bytes = 0;        // shared memory per warp for the activation fragments of batch rows 8..15
     int direct = 0;             // served by the register-pipeline kernel (dq_gemv_direct.cu) instead of the ring kernel
     int prefetch_tiles = 0;     // register-pipeline kernel: L2 prefetch window in row tiles
+    int l1_lines = 0;           // register-pipeline kernel: weight loads take lines in L1
 };
 
 int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
