@@ -41,7 +41,7 @@ namespace
 using namespace nnf::ptx;
 
 constexpr int kMaxWarps = 16;
-constexpr int kBatch = 16; // most row tiles between two reductions over the warps
+constexpr int kBatch = 32; // most row tiles between two reductions over the warps
 
 struct DirectParams
 {
@@ -71,6 +71,9 @@ struct DirectParams
     int sc_row_bytes; // bytes of one row of scales
     int pmode;       // see the kernel's PMODE
     int scale_tile_bytes, zp_tile_bytes;
+    // Rows of scales / zero-points as they lie in shared memory: whole rows, or (range_params) only the 16-byte
+    // pieces that hold the columns of this CTA's K range, the widest range over the splits.
+    int sm_sc_row, sm_zp_row;
     int xfrag_bytes;    // shared memory per warp for the activation fragments of batch rows 8..15 (0 when M <= 8)
     int prefetch_tiles; // L2 prefetch window in row tiles ahead of the register pipeline (0: no prefetch)
     int l1_lines;       // weight loads take lines in L1 (long launches)
@@ -199,13 +202,38 @@ struct Fmt
     static constexpr int NF = LE / 2;                  // half2 fragments per chunk
 };
 
+// The 16-byte pieces of a row of scales and of a row of zero-points that hold the quantisation groups of the slices
+// [slice0, slice0 + slices) (a slice is slice_elems elements of K): first byte and number of pieces of each.
+struct ParamRange
+{
+    int sc_b0, sc_pieces, zp_b0, zp_pieces;
+};
+__host__ __device__ inline ParamRange param_range(int slice0, int slices, int slice_elems, int K, int group, int sbytes,
+                                                  int wbits, int sc_row_bytes, int zp_row_bytes)
+{
+    const int e0 = slice0 * slice_elems;
+    const int e1 = (slice0 + slices) * slice_elems < K ? (slice0 + slices) * slice_elems : K;
+    const int g0 = e0 / group, g1 = (e1 + group - 1) / group;
+    ParamRange r;
+    r.sc_b0 = (g0 * sbytes) & ~15;
+    const int sc_end = (g1 * sbytes + 15) & ~15;
+    r.sc_pieces = ((sc_end < sc_row_bytes ? sc_end : sc_row_bytes) - r.sc_b0) >> 4;
+    const int z0 = wbits == 4 ? g0 >> 1 : g0, z1 = wbits == 4 ? (g1 + 1) >> 1 : g1;
+    r.zp_b0 = z0 & ~15;
+    const int zp_end = (z1 + 15) & ~15;
+    r.zp_pieces = ((zp_end < zp_row_bytes ? zp_end : zp_row_bytes) - r.zp_b0) >> 4;
+    return r;
+}
+
 // Shared-memory footprint, shared by host and device.  All sizes in bytes.
 struct DirectSmem
 {
     size_t params, bars, red, ss, flags, xsm, total;
-    __host__ __device__ DirectSmem(int sets, int mb, int warps, int batch, int tq, int pset_bytes, int xfrag_bytes)
+    __host__ __device__ DirectSmem(int sets, int mb, int warps, int batch, int tq, int pset_bytes, int xfrag_bytes,
+                                   int nbuf = 2)
     {
-        params = (size_t)2 * batch * sets * pset_bytes; // two batches of (scales, zero-points) per weight set
+        // (scales, zero-points) of a batch per weight set; two batches take turns unless one holds all tiles
+        params = (size_t)nbuf * batch * sets * pset_bytes;
         bars = 0;
         red = sizeof(float) * (size_t)warps * batch * sets * mb * 8 * tq * 4;
         ss = sizeof(float) * ((size_t)warps * 8 * mb + 8 * mb);
@@ -328,7 +356,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     const int tq_shift = tq >> 1; // tq is 1, 2 or 4
     const int pt_shift = 5 + tq_shift + (MB == 2 ? 1 : 0);
     const int per_tile = 1 << pt_shift; // MB * 8 * tq * 4 floats: one warp's partial sums of one tile and weight set
-    const int pset_bytes = p.scale_tile_bytes + p.zp_tile_bytes;
+    const int sm_scale_tile = 16 * p.sm_sc_row, sm_zp_tile = 16 * p.sm_zp_row; // one tile's rows in shared memory
+    const int pset_bytes = sm_scale_tile + sm_zp_tile;
     // (pointers stay derived from the array itself, never from an integer, so that every access below is compiled
     // as a shared-memory access with a 32-bit address rather than as a generic one)
     uint8_t* pbuf = smem_raw; // [2 batches][SETS][scales of the batch's tiles | zero-points of the batch's tiles]
@@ -340,7 +369,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     const uint32_t xsm_s = smem_u32(last_flag + 2 * kBatch + 4) + (uint32_t)(warp * p.xfrag_bytes) + (uint32_t)lane * 8u;
     const uint32_t pbuf_s = smem_u32(pbuf);
     const uint32_t pbatch_bytes = (uint32_t)(p.batch * SETS * pset_bytes); // one batch's parameters
-    const uint32_t pzp_off = (uint32_t)(p.batch * p.scale_tile_bytes);     // zero-points follow the batch's scales
+    const uint32_t pzp_off = (uint32_t)(p.batch * sm_scale_tile);          // zero-points follow the batch's scales
 
     // Parameters of the local tiles [first, first + count) into buffer `which`: every thread copies its share of
     // 16-byte pieces with cp.async and closes one copy group (an empty one when there is nothing to copy, so that
@@ -350,18 +379,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     auto copy_params = [&](int first, int count, int which) {
         if (p.bulk_params && p.range_params && count > 0)
         {
-            // K split over several CTAs: a CTA uses only the groups of its own slices.  Their bytes land where the
-            // whole rows would put them, so that nothing else changes; the other columns of the block stay unwritten.
-            // byte range of this CTA's groups inside a row of scales / of zero-points, widened to 16-byte pieces
+            // K split over several CTAs: a CTA uses only the groups of its own slices, and its rows in shared memory
+            // hold only the 16-byte pieces with those columns (a row there starts at column byte sc_b0 / zp_b0).
             // (worked out here, where it is needed, rather than kept in registers through the main loop)
-            const int e0 = slice0 * 2 * F::UE, e1 = min(p.K, (slice0 + my_slices) * 2 * F::UE); // a slice is two units
-            const int g0 = e0 / p.group, g1 = (e1 + p.group - 1) / p.group;
-            const int sb = p.scale_f32 ? 4 : 2;
-            const int sc_b0 = (g0 * sb) & ~15;
-            const int sc_pieces = (min(p.sc_row_bytes, (g1 * sb + 15) & ~15) - sc_b0) >> 4;
-            const int z0 = WBITS == 4 ? g0 >> 1 : g0, z1 = WBITS == 4 ? (g1 + 1) >> 1 : g1;
-            const int zp_b0 = z0 & ~15;
-            const int zp_pieces = (min(p.zp_row_bytes, (z1 + 15) & ~15) - zp_b0) >> 4;
+            const ParamRange pr = param_range(slice0, my_slices, 2 * F::UE, p.K, p.group, p.scale_f32 ? 4 : 2, WBITS,
+                                              p.sc_row_bytes, p.zp_row_bytes);
+            const int sc_b0 = pr.sc_b0, sc_pieces = pr.sc_pieces, zp_b0 = pr.zp_b0, zp_pieces = pr.zp_pieces;
             const int rows = count * 16;
             const int per_row = sc_pieces + zp_pieces;
 #pragma unroll
@@ -375,10 +398,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 {
                     const int row = i / per_row, c = i - row * per_row;
                     if (c < sc_pieces)
-                        cp_async16(dst + (uint32_t)(row * p.sc_row_bytes + sc_b0 + c * 16),
+                        cp_async16(dst + (uint32_t)(row * p.sm_sc_row + c * 16),
                                    sc_src + (size_t)row * p.sc_row_bytes + c * 16);
                     else
-                        cp_async16(dst + pzp_off + (uint32_t)(row * p.zp_row_bytes + zp_b0 + (c - sc_pieces) * 16),
+                        cp_async16(dst + pzp_off + (uint32_t)(row * p.sm_zp_row + (c - sc_pieces) * 16),
                                    zp_src + (size_t)row * p.zp_row_bytes + (c - sc_pieces) * 16);
                 }
             }
@@ -446,14 +469,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     // Byte offsets of this lane's scales / zero-points inside a tile's parameter block: rows g and g + 8 of the
     // tile, groups of the two units of the slice.
     const int sbytes = p.scale_f32 ? 4 : 2;
+    // first column byte of the rows in shared memory (0 unless only this CTA's K range was copied)
+    ParamRange col0{0, 0, 0, 0};
+    if (p.bulk_params && p.range_params)
+        col0 = param_range(slice0, my_slices, 2 * F::UE, p.K, p.group, sbytes, WBITS, p.sc_row_bytes, p.zp_row_bytes);
     int soff[2][2], zoff[2][2];
 #pragma unroll
     for (int l = 0; l < 2; l++)
 #pragma unroll
         for (int h = 0; h < 2; h++)
         {
-            soff[l][h] = ((g + 8 * h) * p.G + grp_of[l]) * sbytes;
-            zoff[l][h] = (g + 8 * h) * p.zp_row_bytes + (WBITS == 4 ? grp_of[l] >> 1 : grp_of[l]);
+            soff[l][h] = (g + 8 * h) * p.sm_sc_row + grp_of[l] * sbytes - col0.sc_b0;
+            zoff[l][h] = (g + 8 * h) * p.sm_zp_row + (WBITS == 4 ? grp_of[l] >> 1 : grp_of[l]) - col0.zp_b0;
         }
     const int zsh[2] = {(WBITS == 4) ? 4 * (grp_of[0] & 1) : 0, (WBITS == 4) ? 4 * (grp_of[1] & 1) : 0};
 
@@ -870,16 +897,22 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
         // this rank's sums (in every rank's memory) are ordered before the announcements by the barrier and the
         // release stores (cumulative over what the barrier made visible to the storing thread)
         __syncthreads();
-        if (tid < count * p.ar_world) // thread (tile j, peer r): announce, then wait
+        // pair (tile j, peer r) = idx: every announcement leaves before the first wait starts
+        for (int idx = tid; idx < count * p.ar_world; idx += nthreads)
         {
-            const int j = tid / p.ar_world, r = tid - j * p.ar_world;
+            const int j = idx / p.ar_world, r = idx - j * p.ar_world;
+            if (r != p.ar_rank && owns(j))
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ar_flags[r] + (size_t)(tile0 + first + j) * 8 + p.ar_rank),
+                             "r"(ep_s[j])
+                             : "memory");
+        }
+        for (int idx = tid; idx < count * p.ar_world; idx += nthreads)
+        {
+            const int j = idx / p.ar_world, r = idx - j * p.ar_world;
             if (r != p.ar_rank && owns(j))
             {
-                const int rt = tile0 + first + j;
                 const uint32_t e = ep_s[j];
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ar_flags[r] + (size_t)rt * 8 + p.ar_rank), "r"(e)
-                             : "memory");
-                const uint32_t* mine = p.ar_flags[p.ar_rank] + (size_t)rt * 8 + r;
+                const uint32_t* mine = p.ar_flags[p.ar_rank] + (size_t)(tile0 + first + j) * 8 + r;
                 bool seen = false;
                 for (uint32_t i = 0; i < (1u << 19) && !seen; i++) // roughly 0.4 s
                 {
@@ -1060,7 +1093,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                     red_a += red_step;
                     if (s == SETS - 1)
                     {
-                        sc_s += (uint32_t)p.scale_tile_bytes, zp_s += (uint32_t)p.zp_tile_bytes;
+                        sc_s += (uint32_t)sm_scale_tile, zp_s += (uint32_t)sm_zp_tile;
                         // keep the L2 window full: warp 0 of the split whose turn it is asks for the tile that
                         // enters it (a handful of instructions per tile; everybody else only skips a branch)
                         if (warp == 0 && jt < pf_until && lane < SETS && pf_turn == my_turn)
@@ -1216,21 +1249,48 @@ bool gemv_direct_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, Ge
     pl.warps = (pl.slices + pl.splits - 1) / pl.splits;
     const int steps = (pl.row_tiles + pl.ctas_per_split - 1) / pl.ctas_per_split;
     pl.depth = 2; // stages in the register pipeline (the PD of every instantiated variant)
-    // The longest batch whose double-buffered parameters and partial sums fit next to `best_res` CTAs per SM.
+    // Rows of scales / zero-points in shared memory: whole rows, or, when K is split and the rows are whole 16-byte
+    // pieces, only the pieces with the columns of a CTA's own K range (the widest range over the splits).
+    {
+        const int group = d.group_size > 0 ? d.group_size : d.K;
+        const int G = d.K / group, sbytes = d.scale_dtype == NNF_B200_F32 ? 4 : 2;
+        const int sc_row = G * sbytes, zp_row = d.w_bits == 4 ? (G + 1) / 2 : G;
+        pl.sm_sc_row = sc_row, pl.sm_zp_row = zp_row;
+        pl.range_layout = pset > 0 && pl.splits > 1 && sc_row % 16 == 0 && zp_row % 16 == 0;
+        if (pl.range_layout)
+        {
+            const int lo = pl.slices / pl.splits, rem = pl.slices % pl.splits;
+            int sc_pieces = 0, zp_pieces = 0;
+            for (int i = 0; i < pl.splits; i++)
+            {
+                const ParamRange r = param_range(i * lo + std::min(i, rem), lo + (i < rem ? 1 : 0),
+                                                 d.w_bits == 4 ? 256 : 128, d.K, group, sbytes, d.w_bits, sc_row, zp_row);
+                sc_pieces = std::max(sc_pieces, r.sc_pieces), zp_pieces = std::max(zp_pieces, r.zp_pieces);
+            }
+            pl.sm_sc_row = 16 * sc_pieces, pl.sm_zp_row = 16 * zp_pieces;
+        }
+        pl.pset_sm = pset > 0 ? 16 * (pl.sm_sc_row + pl.sm_zp_row) : 0;
+    }
+    // The longest batch whose parameters (two buffers, or one when a single batch holds every tile of a CTA) and
+    // partial sums fit next to `best_res` CTAs per SM: every batch ends with a reduction over the warps during which
+    // no weight is asked for, 2.5 to 3 us each.
     pl.batch = 0;
     for (int b = std::min(kBatch, steps); b >= 1; b--)
     {
         if (b < steps && (b * sets) % pl.depth != 0)
             continue; // every batch but the last is a whole number of trips through the register pipeline
-        if ((int)DirectSmem(sets, pl.mb, pl.warps, b, pl.tq, pset, pl.xfrag_bytes).total + 1024 <= smem_cap / best_res)
+        const int nbuf = b >= steps ? 1 : 2;
+        if ((int)DirectSmem(sets, pl.mb, pl.warps, b, pl.tq, pl.pset_sm, pl.xfrag_bytes, nbuf).total + 1024 <=
+            smem_cap / best_res)
         {
             pl.batch = b;
+            pl.param_bufs = nbuf;
             break;
         }
     }
     if (pl.batch == 0)
         return false;
-    pl.smem_bytes = DirectSmem(sets, pl.mb, pl.warps, pl.batch, pl.tq, pset, pl.xfrag_bytes).total;
+    pl.smem_bytes = DirectSmem(sets, pl.mb, pl.warps, pl.batch, pl.tq, pl.pset_sm, pl.xfrag_bytes, pl.param_bufs).total;
     // L2 window ahead of the register pipeline: about 192 KB per CTA (whole tiles, shared by the K splits)
     const int row_bytes = d.w_bits == 4 ? d.K / 2 : d.K;
     pl.prefetch_tiles = std::max(1, std::min(64, (192 * 1024 * pl.splits) / (sets * 16 * row_bytes)));
@@ -1318,7 +1378,7 @@ cudaError_t gemv_direct_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& 
                     (!plan.dual || (ok16(w2->scale) && ok16(w2->zp)));
     {
         const DirectSmem lay(plan.dual ? 2 : 1, plan.mb, plan.warps, plan.batch, plan.tq,
-                             p.bulk_params ? plan.pset_bytes : 0, plan.xfrag_bytes);
+                             p.bulk_params ? plan.pset_sm : 0, plan.xfrag_bytes, plan.param_bufs);
         p.off_bars = (int)lay.params;
         p.off_red = p.off_bars + (int)lay.bars;
         p.off_ss = p.off_red + (int)lay.red;
@@ -1327,7 +1387,8 @@ cudaError_t gemv_direct_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& 
     p.group_units = p.group / ue;
     p.group_magic = p.group_units > 1 ? (uint32_t)((0x100000000ull + p.group_units - 1) / p.group_units) : 0u;
     p.sc_row_bytes = p.G * (p.scale_f32 ? 4 : 2);
-    p.range_params = p.bulk_params && plan.splits > 1 && p.sc_row_bytes % 16 == 0 && p.zp_row_bytes % 16 == 0;
+    p.range_params = p.bulk_params && plan.range_layout;
+    p.sm_sc_row = plan.sm_sc_row, p.sm_zp_row = plan.sm_zp_row;
     p.pmode = 0;
     if (p.bulk_params && d.w_bits == 4 && p.group == 128 && !p.scale_f32 && (p.G & 1) == 0)
         p.pmode = 1;

@@ -54,6 +54,11 @@ struct GemvPlan
     int direct = 0;             // served by the register-pipeline kernel (dq_gemv_direct.cu) instead of the ring kernel
     int prefetch_tiles = 0;     // register-pipeline kernel: L2 prefetch window in row tiles
     int l1_lines = 0;           // register-pipeline kernel: weight loads take lines in L1
+    int sm_sc_row = 0;          // register-pipeline kernel: bytes of a row of scales in shared memory
+    int sm_zp_row = 0;          // ... and of a row of zero-points
+    int range_layout = 0;       // ... which hold only the columns of a CTA's own K range
+    int pset_sm = 0;            // ... shared memory per tile and weight set for both
+    int param_bufs = 2;         // ... and the number of batches of parameters held at a time (1: one batch is all)
 };
 
 int set_error(nnf_b200_ctx* ctx, int status, const std::string& msg);
