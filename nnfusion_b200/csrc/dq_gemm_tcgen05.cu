@@ -274,19 +274,12 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
     const uint32_t tmem_base = *tmem_slot;
     WorkList<C::KB_PER_CHUNK> work(p);
     Segment sg;
-    // Launched as the programmatic dependent of the kernel before it on the stream, this CTA may have started while
-    // that kernel's last CTAs were still running.  Weights, scales and zero-points are constants: the raw-chunk
-    // producer and the conversion into tensor memory start at once.  The activations, the result, the addend and
-    // the workspace may be the earlier kernel's: the activation producer waits before its first load and the
-    // conversion warps before their first read-back.  The launch behind this one may be scheduled from here on.
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == TMA_WARP)
     {
         // ------------------------------------------------------------ TMA producer: activation tiles
         if (lane == 0)
         {
-            asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             uint32_t pr = 0; // pairs of k-blocks of this CTA so far: ring position (every segment starts a pair)
             while (ok && work.next(p, sg))
@@ -446,7 +439,6 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
             q.z = __ldg(n.zp + (WBITS == 4 ? q.g >> 1 : q.g));
         };
         bool asked = false;
-        bool dep_waited = false; // has this thread waited for the kernel before this one on the stream?
 
         while (ok && work.next(p, sg))
         {
@@ -473,10 +465,6 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
 #pragma unroll
                 for (int v = 0; v < NV; v++)
                     raw[v] = lds128(row + (uint32_t)(((j * NV + v) ^ (r & 7)) * 16));
-                // One arrival per k-block read; the tile's last k-block also stands in for the k-blocks that a
-                // short last chunk does not have.
-                mbar_arrive_n(empty_w(sw), kb == KB - 1 ? (uint32_t)(C::KB_PER_CHUNK - j) : 1u);
-
                 const float sc = p.scale_f32 ? __uint_as_float(q.s) : __half2float(__ushort_as_half((unsigned short)q.s));
                 const uint32_t zq = WBITS == 4 ? (q.z >> (4 * (q.g & 1))) & 0xFu : q.z;
                 ask(n, kb + 2 * C::DQ_GROUPS, sg.kb1 - 1, q);
@@ -526,12 +514,22 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                 const int rel = kb - sg.kb0;
                 const uint32_t prv = pr_base + (uint32_t)(rel >> 1);
                 const int pq = prv % C::PAIRS, sa = 2 * pq + (rel & 1);
-                if (!wait_or_abort(empty(pq), ((prv / C::PAIRS) & 1u) ^ 1u, abort_flag))
+                // (the vote brings the warp's lanes back together: each polled on its own and may have left the loop
+                // on a different round, and the tensor-memory store below is a warp-wide instruction that every
+                // lane must execute in the same issue)
+                if (!__all_sync(0xffffffffu, wait_or_abort(empty(pq), ((prv / C::PAIRS) & 1u) ^ 1u, abort_flag)))
                     return false;
                 tcgen05_fence_after();
                 tmem_st_32x32(tmem_base + lane_addr + (uint32_t)(C::A_COL0 + sa * C::A_STAGE_COLS), a);
                 tcgen05_wait_st();
                 tcgen05_fence_before();
+                // The raw stage goes back to the copy engine only now: one arrival per k-block read (the tile's last
+                // k-block also stands in for the k-blocks that a short last chunk does not have).  The arrival must
+                // not be issued before the shared-memory loads have delivered, and nothing but an instruction that
+                // needs their data makes an instruction wait for them: the tensor-memory store above consumed every
+                // loaded word.  (Issued right behind the loads, the arrival could pass a load that was queued behind
+                // a burst of global stores; the next chunk then landed first and the load read its bytes.)
+                mbar_arrive_n(empty_w(sw), kb == KB - 1 ? (uint32_t)(C::KB_PER_CHUNK - j) : 1u);
                 // a segment that ends on the first k-block of a pair: its threads also stand in for the second
                 mbar_arrive_n(full(pq), ((rel & 1) == 0 && kb == sg.kb1 - 1) ? 2u : 1u);
                 return true;
@@ -592,14 +590,9 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                     }
                 }
             };
-            if (!dep_waited)
-            {
-                asm volatile("griddepcontrol.wait;" ::: "memory"); // y, the addend and the workspace are touched from here on
-                dep_waited = true;
-            }
             ask_gates(col0);
-            if (ok)
-                ok = wait_or_abort(acc_full, si & 1u, abort_flag);
+            // (a vote again: the tensor-memory loads below are warp-wide instructions)
+            ok = __all_sync(0xffffffffu, ok && wait_or_abort(acc_full, si & 1u, abort_flag));
             si++;
             if (!ok)
                 break;
@@ -834,17 +827,8 @@ cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap
         configured[dev] = true;
     }
     (void)cudaGetLastError();
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(C::THREADS);
-    cfg.dynamicSmemBytes = C::SMEM_BYTES;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, dq_gemm_kernel<WBITS, GATED>, p, tx, tw);
+    dq_gemm_kernel<WBITS, GATED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, tx, tw);
+    return cudaGetLastError();
 }
 } // namespace
 

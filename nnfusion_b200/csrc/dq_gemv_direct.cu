@@ -32,6 +32,7 @@
 #include <cuda_runtime.h>
 #include <algorithm>
 #include <cstdio>
+#include <mutex>
 
 #include "nnf_internal.h"
 #include "sm100_ptx.cuh"
@@ -77,6 +78,10 @@ struct DirectParams
     int xfrag_bytes;    // shared memory per warp for the activation fragments of batch rows 8..15 (0 when M <= 8)
     int prefetch_tiles; // L2 prefetch window in row tiles ahead of the register pipeline (0: no prefetch)
     int l1_lines;       // weight loads take lines in L1 (long launches)
+    // K split: the CTAs that share a tile form a thread-block cluster (grid.y = cluster size = splits) and their sums
+    // meet in the shared memory of the cluster's first CTA instead of the workspace.
+    int cluster;
+    int off_cslots;     // shared-memory offset of [splits][batch][slot_floats] floats (cluster only)
     int slot_floats;
     float eps;
     // shared-memory byte offsets (DirectSmem, computed once on the host)
@@ -228,9 +233,9 @@ __host__ __device__ inline ParamRange param_range(int slice0, int slices, int sl
 // Shared-memory footprint, shared by host and device.  All sizes in bytes.
 struct DirectSmem
 {
-    size_t params, bars, red, ss, flags, xsm, total;
+    size_t params, bars, red, ss, flags, xsm, cslots, total;
     __host__ __device__ DirectSmem(int sets, int mb, int warps, int batch, int tq, int pset_bytes, int xfrag_bytes,
-                                   int nbuf = 2)
+                                   int nbuf = 2, int cluster_splits = 0)
     {
         // (scales, zero-points) of a batch per weight set; two batches take turns unless one holds all tiles
         params = (size_t)nbuf * batch * sets * pset_bytes;
@@ -238,8 +243,10 @@ struct DirectSmem
         red = sizeof(float) * (size_t)warps * batch * sets * mb * 8 * tq * 4;
         ss = sizeof(float) * ((size_t)warps * 8 * mb + 8 * mb);
         flags = sizeof(int) * (2 * kBatch + 4); // last-arriver flags, call numbers, "all peers answered"
-        xsm = (size_t)warps * xfrag_bytes;
-        total = params + bars + red + ss + flags + xsm;
+        xsm = ((size_t)warps * xfrag_bytes + 15) / 16 * 16;
+        // the splits' sums of a batch, in the first CTA of a cluster: [split][tile][sets * mb * 128 + 8 * mb] floats
+        cslots = sizeof(float) * (size_t)cluster_splits * batch * ((size_t)sets * mb * 128 + 8 * mb);
+        total = params + bars + red + ss + flags + xsm + cslots;
     }
 };
 
@@ -300,6 +307,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     int issue_row = tile0 * 16 + g;            // row g of the next tile to ask for
     int to_issue = has_slice ? nstages : 0;    // stages not asked for yet
     const bool l1_lines = p.l1_lines != 0;
+    // A CTA's shared memory may be written from another CTA of its cluster only once it runs: everybody arrives at
+    // the cluster's barrier here and waits there before its first such write (end of the first batch).
+    if (p.cluster)
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    bool cluster_met = false;
     auto issue = [&](Stage& b, int s) {
         const uint8_t* base = (s == 0 ? p.wq[0] : p.wq[1]) + lane_off;
         const uint8_t* r0 = base + (size_t)min(issue_row, last_row) * (size_t)p.row_bytes;
@@ -979,6 +991,78 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
             if (ar)
                 ar_end(first, count, false);
         }
+        else if (p.cluster)
+        {
+            // The splits of these tiles are the CTAs of one cluster (rank = split).  1. every CTA writes its sums
+            // (and its share of the sum of squares) into the first CTA's shared memory; 2. the cluster meets at its
+            // barrier; 3. the first CTA adds the splits' sums in split order.  No global memory, no counter, and
+            // the hardware schedules a cluster's CTAs together: nothing here can wait for a CTA that is not running.
+            float* const cslots = reinterpret_cast<float*>(smem_raw + p.off_cslots);
+            uint32_t remote; // the same array in the first CTA
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(cslots)), "r"(0));
+            const uint32_t my_part = remote + (uint32_t)(split * p.batch * p.slot_floats) * 4u;
+            if (!cluster_met)
+            {
+                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+                cluster_met = true;
+            }
+            auto put = [&](uint32_t float_index, float v) {
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(my_part + float_index * 4u), "f"(v) : "memory");
+            };
+            for (int idx = tid; idx < count * per_tile; idx += nthreads)
+            {
+                const int j = idx >> pt_shift, e = idx & (per_tile - 1);
+                int row, m, o;
+                decode(e, row, m, o);
+                if (m >= p.M)
+                    continue;
+                put((uint32_t)(j * p.slot_floats + o), sum_warps(j, 0, e));
+                if (DUAL)
+                    put((uint32_t)(j * p.slot_floats + MB * 128 + o), sum_warps(j, 1, e));
+            }
+            if (p.rmsnorm)
+                for (int idx = tid; idx < count * MPAD; idx += nthreads)
+                {
+                    const int j = idx / MPAD, mm = idx - j * MPAD;
+                    put((uint32_t)(j * p.slot_floats + SETS * MB * 128 + mm), ss_cta[mm]);
+                }
+            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            if (tid < count)
+                last_flag[tid] = (split == 0);
+            __syncthreads();
+            if (ar)
+                ar_begin(first, count, true);
+            if (split == 0)
+                for (int idx = tid; idx < count * per_tile; idx += nthreads)
+                {
+                    const int j = idx >> pt_shift, e = idx & (per_tile - 1);
+                    int row, m, o;
+                    decode(e, row, m, o);
+                    const int n = (tile0 + first + j) * 16 + row;
+                    if (m < p.M && n < p.N)
+                    {
+                        float a0 = 0.f, a1 = 0.f, ssum = 0.f;
+                        for (int sp = 0; sp < p.splits; sp++) // fixed order: repeatable
+                        {
+                            const float* slot = cslots + (size_t)(sp * p.batch + j) * p.slot_floats;
+                            a0 += slot[o];
+                            if (DUAL)
+                                a1 += slot[MB * 128 + o];
+                            if (p.rmsnorm)
+                                ssum += slot[SETS * MB * 128 + m];
+                        }
+                        if (ar)
+                            ar_put(j, m, n, a0);
+                        else
+                            store_y(m, n, finish(a0, a1, ssum, m, n));
+                    }
+                }
+            if (ar)
+                ar_end(first, count, true);
+            // another batch follows: its sums must not land before the first CTA has read these
+            if (first + count < ntiles)
+                asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
         else
         {
             // 1. publish this split's sums (and its share of the sum of squares)
@@ -1136,11 +1220,58 @@ cudaError_t ensure_smem(size_t smem)
 }
 
 template <int WBITS, int MB, bool XSPLIT, bool DUAL, int PD, int PMODE, bool M1>
-cudaError_t launch(const DirectParams& p, const nnf::GemvPlan& plan, cudaStream_t stream)
+cudaError_t launch(const DirectParams& p_in, const nnf::GemvPlan& plan, cudaStream_t stream)
 {
     cudaError_t e = ensure_smem<WBITS, MB, XSPLIT, DUAL, PD, PMODE, M1>(plan.smem_bytes);
     if (e != cudaSuccess)
         return e;
+    DirectParams p = p_in;
+    if (p.cluster)
+    {
+        // Clusters only when the device holds all of them at once (asked once per launch shape and device).
+        struct Seen
+        {
+            int dev, splits, threads, ctas;
+            size_t smem;
+            bool ok;
+        };
+        static std::mutex mu;
+        static Seen seen[64]; // launch shapes asked about so far (a full table answers "no clusters" for new ones)
+        static int nseen = 0;
+        int dev = 0;
+        e = cudaGetDevice(&dev);
+        if (e != cudaSuccess)
+            return e;
+        std::lock_guard<std::mutex> lock(mu);
+        const Seen* hit = nullptr;
+        for (int i = 0; i < nseen; i++)
+        {
+            const Seen& q = seen[i];
+            if (q.dev == dev && q.splits == plan.splits && q.threads == plan.warps * 32 &&
+                q.ctas == plan.ctas_per_split && q.smem == (size_t)plan.smem_bytes)
+                hit = &q;
+        }
+        if (!hit && nseen < 64)
+        {
+            cudaLaunchConfig_t qc = {};
+            qc.gridDim = dim3(plan.ctas_per_split, plan.splits);
+            qc.blockDim = dim3(plan.warps * 32);
+            qc.dynamicSmemBytes = plan.smem_bytes;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = 1, qa[0].val.clusterDim.y = (unsigned)plan.splits, qa[0].val.clusterDim.z = 1;
+            qc.attrs = qa, qc.numAttrs = 1;
+            int clusters = 0;
+            const cudaError_t qe = cudaOccupancyMaxActiveClusters(
+                &clusters, dq_gemv_direct_kernel<WBITS, MB, XSPLIT, DUAL, PD, PMODE, M1>, &qc);
+            (void)cudaGetLastError();
+            seen[nseen] = Seen{dev, plan.splits, plan.warps * 32, plan.ctas_per_split, (size_t)plan.smem_bytes,
+                               qe == cudaSuccess && clusters >= plan.ctas_per_split};
+            hit = &seen[nseen++];
+        }
+        if (!hit || !hit->ok)
+            p.cluster = 0;
+    }
     (void)cudaGetLastError(); // do not inherit a stale error left behind by an unrelated earlier call
     // Programmatic dependent launch: the CTAs may start while the launch before this one on the stream is still
     // finishing; they stream their weights at once and wait (griddepcontrol.wait) before touching anything else.
@@ -1149,8 +1280,16 @@ cudaError_t launch(const DirectParams& p, const nnf::GemvPlan& plan, cudaStream_
     cfg.blockDim = dim3(plan.warps * 32);
     cfg.dynamicSmemBytes = plan.smem_bytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     nnf::overlap_attribute(attr, &cfg.numAttrs);
+    if (p.cluster)
+    {
+        attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+        attr[cfg.numAttrs].val.clusterDim.x = 1;
+        attr[cfg.numAttrs].val.clusterDim.y = (unsigned)plan.splits;
+        attr[cfg.numAttrs].val.clusterDim.z = 1;
+        cfg.numAttrs++;
+    }
     cfg.attrs = attr;
     return cudaLaunchKernelEx(&cfg, dq_gemv_direct_kernel<WBITS, MB, XSPLIT, DUAL, PD, PMODE, M1>, p);
 }
@@ -1291,6 +1430,20 @@ bool gemv_direct_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, Ge
     if (pl.batch == 0)
         return false;
     pl.smem_bytes = DirectSmem(sets, pl.mb, pl.warps, pl.batch, pl.tq, pl.pset_sm, pl.xfrag_bytes, pl.param_bufs).total;
+    // K split 2 to 8 ways: the splits of a tile as one cluster, if the sums' meeting place fits as well.  The launch
+    // falls back to the workspace when the device cannot hold every cluster at once: 148 SMs hold 74 clusters of 2
+    // one-per-SM CTAs but only 45 of 3, 33 of 4, 26 of 5, 22 of 6 and 15 of 7 or 8 (the occupancy calculator's
+    // answers), so in practice halves of K meet in shared memory and finer splits do when a split has few CTAs.
+    pl.cluster = 0;
+#ifndef NNF_NO_CLUSTER
+    if (pl.splits >= 2 && pl.splits <= 8)
+    {
+        const size_t with = DirectSmem(sets, pl.mb, pl.warps, pl.batch, pl.tq, pl.pset_sm, pl.xfrag_bytes, pl.param_bufs,
+                                       pl.splits).total;
+        if ((int)with + 1024 <= smem_cap / best_res)
+            pl.cluster = 1, pl.smem_bytes = with;
+    }
+#endif
     // L2 window ahead of the register pipeline: about 192 KB per CTA (whole tiles, shared by the K splits)
     const int row_bytes = d.w_bits == 4 ? d.K / 2 : d.K;
     pl.prefetch_tiles = std::max(1, std::min(64, (192 * 1024 * pl.splits) / (sets * 16 * row_bytes)));
@@ -1378,11 +1531,14 @@ cudaError_t gemv_direct_dispatch(const nnf_b200_linear_desc& d, const GemvPlan& 
                     (!plan.dual || (ok16(w2->scale) && ok16(w2->zp)));
     {
         const DirectSmem lay(plan.dual ? 2 : 1, plan.mb, plan.warps, plan.batch, plan.tq,
-                             p.bulk_params ? plan.pset_sm : 0, plan.xfrag_bytes, plan.param_bufs);
+                             p.bulk_params ? plan.pset_sm : 0, plan.xfrag_bytes, plan.param_bufs,
+                             plan.cluster ? plan.splits : 0);
         p.off_bars = (int)lay.params;
         p.off_red = p.off_bars + (int)lay.bars;
         p.off_ss = p.off_red + (int)lay.red;
         p.off_flags = p.off_ss + (int)lay.ss;
+        p.off_cslots = p.off_flags + (int)lay.flags + (int)lay.xsm;
+        p.cluster = plan.cluster;
     }
     p.group_units = p.group / ue;
     p.group_magic = p.group_units > 1 ? (uint32_t)((0x100000000ull + p.group_units - 1) / p.group_units) : 0u;

@@ -58,6 +58,7 @@ struct GemvPlan
     int sm_zp_row = 0;          // ... and of a row of zero-points
     int range_layout = 0;       // ... which hold only the columns of a CTA's own K range
     int pset_sm = 0;            // ... shared memory per tile and weight set for both
+    int cluster = 0;            // ... the splits of a tile form a thread-block cluster (sums meet in shared memory)
     int param_bufs = 2;         // ... and the number of batches of parameters held at a time (1: one batch is all)
 };
 

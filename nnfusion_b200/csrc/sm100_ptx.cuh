@@ -119,15 +119,18 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map)
 // ------------------------------------------------------------------------------------------------ tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t columns)
 {
+    __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(columns)
                  : "memory");
 }
 __device__ __forceinline__ void tmem_relinquish()
 {
+    __syncwarp();
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns)
 {
+    __syncwarp();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before()
@@ -140,10 +143,12 @@ __device__ __forceinline__ void tcgen05_fence_after()
 }
 __device__ __forceinline__ void tcgen05_wait_ld()
 {
+    __syncwarp();
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tcgen05_wait_st()
 {
+    __syncwarp();
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // The mbarrier gets one arrival once every tcgen05.mma issued so far by this thread has completed.
@@ -171,8 +176,11 @@ __device__ __forceinline__ void tcgen05_mma_ss(uint32_t d_tmem, uint64_t a_desc,
 }
 
 // 32 lanes x 32 columns of 32-bit: thread i of the warp receives lane (base lane + i), columns [c, c+32).
+// (warp-wide instructions: every lane must issue them together, and lanes that took different paths or left a polling
+// loop on different rounds are not back together by themselves: hence the __syncwarp() in front of each)
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 {
+    __syncwarp();
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
                  "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -186,6 +194,7 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32])
 {
+    __syncwarp();
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
                  "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"

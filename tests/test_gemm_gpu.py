@@ -238,3 +238,28 @@ def test_output_padding_untouched_with_shared_tiles():
     assert not torch.isnan(y).any()
     _check(y.cpu().numpy(), oracle_linear(x, w), TOL_F16, tight=2e-3)
     op.ctx.device_status()
+
+
+@pytest.mark.parametrize("M,N,K,dual,launches", [
+    (4096, 11008, 4096, False, 60),     # 9 tiles per CTA
+    (256, 3584, 8192, True, 300),       # every tile shared by 6 CTAs, segments as short as one chunk, two passes
+])
+def test_back_to_back_launches_repeat_bit_for_bit(M, N, K, dual, launches):
+    """Many launches in a row, no host synchronisation in between, must all give the first launch's bits.  Two races
+    showed up only this way, as a few weight rows of one tile wrong for every batch row in a few launches per hundred:
+    lanes that had left a polling loop on different rounds issued a warp-wide tensor-memory store apart, and a raw
+    weight stage was handed back to the copy engine before the shared-memory loads from it had delivered."""
+    import torch
+    from nnfusion_b200.linear import DequantDot, DeviceWeight
+
+    rng = np.random.Generator(np.random.PCG64(5 + M))
+    dev = "cuda:0"
+    ws = [DeviceWeight.from_host(synth.make_weights(rng, N, K, 4, 128), dev) for _ in range(2 if dual else 1)]
+    op = DequantDot(*ws)
+    x = torch.from_numpy(synth.make_x(rng, M, K, np.float16)).to(dev)
+    first = op(x).clone()
+    outs = [op(x) for _ in range(launches)]
+    torch.cuda.synchronize()
+    differ = [i for i, y in enumerate(outs) if not torch.equal(y, first)]
+    op.ctx.device_status()
+    assert not differ, f"launches {differ[:8]} of {launches} differ from the first"

@@ -213,3 +213,25 @@ def test_k_split_with_idle_warps_after_other_kernels_used_shared_memory(K, M, N,
     w = synth.make_weights(rng, N, K, bits, group, sd)
     w2 = synth.make_weights(rng, N, K, bits, group, sd) if dual else None
     _check(gpu_linear(x, w, w2), oracle_linear(x, w, w2), TOL_F32 if xdt == np.float32 else TOL_F16)
+
+
+@pytest.mark.parametrize("M,N,K,split_k,dual,norm", [
+    (1, 33 * 74 * 16, 8192, 0, False, False),   # halves of K as clusters of 2; 33 tiles per CTA: two batches
+    (3, 2048, 8192, 0, True, True),             # RMSNorm + SiLU(gate) * up: sums of squares meet in shared memory too
+    (2, 208, 4096, 4, False, False),            # 13 tiles: 13 clusters of 4 fit at once
+    (1, 160, 7168, 7, False, True),             # 10 clusters of 7
+    (5, 1024, 2048, 8, False, False),           # one slice per CTA, clusters of 8 (the device holds 15 at most: workspace)
+])
+def test_k_splits_that_meet_in_shared_memory(M, N, K, split_k, dual, norm):
+    """K splits whose CTAs form a thread-block cluster add their sums in the first CTA's shared memory; the same
+    descriptor falls back to the workspace when the device cannot hold every cluster at once.  Either way the result
+    matches the oracle and repeats bit for bit."""
+    rng = np.random.Generator(np.random.PCG64(77 + N))
+    x = synth.make_x(rng, M, K, np.float16)
+    w = synth.make_weights(rng, N, K, 4, 128)
+    w2 = synth.make_weights(rng, N, K, 4, 128) if dual else None
+    gain = rng.uniform(0.5, 1.5, K).astype(np.float32) if norm else None
+    ys = gpu_linear(x, w, w2, gain=gain, split_k=split_k, repeat=3)
+    ref = oracle_linear(x, w, w2, gain=gain)
+    assert orc.max_rel_err(ys[0], ref) <= TOL_F16
+    assert all(np.array_equal(ys[0], y) for y in ys[1:])
