@@ -274,12 +274,19 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
     const uint32_t tmem_base = *tmem_slot;
     WorkList<C::KB_PER_CHUNK> work(p);
     Segment sg;
+    // Launched as the programmatic dependent of the kernel before it on the stream, this CTA may have started while
+    // that kernel's last CTAs were still running.  Weights, scales and zero-points are constants: the raw-chunk
+    // producer and the conversion into tensor memory start at once.  The activations, the result, the addend and
+    // the workspace may be the earlier kernel's: the activation producer waits before its first load and the
+    // conversion warps before their first read-back.  The launch behind this one may be scheduled from here on.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == TMA_WARP)
     {
         // ------------------------------------------------------------ TMA producer: activation tiles
         if (lane == 0)
         {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
             uint32_t pr = 0; // pairs of k-blocks of this CTA so far: ring position (every segment starts a pair)
             while (ok && work.next(p, sg))
@@ -439,6 +446,7 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
             q.z = __ldg(n.zp + (WBITS == 4 ? q.g >> 1 : q.g));
         };
         bool asked = false;
+        bool dep_waited = false; // has this thread waited for the kernel before this one on the stream?
 
         while (ok && work.next(p, sg))
         {
@@ -590,6 +598,11 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                     }
                 }
             };
+            if (!dep_waited)
+            {
+                asm volatile("griddepcontrol.wait;" ::: "memory"); // y, the addend and the workspace are touched from here on
+                dep_waited = true;
+            }
             ask_gates(col0);
             // (a vote again: the tensor-memory loads below are warp-wide instructions)
             ok = __all_sync(0xffffffffu, ok && wait_or_abort(acc_full, si & 1u, abort_flag));
@@ -827,8 +840,17 @@ cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap
         configured[dev] = true;
     }
     (void)cudaGetLastError();
-    dq_gemm_kernel<WBITS, GATED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(p, tx, tw);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, dq_gemm_kernel<WBITS, GATED>, p, tx, tw);
 }
 } // namespace
 
