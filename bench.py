@@ -475,6 +475,14 @@ def extra_measurements(torch, budget_s=90.0):
         also[name] = {"us": round(ms * 1e3 / steps, 1), "TFLOP/s": round(tf, 1),
                       "frac_of_bf16_burst_peak": round(tf / peaks["bf16_tflops"], 4),
                       "frac_of_bf16_sustained_peak": round(tf / peaks["bf16_tflops_sustained"], 4)}
+        if M <= 256:
+            # a launch this short is partly host-bound when every call goes through Python: the same calls replayed
+            # from a CUDA graph, as a serving loop would issue them
+            gsteps = 6 * steps
+            msg = timed_graph_steps(torch, [lambda: op(x, y)], gsteps, 5, repeats=7)
+            tfg = 2.0 * M * N * K * (2 if dual else 1) * gsteps / (msg * 1e-3) / 1e12
+            also[name].update({"us_graph_replay": round(msg * 1e3 / gsteps, 1),
+                               "frac_of_bf16_burst_peak_graph_replay": round(tfg / peaks["bf16_tflops"], 4)})
 
     def layer7b(name, copies=2, steps=200):
         """Configuration 4: one 7B-shaped decoder layer at decode time, 2048 cached rows, the token at position

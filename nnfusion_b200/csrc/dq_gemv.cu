@@ -1061,6 +1061,7 @@ __global__ void __launch_bounds__((kMaxWarps + 1) * 32, 1)
             const int st = first + j;
             if (use_full && !mbar_wait(full_s + 8 * slot, parity))
                 timed_out = true;
+            __syncwarp(); // lanes may leave the polling loop on different rounds; the MMAs below are warp-wide
             if (lsu)
                 cp_async_wait(p.depth - 1); // this thread's pieces of tile st have landed
             float4* my = reinterpret_cast<float4*>(red + warp * warp_stride + j * SETS * per_tile);

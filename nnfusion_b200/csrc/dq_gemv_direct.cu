@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
     // A CTA's shared memory may be written from another CTA of its cluster only once it runs: everybody arrives at
     // the cluster's barrier here and waits there before its first such write (end of the first batch).
     if (p.cluster)
-        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     bool cluster_met = false;
     auto issue = [&](Stage& b, int s) {
         const uint8_t* base = (s == 0 ? p.wq[0] : p.wq[1]) + lane_off;
@@ -1003,7 +1003,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
             const uint32_t my_part = remote + (uint32_t)(split * p.batch * p.slot_floats) * 4u;
             if (!cluster_met)
             {
-                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+                asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
                 cluster_met = true;
             }
             auto put = [&](uint32_t float_index, float v) {
@@ -1026,7 +1026,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                     const int j = idx / MPAD, mm = idx - j * MPAD;
                     put((uint32_t)(j * p.slot_floats + SETS * MB * 128 + mm), ss_cta[mm]);
                 }
-            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
             if (tid < count)
                 last_flag[tid] = (split == 0);
             __syncthreads();
@@ -1061,7 +1061,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1)
                 ar_end(first, count, true);
             // another batch follows: its sums must not land before the first CTA has read these
             if (first + count < ntiles)
-                asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+                asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
         }
         else
         {
