@@ -1369,6 +1369,9 @@ bool gemv_direct_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d, Ge
             score -= 0.5; // narrow CTAs pay the fixed cost of a CTA (activation fragments, barriers) too often
         if (warps * std::min(resident, per_sm) < 8)
             score -= 0.1; // too few warps per SM to keep enough bytes in flight
+        if (s == 2 && smin == 2)
+            score += 0.1; // halves of K meet in a cluster's shared memory, finer splits through the workspace: about
+                          // 2 us per launch (measured: two [7168,8192] matrices 20.4 us cut 3 ways, 15.8 us in halves)
         if (score > best_score + 1e-9)
             best_score = score, best_s = s, best_per = per_split, best_res = std::min(resident, per_sm);
     };
