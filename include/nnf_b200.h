@@ -173,7 +173,13 @@ NNF_B200_API size_t nnf_b200_linear_workspace_bytes(const nnf_b200_ctx* ctx, con
 /* Launch shape the library would use for a descriptor, for tuning and reporting:
  * out[0] kernel (NNF_B200_KERNEL_*), out[1] warps per CTA, out[2] split-K factor,
  * out[3] load-ring depth, out[4] CTAs, out[5] dynamic shared memory in bytes,
- * out[6..7] zero.  ctx may be NULL (a 148-SM device is assumed).  No reference
+ * out[6] row tiles between two meetings of a CTA's warps, out[7] bits: 1 the CTAs
+ * that share a tile ask to be launched as a thread-block cluster (their sums then
+ * meet in shared memory; the launch falls back to the workspace when the device
+ * cannot hold every cluster at once), 2 weight loads take lines in L1, 4 only the
+ * scale / zero-point columns of a CTA's own K range are kept in shared memory,
+ * 8 one batch holds every tile of a CTA.  out[6..7] are zero for the tensor-core
+ * kernel.  ctx may be NULL (a 148-SM device is assumed).  No reference
  * counterpart: the reference leaves such choices to cuBLAS. */
 NNF_B200_API int nnf_b200_linear_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* desc, int32_t out[8]);
 

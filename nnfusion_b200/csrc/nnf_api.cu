@@ -329,6 +329,9 @@ int nnf_b200_linear_plan(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc* de
             return rc;
         out[1] = plan.warps, out[2] = plan.splits, out[3] = plan.depth, out[4] = plan.splits * plan.ctas_per_split;
         out[5] = (int32_t)plan.smem_bytes;
+        out[6] = plan.batch;
+        out[7] = (plan.cluster ? 1 : 0) | (plan.l1_lines ? 2 : 0) | (plan.range_layout ? 4 : 0) |
+                 (plan.direct && plan.param_bufs == 1 ? 8 : 0);
     }
     return NNF_B200_OK;
 }

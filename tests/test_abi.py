@@ -78,3 +78,61 @@ def test_workspace_sizes_without_a_device(lib):
     assert need(32, 128, 256) == 256 + 2 * 1 * 128 * 256 * 4
     # small M: split-K scratch only
     assert need(1, 11008, 4096) < 1 << 20
+
+
+def _plan(lib, M, N, K, bits=4, group=128, x=L.F16, scale=L.F16, epilogue=0, split_k=0, prologue=0):
+    d = L.LinearDesc(M=M, N=N, K=K, w_bits=bits, group_size=group, x_dtype=x, y_dtype=x, scale_dtype=scale,
+                     prologue=prologue, epilogue=epilogue, split_k=split_k)
+    out = (ctypes.c_int32 * 8)()
+    assert lib.nnf_b200_linear_plan(None, ctypes.byref(d), ctypes.byref(out)) == L.OK
+    return dict(kernel=out[0], warps=out[1], splits=out[2], ctas=out[4], smem=out[5], batch=out[6],
+                cluster=bool(out[7] & 1), l1_lines=bool(out[7] & 2), own_columns=bool(out[7] & 4),
+                one_batch=bool(out[7] & 8))
+
+
+def test_small_m_launch_shapes_without_a_device(lib):
+    """The small-M planner's choices for the shapes whose timings the design notes quote (no context: a 148-SM
+    device is assumed): how K is cut, which cuts may meet in a cluster's shared memory, which launches take L1
+    lines for their weight loads, and how many tiles lie between two meetings of a CTA's warps."""
+    silu = L.EPILOGUE_SILU_MUL
+    # 7B decode: K = 4096 is 16 slices of 128 bytes, one CTA covers it; every tile of a CTA in one batch
+    p = _plan(lib, 1, 11008, 4096)
+    assert (p["kernel"], p["splits"], p["warps"], p["ctas"]) == (L.KERNEL_GEMV, 1, 16, 148)
+    assert not p["cluster"] and not p["l1_lines"] and p["one_batch"] and p["batch"] == 5
+    # K = 8192 has to be cut: in halves, which ask for clusters of two
+    for N in (8192, 10240, 28672):
+        p = _plan(lib, 1, N, 8192)
+        assert p["splits"] == 2 and p["cluster"] and p["own_columns"] and not p["l1_lines"], (N, p)
+    # two weight sets: halves as well (a three-way cut rates a little better on SM load alone), L1 lines only
+    # when the pair is larger than L2
+    p = _plan(lib, 1, 7168, 8192, epilogue=silu)
+    assert p["splits"] == 2 and p["cluster"] and not p["l1_lines"]
+    p = _plan(lib, 1, 28672, 8192, epilogue=silu)
+    assert p["splits"] == 2 and p["cluster"] and p["l1_lines"] and p["one_batch"] and p["batch"] == 25
+    # 70B down projection: K cut 7 ways (no cluster wish beyond what fits is decided at launch), L1 lines, one batch
+    p = _plan(lib, 1, 8192, 28672)
+    assert p["splits"] == 7 and p["l1_lines"] and p["own_columns"] and p["one_batch"] and p["batch"] == 25
+    # 7B down projection: 43 slices, four ways, no L1 lines
+    p = _plan(lib, 1, 4096, 11008)
+    assert p["splits"] == 4 and not p["l1_lines"]
+    # configuration 1: uint8 rows of 4096 bytes are 32 slices: halves, cluster
+    p = _plan(lib, 16, 4096, 4096, bits=8, group=4096, x=L.F32, scale=L.F32)
+    assert p["splits"] == 2 and p["cluster"]
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+@pytest.mark.parametrize("bits,group", [(4, 128), (8, 128), (8, 0)])
+def test_small_m_plans_stay_inside_the_device(lib, M, bits, group):
+    """Over a sweep of shapes: shared memory within the 227 KB a CTA may have, at most 16 warps, at most 32 tiles per
+    batch, no more CTAs than four per SM, and a forced split honoured."""
+    for N in (16, 160, 1024, 4096, 11008, 28672, 128256):
+        for K in (256, 1024, 3584, 4096, 5120, 8192, 11008, 14336, 28672):
+            g = group if group else K
+            if K % g or (bits == 4 and K % 256) or K % 128:
+                continue
+            p = _plan(lib, M, N, K, bits=bits, group=g)
+            if p["kernel"] != L.KERNEL_GEMV:
+                continue
+            assert 1 <= p["warps"] <= 16 and p["smem"] <= 227 * 1024, (N, K, p)
+            assert 1 <= p["batch"] <= 32 and 1 <= p["ctas"] <= 4 * 148, (N, K, p)
+            assert not p["cluster"] or 2 <= p["splits"] <= 8, (N, K, p)
