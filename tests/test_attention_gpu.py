@@ -60,11 +60,20 @@ def test_ragged_lengths(pos):
     _check(outs[0], ref)
 
 
-@pytest.mark.parametrize("H,Hkv", [(8, 8), (8, 2), (64, 8), (3, 1)])
+@pytest.mark.parametrize("H,Hkv", [(8, 8), (8, 2), (64, 8), (3, 1), (12, 2), (10, 5), (16, 1)])
 def test_grouped_queries(H, Hkv):
+    """Groups of 1, 2, 3, 4, 6, 8 and 16 query heads per key/value head."""
     outs, ref, caches, caches_ref = _run(H, Hkv, 600, 555, seed=50 + H)
     _check(outs[0], ref)
     np.testing.assert_array_equal(caches[1], caches_ref[1])
+
+
+def test_grouped_queries_long_cache_repeats():
+    # 64 query heads on 8 key/value heads over 4097 rows (a 70B-shaped decode step), three calls: same bits
+    outs, ref, _, _ = _run(64, 8, 4100, 4096, seed=59, calls=3)
+    _check(outs[0], ref)
+    np.testing.assert_array_equal(outs[0], outs[1])
+    np.testing.assert_array_equal(outs[0], outs[2])
 
 
 def test_without_rotary_and_last_row_of_the_cache():
