@@ -38,11 +38,14 @@ namespace
 {
 using namespace nnf::ptx;
 
-template <int WBITS>
+// BXV: batch rows per tile, 256, or 64 for launches of up to 64 batch rows (a quarter of the activation bytes, of the
+// tensor time and of the accumulator to read back and, for shared tiles, to pass through the workspace).
+template <int WBITS, int BXV = 256>
 struct Cfg
 {
+    static_assert(BXV == 256 || BXV == 64, "batch tile of 256 or 64 rows");
     static constexpr int BN = 128;              // weight rows per tile  (UMMA M, TMEM lanes)
-    static constexpr int BX = 256;              // batch rows per tile   (UMMA N, accumulator columns)
+    static constexpr int BX = BXV;              // batch rows per tile   (UMMA N, accumulator columns)
     static constexpr int BK = 64;               // k-block: one 128-byte swizzle row of fp16
     // One ring index for the x tile in shared memory and the converted weights in tensor memory, and one pair of
     // barriers for every PAIR of k-blocks: the MMA thread, whose own time per k-block is what bounds the kernel,
@@ -59,7 +62,7 @@ struct Cfg
     static constexpr int W_STAGE_BYTES = BN * 128;
     static constexpr int A_COL0 = BX;            // first TMEM column of the A stages
     static constexpr int A_STAGE_COLS = BK / 2;  // 64 fp16 per lane = 32 columns
-    static constexpr int TMEM_COLS = 512;
+    static constexpr int TMEM_COLS = BX == 256 ? 512 : 256;
     // full / empty per ring stage, full / empty per raw-weight stage, then: accumulator full, accumulator drained,
     // partial sums written, ticket known
     static constexpr int NUM_BARRIERS = 2 * PAIRS + 2 * WSTAGES + 4;
@@ -211,12 +214,12 @@ __device__ __forceinline__ float gate_value(const GemmParams& p, uint32_t bits)
 }
 
 // GATED: y holds the gate products of an earlier launch (the second half of SiLU(gate) * up).
-template <int WBITS, bool GATED>
-__global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
+template <int WBITS, bool GATED, int BXV>
+__global__ void __launch_bounds__(Cfg<WBITS, BXV>::THREADS, 1)
     dq_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_x,
                    const __grid_constant__ CUtensorMap tmap_w)
 {
-    using C = Cfg<WBITS>;
+    using C = Cfg<WBITS, BXV>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* xs = base;                                             // [STAGES][BX][128 B]
@@ -572,7 +575,11 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
             // 32-column pieces of D with both loads in flight, then lets the MMA thread have the accumulator back.
             const int n_base = (sg.tile / p.m_tiles) * C::BN, m0 = (sg.tile % p.m_tiles) * C::BX;
             const int nrow = n_base + r;
-            static_assert(C::BX / 32 == 2 * C::DQ_GROUPS, "two 32-column pieces per warp");
+            // 256 columns: two 32-column pieces per warp.  64 columns: one piece for the warps of the first two groups,
+            // none for the others (which only say that they are done with D).
+            static_assert(C::BX / 32 == 2 * C::DQ_GROUPS || C::BX / 32 == C::DQ_GROUPS / 2, "pieces per warp");
+            constexpr bool kWide = C::BX / 32 == 2 * C::DQ_GROUPS;
+            const bool has_piece = kWide || grp < C::BX / 32; // the same for every lane of a warp
             const int col0 = grp * 32, col1 = (grp + C::DQ_GROUPS) * 32;
             // With the gate products in y, those of the first piece are asked for before the accumulator is ready.
             const float bias = (p.has_bias && nrow < p.N) ? __ldg(p.bias + nrow) : 0.f;
@@ -603,7 +610,8 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                 asm volatile("griddepcontrol.wait;" ::: "memory"); // y, the addend and the workspace are touched from here on
                 dep_waited = true;
             }
-            ask_gates(col0);
+            if (has_piece)
+                ask_gates(col0);
             // (a vote again: the tensor-memory loads below are warp-wide instructions)
             ok = __all_sync(0xffffffffu, ok && wait_or_abort(acc_full, si & 1u, abort_flag));
             si++;
@@ -612,27 +620,53 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
             tcgen05_fence_after();
             if (sg.whole)
             {
-                uint32_t d[32];
-                tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col0, d);
-                tcgen05_wait_ld();
-                if (nrow < p.N)
+                if constexpr (kWide)
                 {
-#pragma unroll
-                    for (int jx = 0; jx < 32; jx++)
-                        if (m0 + col0 + jx < p.M)
-                            store_value(p, m0 + col0 + jx, nrow, __uint_as_float(d[jx]), gated, gate_value(p, gb[GATED ? jx : 0]), bias);
+                    uint32_t d[32];
+                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col0, d);
+                    tcgen05_wait_ld();
+                    if (nrow < p.N)
+                    {
+    #pragma unroll
+                        for (int jx = 0; jx < 32; jx++)
+                            if (m0 + col0 + jx < p.M)
+                                store_value(p, m0 + col0 + jx, nrow, __uint_as_float(d[jx]), gated, gate_value(p, gb[GATED ? jx : 0]), bias);
+                    }
+                    ask_gates(col1);
+                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col1, d);
+                    tcgen05_wait_ld();
+                    tcgen05_fence_before();
+                    mbar_arrive(acc_empty); // this thread's last read of D: the next segment may overwrite it
+                    if (nrow < p.N)
+                    {
+    #pragma unroll
+                        for (int jx = 0; jx < 32; jx++)
+                            if (m0 + col1 + jx < p.M)
+                                store_value(p, m0 + col1 + jx, nrow, __uint_as_float(d[jx]), gated, gate_value(p, gb[GATED ? jx : 0]), bias);
+                    }
                 }
-                ask_gates(col1);
-                tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col1, d);
-                tcgen05_wait_ld();
-                tcgen05_fence_before();
-                mbar_arrive(acc_empty); // this thread's last read of D: the next segment may overwrite it
-                if (nrow < p.N)
+                else
                 {
+                    if (has_piece)
+                    {
+                        uint32_t d[32];
+                        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col0, d);
+                        tcgen05_wait_ld();
+                        tcgen05_fence_before();
+                        mbar_arrive(acc_empty);
+                        if (nrow < p.N)
+                        {
 #pragma unroll
-                    for (int jx = 0; jx < 32; jx++)
-                        if (m0 + col1 + jx < p.M)
-                            store_value(p, m0 + col1 + jx, nrow, __uint_as_float(d[jx]), gated, gate_value(p, gb[GATED ? jx : 0]), bias);
+                            for (int jx = 0; jx < 32; jx++)
+                                if (m0 + col0 + jx < p.M)
+                                    store_value(p, m0 + col0 + jx, nrow, __uint_as_float(d[jx]), gated, gate_value(p, gb[GATED ? jx : 0]), bias);
+                        }
+                    }
+                    else
+                    {
+                        tcgen05_fence_before();
+                        mbar_arrive(acc_empty);
+                    }
                 }
             }
             else
@@ -643,6 +677,7 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
                 const int c_last = cta_of_unit((long long)(sg.tile + 1) * p.cpt - 1, U, G);
                 const uint32_t pieces = (uint32_t)(c_last - c_first + 1);
                 float* mine = p.slots + (size_t)slot_of((int)blockIdx.x, sg.tile, U, G, p.cpt) * C::SLOT_FLOATS;
+                if constexpr (kWide)
                 {
                     uint32_t d[32];
                     tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col0, d);
@@ -657,6 +692,22 @@ __global__ void __launch_bounds__(Cfg<WBITS>::THREADS, 1)
 #pragma unroll
                     for (int jx = 0; jx < 32; jx++)
                         mine[(size_t)(col1 + jx) * C::BN + r] = __uint_as_float(d[jx]);
+                }
+                else if (has_piece)
+                {
+                    uint32_t d[32];
+                    tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)col0, d);
+                    tcgen05_wait_ld();
+                    tcgen05_fence_before();
+                    mbar_arrive(acc_empty);
+#pragma unroll
+                    for (int jx = 0; jx < 32; jx++)
+                        mine[(size_t)(col0 + jx) * C::BN + r] = __uint_as_float(d[jx]);
+                }
+                else
+                {
+                    tcgen05_fence_before();
+                    mbar_arrive(acc_empty);
                 }
                 __threadfence();
                 mbar_arrive(part_done);
@@ -820,10 +871,10 @@ __global__ void __launch_bounds__(256) prep_activations_kernel(const void* x, co
     }
 }
 
-template <int WBITS, bool GATED>
+template <int WBITS, bool GATED, int BXV>
 cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap& tw, int grid, cudaStream_t stream)
 {
-    using C = Cfg<WBITS>;
+    using C = Cfg<WBITS, BXV>;
     static bool configured[nnf::kMaxDevices] = {}; // the attribute belongs to the device that is current
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -833,7 +884,7 @@ cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap
         return cudaErrorInvalidDevice;
     if (!configured[dev])
     {
-        e = cudaFuncSetAttribute(dq_gemm_kernel<WBITS, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(dq_gemm_kernel<WBITS, GATED, BXV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)C::SMEM_BYTES);
         if (e != cudaSuccess)
             return e;
@@ -850,7 +901,7 @@ cudaError_t launch(const GemmParams& p, const CUtensorMap& tx, const CUtensorMap
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, dq_gemm_kernel<WBITS, GATED>, p, tx, tw);
+    return cudaLaunchKernelEx(&cfg, dq_gemm_kernel<WBITS, GATED, BXV>, p, tx, tw);
 }
 } // namespace
 
@@ -879,7 +930,7 @@ struct GemmLayout
 static GemmLayout gemm_layout(const nnf_b200_ctx* ctx, const nnf_b200_linear_desc& d)
 {
     GemmLayout L{};
-    L.bx = 256;
+    L.bx = d.M <= 64 ? 64 : 256; // a narrow batch tile for small batches
     L.m_tiles = (d.M + L.bx - 1) / L.bx;
     L.n_tiles = (d.N + 127) / 128;
     L.tiles = L.m_tiles * L.n_tiles;
@@ -891,6 +942,8 @@ static GemmLayout gemm_layout(const nnf_b200_ctx* ctx, const nnf_b200_linear_des
     // about 30 k-blocks' worth of time on top of the 8 of an epilogue) or at tile boundaries only (the CTA with the
     // most tiles sets the time): whichever the estimate, in k-block times, favours.
     const double kb = d.K / 64.0;
+    // (the same estimate serves the narrow tile: with a lower price for its smaller shared tiles the up projection
+    // at 17 to 64 batch rows was cut across all SMs and took 24.9 us instead of 23.5)
     const double t_split = (double)L.tiles * kb / sms + 8.0 + 30.0;
     const double t_whole = (double)((L.tiles + sms - 1) / sms) * (kb + 8.0);
     L.whole_tiles = t_whole <= t_split;
@@ -899,7 +952,7 @@ static GemmLayout gemm_layout(const nnf_b200_ctx* ctx, const nnf_b200_linear_des
     else
         L.grid = (int)(units < sms ? units : sms);
     L.counter_bytes = ((size_t)L.tiles * sizeof(uint32_t) + 255) / 256 * 256;
-    L.slot_bytes = (size_t)2 * L.grid * 128 * 256 * sizeof(float); // two slots of one fp32 tile per CTA
+    L.slot_bytes = (size_t)2 * L.grid * 128 * L.bx * sizeof(float); // two slots of one fp32 tile per CTA
     L.prepass_bytes = needs_prepass(d) ? ((size_t)d.M * d.K * sizeof(__half) + 255) / 256 * 256 : 0;
     return L;
 }
@@ -1005,9 +1058,15 @@ int gemm_launch(nnf_b200_ctx* ctx, cudaStream_t stream, const nnf_b200_linear_de
             return set_error(ctx, NNF_B200_ECUDA, "cuTensorMapEncodeTiled failed for the weight tensor");
         twv = *tw;
         const bool gated = silu_mul && pass == 1;
-        const cudaError_t e = d.w_bits == 4
-                                  ? (gated ? launch<4, true>(p, tx, twv, L.grid, stream) : launch<4, false>(p, tx, twv, L.grid, stream))
-                                  : (gated ? launch<8, true>(p, tx, twv, L.grid, stream) : launch<8, false>(p, tx, twv, L.grid, stream));
+        cudaError_t e;
+        if (L.bx == 256)
+            e = d.w_bits == 4
+                    ? (gated ? launch<4, true, 256>(p, tx, twv, L.grid, stream) : launch<4, false, 256>(p, tx, twv, L.grid, stream))
+                    : (gated ? launch<8, true, 256>(p, tx, twv, L.grid, stream) : launch<8, false, 256>(p, tx, twv, L.grid, stream));
+        else
+            e = d.w_bits == 4
+                    ? (gated ? launch<4, true, 64>(p, tx, twv, L.grid, stream) : launch<4, false, 64>(p, tx, twv, L.grid, stream))
+                    : (gated ? launch<8, true, 64>(p, tx, twv, L.grid, stream) : launch<8, false, 64>(p, tx, twv, L.grid, stream));
         if (e != cudaSuccess)
             return set_error(ctx, NNF_B200_ECUDA, std::string("dq_gemm launch: ") + cudaGetErrorString(e));
         ctx->launches++;

@@ -74,8 +74,10 @@ def test_workspace_sizes_without_a_device(lib):
     assert plain == (tiles * 4 + 255) // 256 * 256 + slots
     assert need(4096, 11008, 4096, x=L.F32) == plain + 4096 * 4096 * 2
     assert need(4096, 11008, 4096, prologue=L.PROLOGUE_RMSNORM) == plain + 4096 * 4096 * 2
-    # a launch with fewer units of work than SMs uses fewer CTAs, hence fewer slots
-    assert need(32, 128, 256) == 256 + 2 * 1 * 128 * 256 * 4
+    # a launch with fewer units of work than SMs uses fewer CTAs, hence fewer slots; up to 64 batch rows the tile
+    # (and with it a slot) is 64 rows wide instead of 256
+    assert need(32, 128, 256) == 256 + 2 * 1 * 128 * 64 * 4
+    assert need(65, 128, 256) == 256 + 2 * 1 * 128 * 256 * 4
     # small M: split-K scratch only
     assert need(1, 11008, 4096) < 1 << 20
 

@@ -263,3 +263,34 @@ def test_back_to_back_launches_repeat_bit_for_bit(M, N, K, dual, launches):
     differ = [i for i, y in enumerate(outs) if not torch.equal(y, first)]
     op.ctx.device_status()
     assert not differ, f"launches {differ[:8]} of {launches} differ from the first"
+
+
+@pytest.mark.parametrize("M", [17, 48, 64, 65])
+@pytest.mark.parametrize("N,K,bits,dual", [
+    (1024, 4096, 4, False),    # 8 tiles of 16 chunks on 128 CTAs: every tile shared by 16 CTAs
+    (1001, 2048, 4, True),     # odd N (scalar stores), SiLU(gate) * up in two passes
+    (640, 1024, 8, False),     # uint8 weights
+])
+def test_narrow_batch_tile(M, N, K, bits, dual):
+    """Up to 64 batch rows the tensor-core kernel works on tiles of 64 batch rows (a quarter of the accumulator, of
+    the activation tile and of a shared tile's slot); 65 rows are the first to take the 256-row tile again.  Both
+    against the oracle, and three calls in a row bit for bit."""
+    rng = np.random.Generator(np.random.PCG64(300 + M + N))
+    x = synth.make_x(rng, M, K, np.float16)
+    w = synth.make_weights(rng, N, K, bits, 128)
+    w2 = synth.make_weights(rng, N, K, bits, 128) if dual else None
+    ys = gpu_linear(x, w, w2, kernel=L.KERNEL_GEMM, repeat=3)
+    _check(ys[0], oracle_linear(x, w, w2), TOL_F16, tight=3e-3)
+    assert all(np.array_equal(ys[0], y) for y in ys[1:])
+
+
+def test_narrow_batch_tile_epilogues_and_padding():
+    rng = np.random.Generator(np.random.PCG64(333))
+    M, N, K = 40, 520, 2048
+    x = synth.make_x(rng, M, K, np.float32)
+    w = synth.make_weights(rng, N, K, 4, 128)
+    bias = rng.standard_normal(N).astype(np.float32)
+    gain = rng.uniform(0.5, 1.5, K).astype(np.float32)
+    # fp32 activations and RMSNorm through the pre-pass, bias, fp32 output
+    y = gpu_linear(x, w, gain=gain, bias=bias, kernel=L.KERNEL_GEMM, out_dtype=np.float32)
+    _check(y, oracle_linear(x, w, gain=gain, bias=bias, out_dtype=np.float32), TOL_F16, tight=2e-3)
