@@ -483,6 +483,10 @@ def extra_measurements(torch, budget_s=90.0):
             tfg = 2.0 * M * N * K * (2 if dual else 1) * gsteps / (msg * 1e-3) / 1e12
             also[name].update({"us_graph_replay": round(msg * 1e3 / gsteps, 1),
                                "frac_of_bf16_burst_peak_graph_replay": round(tfg / peaks["bf16_tflops"], 4)})
+            if M <= 64:
+                # this few batch rows are bound by the weight bytes, not by the tensor core: the HBM fraction as well
+                gbs = linear_bytes(M, N, K) * gsteps / (msg * 1e-3) / 1e9
+                also[name]["frac_of_hbm_peak_graph_replay"] = round(gbs / peaks["hbm_gbs"], 4)
 
     def layer7b(name, copies=2, steps=200):
         """Configuration 4: one 7B-shaped decoder layer at decode time, 2048 cached rows, the token at position
@@ -552,7 +556,7 @@ def extra_measurements(torch, budget_s=90.0):
     attention("decode_attention_32x2048x128")
     layer7b("layer7b_decode_pos2048")
     mlp70b_one_gpu("mlp70b_decode_whole_mlp_m1_one_gpu")
-    for M in (256, 1024, 4096):
+    for M in (32, 256, 1024, 4096):     # 32: the 64-row batch tile of the tensor-core kernel
         gemm(f"prefill_gemm_up_m{M}_11008x4096", M, 11008, 4096)
     gemm("prefill_gemm_down_m4096_4096x11008", 4096, 4096, 11008)
     return also
